@@ -1,0 +1,135 @@
+"""ctypes view of the C ABI in include/decoding_attn_b200.h (libdecoding_attn_b200.so).
+
+This is the binding a non-C++ host would write; the parity tests and the benchmark call the
+library through it, with torch only providing the device (or pinned host) memory.  Importing it
+fails loudly when the library has not been built: there is no fallback path.
+"""
+import ctypes
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libdecoding_attn_b200.so")
+
+DA_OK, DA_ERR_INVALID_ARG, DA_ERR_UNSUPPORTED, DA_ERR_WORKSPACE, DA_ERR_CUDA, DA_ERR_TIMEOUT = range(6)
+
+EXPORTS = ["da_decode_fwd", "da_decode_fwd_host", "da_decode_workspace_bytes", "da_decode_num_splits",
+           "da_merge_partials", "da_device_status", "da_status_string", "da_last_error", "da_launch_count"]
+
+
+class DecodeArgs(ctypes.Structure):
+    """Mirror of ``da_decode_args_t``."""
+    _fields_ = [
+        ("struct_size", ctypes.c_uint32), ("is_bf16", ctypes.c_int32), ("is_alibi", ctypes.c_int32),
+        ("num_splits", ctypes.c_int32),
+        ("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p), ("o", ctypes.c_void_p),
+        ("cu_seq_k", ctypes.c_void_p),
+        ("max_seq_k", ctypes.c_int64), ("batch", ctypes.c_int64), ("head_q", ctypes.c_int64),
+        ("head_k", ctypes.c_int64), ("dim", ctypes.c_int64), ("dim_v", ctypes.c_int64),
+        ("q_row_stride", ctypes.c_int64), ("k_row_stride", ctypes.c_int64), ("v_row_stride", ctypes.c_int64),
+        ("o_row_stride", ctypes.c_int64),
+        ("softmax_scale", ctypes.c_float), ("reserved0", ctypes.c_uint32),
+        ("lse", ctypes.c_void_p), ("o_f32", ctypes.c_void_p),
+        ("kv_pos_offset", ctypes.c_void_p), ("kv_total_len", ctypes.c_void_p),
+        ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
+        ("stream", ctypes.c_void_p),
+    ]
+
+
+class DecodingAttnError(RuntimeError):
+    def __init__(self, status, message):
+        super().__init__(f"decoding_attn_b200 status {status}: {message}")
+        self.status = status
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: run `python -m decoding_attention_b200.build` "
+                              "(there is no CPU or PyTorch fallback)")
+        l = ctypes.CDLL(LIB_PATH)
+        l.da_decode_fwd.restype = ctypes.c_int
+        l.da_decode_fwd.argtypes = [ctypes.POINTER(DecodeArgs)]
+        l.da_decode_fwd_host.restype = ctypes.c_int
+        l.da_decode_fwd_host.argtypes = [ctypes.POINTER(DecodeArgs)]
+        l.da_decode_workspace_bytes.restype = ctypes.c_size_t
+        l.da_decode_workspace_bytes.argtypes = [ctypes.POINTER(DecodeArgs)]
+        l.da_decode_num_splits.restype = ctypes.c_int
+        l.da_decode_num_splits.argtypes = [ctypes.POINTER(DecodeArgs)]
+        l.da_merge_partials.restype = ctypes.c_int
+        l.da_merge_partials.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64,
+                                        ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                        ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                        ctypes.c_int32, ctypes.c_void_p]
+        l.da_device_status.restype = ctypes.c_int
+        l.da_status_string.restype = ctypes.c_char_p
+        l.da_status_string.argtypes = [ctypes.c_int]
+        l.da_last_error.restype = ctypes.c_char_p
+        l.da_launch_count.restype = ctypes.c_uint64
+        _lib = l
+    return _lib
+
+
+def check(status):
+    if status != DA_OK:
+        raise DecodingAttnError(status, lib().da_last_error().decode())
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def make_args(q, k, v, o, cu_seq_k, max_seq_k, dim_v, is_alibi=False, softmax_scale=None, lse=None, o_f32=None,
+              kv_pos_offset=None, kv_total_len=None, workspace=None, num_splits=0, stream=0, packed=False):
+    """Fill a DecodeArgs from torch tensors (device tensors, or host tensors for the *_host call)."""
+    import torch
+    a = DecodeArgs()
+    a.struct_size = ctypes.sizeof(DecodeArgs)
+    a.is_bf16 = int(q.dtype == torch.bfloat16)
+    a.is_alibi = int(bool(is_alibi))
+    a.num_splits = int(num_splits)
+    a.q, a.k, a.v, a.o, a.cu_seq_k = _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(cu_seq_k)
+    a.max_seq_k = int(max_seq_k)
+    a.batch = cu_seq_k.numel() - 1
+    a.head_q, a.dim = q.shape[1], q.shape[2]
+    a.head_k = k.shape[1]
+    a.dim_v = int(dim_v)
+    if not packed:
+        a.q_row_stride, a.k_row_stride = q.stride(0), k.stride(0)
+        a.v_row_stride = v.stride(0) if v is not None else 0
+        a.o_row_stride = o.stride(0) if o is not None else 0
+    a.softmax_scale = float(softmax_scale) if softmax_scale else 0.0
+    a.lse, a.o_f32 = _ptr(lse), _ptr(o_f32)
+    a.kv_pos_offset, a.kv_total_len = _ptr(kv_pos_offset), _ptr(kv_total_len)
+    if workspace is not None:
+        a.workspace = workspace.data_ptr()
+        a.workspace_bytes = workspace.numel() * workspace.element_size()
+    a.stream = int(stream) if stream else None
+    return a
+
+
+def decode_fwd(args):
+    check(lib().da_decode_fwd(ctypes.byref(args)))
+
+
+def decode_fwd_host(args):
+    check(lib().da_decode_fwd_host(ctypes.byref(args)))
+
+
+def workspace_bytes(args):
+    return lib().da_decode_workspace_bytes(ctypes.byref(args))
+
+
+def num_splits(args):
+    return lib().da_decode_num_splits(ctypes.byref(args))
+
+
+def device_status():
+    return lib().da_device_status()
+
+
+def launch_count():
+    return lib().da_launch_count()

@@ -1,0 +1,469 @@
+// C ABI of libdecoding_attn_b200.so: argument checks, split heuristic, scratch management and
+// kernel dispatch.  It does the work of the reference's set_dmha_fwd_params / run_dmha_fwd
+// (csrc/ops/decoding_attn.cpp:13-68) and of its DA_FP16_SWITCH / DA_HEADDIM_SWITCH macros
+// (csrc/common/common.h:62-96), but returns status codes instead of calling exit().
+#include <atomic>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/decoding_attn_b200.h"
+#include "da_internal.h"
+
+namespace da {
+
+namespace {
+
+thread_local char g_err[512] = "";
+std::atomic<uint64_t> g_launches{0};
+
+int fail(int code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+// Kernel status word: one per device (a __device__ variable lives in every device's copy of the
+// module); kernels that give up a bounded wait write kStatusWaitTimeout into it.
+__device__ int g_status_word;
+
+constexpr int kMaxDevices = 64;
+struct DeviceState {
+    std::mutex mu;
+    int *status_ptr = nullptr;
+    void *scratch = nullptr;
+    size_t scratch_bytes = 0;
+    void *staging = nullptr;  // device copies of host tensors for da_decode_fwd_host
+    size_t staging_bytes = 0;
+    int sm_count = 0;
+};
+DeviceState g_dev[kMaxDevices];
+
+int device_state(DeviceState **out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(DA_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= kMaxDevices) return fail(DA_ERR_CUDA, "device ordinal %d out of range", dev);
+    DeviceState &st = g_dev[dev];
+    std::lock_guard<std::mutex> lock(st.mu);
+    if (!st.status_ptr) {
+        e = cudaGetSymbolAddress(reinterpret_cast<void **>(&st.status_ptr), g_status_word);
+        if (e != cudaSuccess) return fail(DA_ERR_CUDA, "cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        e = cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return fail(DA_ERR_CUDA, "cudaDeviceGetAttribute: %s", cudaGetErrorString(e));
+    }
+    *out = &st;
+    return DA_OK;
+}
+
+enum class Shape { kD64, kD96, kD128, kD256, kMla, kNone };
+
+Shape shape_of(int64_t dim, int64_t dim_v, bool has_v) {
+    if (has_v) {
+        if (dim == 64 && dim_v == 64) return Shape::kD64;
+        if (dim == 96 && dim_v == 96) return Shape::kD96;
+        if (dim == 128 && dim_v == 128) return Shape::kD128;
+        if (dim == 256 && dim_v == 256) return Shape::kD256;
+        return Shape::kNone;
+    }
+    if (dim == 576 && dim_v == 512) return Shape::kMla;
+    return Shape::kNone;
+}
+
+int heads_per_cta(Shape s, int group) {
+    if (s == Shape::kMla) return 1;
+    const char *env = getenv("DA_HEADS_PER_CTA");
+    if (env) {
+        int g = atoi(env);
+        if ((g == 1 || g == 2 || g == 4) && group % g == 0) return g;
+    }
+    if (group % 4 == 0) return 4;
+    if (group % 2 == 0) return 2;
+    return 1;
+}
+
+SplitVariantInfo variant_info(Shape s, int heads) {
+    switch (s) {
+        case Shape::kD64: return split_info_d64(heads);
+        case Shape::kD96: return split_info_d96(heads);
+        case Shape::kD128: return split_info_d128(heads);
+        case Shape::kD256: return split_info_d256(heads);
+        case Shape::kMla: return split_info_mla_simt(heads);
+        default: return {0, 0, 0};
+    }
+}
+
+struct Plan {
+    Shape shape;
+    int heads;       // query heads per CTA
+    int head_chunks; // CTAs per KV head
+    int num_splits;
+    int chunk_keys;
+    size_t scratch_bytes;
+};
+
+// Pick the number of key-range splits.  The host does not know the sequence lengths (cu_seq_k is a
+// device array), only max_seq_k, so the grid is (splits, kv heads * head chunks, batch) and CTAs
+// whose range lies beyond their sequence's end retire at once.  Aim for several waves of CTAs over
+// all SMs, but keep at least kMinTiles tiles per CTA (pipeline fill, partial write-out) and at most
+// kMaxTiles (tail effect when lengths vary inside a batch).
+int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
+    const bool has_v = a.v != nullptr;
+    Shape shape = shape_of(a.dim, a.dim_v, has_v);
+    if (shape == Shape::kNone) {
+        return fail(DA_ERR_UNSUPPORTED,
+                    "unsupported (dim=%lld, dim_v=%lld, v %s): supported are (64,64) (96,96) (128,128) (256,256) "
+                    "with v and (576,512) without",
+                    (long long)a.dim, (long long)a.dim_v, has_v ? "given" : "NULL");
+    }
+    const int group = (int)(a.head_q / a.head_k);
+    const int heads = heads_per_cta(shape, group);
+    const SplitVariantInfo info = variant_info(shape, heads);
+    const int tile = info.tile_keys;
+    const int64_t units = a.batch * a.head_k * (group / heads);
+    const int64_t max_len = a.max_seq_k > 0 ? a.max_seq_k : 1;
+    const int64_t tiles_per_unit = (max_len + tile - 1) / tile;
+
+    constexpr int kMinTiles = 4, kMaxTiles = 16, kWaves = 4;
+    int64_t splits;
+    const char *env = getenv("DA_NUM_SPLITS");
+    if (a.num_splits > 0) {
+        splits = a.num_splits;
+    } else if (env && atoi(env) > 0) {
+        splits = atoi(env);
+    } else {
+        const int64_t slots = (int64_t)sm_count * (info.ctas_per_sm > 0 ? info.ctas_per_sm : 1);
+        int64_t tiles_per_cta = (units * tiles_per_unit) / (slots * kWaves);
+        if (tiles_per_cta < kMinTiles) tiles_per_cta = kMinTiles;
+        if (tiles_per_cta > kMaxTiles) tiles_per_cta = kMaxTiles;
+        splits = (tiles_per_unit + tiles_per_cta - 1) / tiles_per_cta;
+    }
+    if (splits < 1) splits = 1;
+    if (splits > tiles_per_unit) splits = tiles_per_unit;
+    if (splits > 65535) splits = 65535;
+    int64_t chunk_tiles = (tiles_per_unit + splits - 1) / splits;
+    splits = (tiles_per_unit + chunk_tiles - 1) / chunk_tiles;  // drop splits that would be empty for every row
+
+    plan->shape = shape;
+    plan->heads = heads;
+    plan->head_chunks = group / heads;
+    plan->num_splits = (int)splits;
+    plan->chunk_keys = (int)(chunk_tiles * tile);
+    plan->scratch_bytes =
+        splits > 1 ? (size_t)a.batch * a.head_q * splits * ((size_t)a.dim_v + 1) * sizeof(float) : 0;
+    return DA_OK;
+}
+
+int check_args(const da_decode_args_t *a) {
+    if (!a) return fail(DA_ERR_INVALID_ARG, "args is NULL");
+    if (a->struct_size != sizeof(da_decode_args_t)) {
+        return fail(DA_ERR_INVALID_ARG, "struct_size %u != sizeof(da_decode_args_t) %zu", a->struct_size,
+                    sizeof(da_decode_args_t));
+    }
+    // Same conditions as the reference's DA_CHECKs (csrc/ops/decoding_attn.cpp:16-22).
+    if (!a->q || !a->k || !a->cu_seq_k) return fail(DA_ERR_INVALID_ARG, "q, k and cu_seq_k must not be NULL");
+    if (!a->o && !a->o_f32) return fail(DA_ERR_INVALID_ARG, "one of o / o_f32 must be given");
+    if (a->batch <= 0 || a->head_q <= 0 || a->head_k <= 0 || a->dim <= 0 || a->dim_v <= 0) {
+        return fail(DA_ERR_INVALID_ARG, "batch, head_q, head_k, dim and dim_v must be positive");
+    }
+    if (a->head_q % a->head_k != 0) {
+        return fail(DA_ERR_INVALID_ARG, "head_q (%lld) must be a multiple of head_k (%lld)", (long long)a->head_q,
+                    (long long)a->head_k);
+    }
+    if (a->dim > 576 || a->dim_v > 512) return fail(DA_ERR_INVALID_ARG, "dim must be <= 576 and dim_v <= 512");
+    if (a->batch > 65535) return fail(DA_ERR_INVALID_ARG, "batch must be <= 65535");
+    if (a->max_seq_k < 0) return fail(DA_ERR_INVALID_ARG, "max_seq_k must not be negative");
+    const uintptr_t align_or = (uintptr_t)a->q | (uintptr_t)a->k | (uintptr_t)a->v | (uintptr_t)a->o |
+                               (uintptr_t)a->o_f32 | (uintptr_t)a->workspace;
+    if (align_or & 15u) return fail(DA_ERR_INVALID_ARG, "q, k, v, o, o_f32 and workspace must be 16-byte aligned");
+    const int64_t strides[4] = {a->q_row_stride, a->k_row_stride, a->v_row_stride, a->o_row_stride};
+    const int64_t mins[4] = {a->head_q * a->dim, a->head_k * a->dim, a->head_k * (a->v ? a->dim_v : a->dim),
+                             a->head_q * a->dim_v};
+    for (int i = 0; i < 4; ++i) {
+        if (strides[i] == 0) continue;
+        if (strides[i] < mins[i] || strides[i] % 8 != 0) {
+            return fail(DA_ERR_INVALID_ARG, "row stride %d must be a multiple of 8 elements and cover a row", i);
+        }
+    }
+    return DA_OK;
+}
+
+}  // namespace
+
+void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+}  // namespace da
+
+using namespace da;
+
+extern "C" {
+
+size_t da_decode_workspace_bytes(const da_decode_args_t *a) {
+    if (check_args(a) != DA_OK) return 0;
+    DeviceState *st = nullptr;
+    if (device_state(&st) != DA_OK) return 0;
+    Plan plan;
+    if (make_plan(*a, st->sm_count, &plan) != DA_OK) return 0;
+    return plan.scratch_bytes;
+}
+
+int da_decode_num_splits(const da_decode_args_t *a) {
+    if (check_args(a) != DA_OK) return -1;
+    DeviceState *st = nullptr;
+    if (device_state(&st) != DA_OK) return -1;
+    Plan plan;
+    if (make_plan(*a, st->sm_count, &plan) != DA_OK) return -1;
+    return plan.num_splits;
+}
+
+int da_decode_fwd(const da_decode_args_t *a) {
+    int rc = check_args(a);
+    if (rc != DA_OK) return rc;
+    DeviceState *st = nullptr;
+    rc = device_state(&st);
+    if (rc != DA_OK) return rc;
+    Plan plan;
+    rc = make_plan(*a, st->sm_count, &plan);
+    if (rc != DA_OK) return rc;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
+
+    float *scratch = nullptr;
+    if (plan.scratch_bytes) {
+        if (a->workspace) {
+            if (a->workspace_bytes < plan.scratch_bytes) {
+                return fail(DA_ERR_WORKSPACE, "workspace has %zu bytes, %zu needed", a->workspace_bytes,
+                            plan.scratch_bytes);
+            }
+            scratch = static_cast<float *>(a->workspace);
+        } else {
+            std::lock_guard<std::mutex> lock(st->mu);
+            if (st->scratch_bytes < plan.scratch_bytes) {
+                // Grow-only.  The old buffer may still be in use by queued kernels: free it only after
+                // the device has drained (growth is rare: sizes settle after the first few calls).
+                if (st->scratch) {
+                    cudaDeviceSynchronize();
+                    cudaFree(st->scratch);
+                    st->scratch = nullptr;
+                    st->scratch_bytes = 0;
+                }
+                size_t want = plan.scratch_bytes + plan.scratch_bytes / 4;
+                cudaError_t e = cudaMalloc(&st->scratch, want);
+                if (e != cudaSuccess) {
+                    return fail(DA_ERR_WORKSPACE, "cudaMalloc(%zu) for split scratch: %s", want,
+                                cudaGetErrorString(e));
+                }
+                st->scratch_bytes = want;
+            }
+            scratch = static_cast<float *>(st->scratch);
+        }
+    }
+
+    SplitParams p;
+    memset(&p, 0, sizeof(p));
+    p.q = a->q;
+    p.k = a->k;
+    p.v = a->v ? a->v : a->k;  // csrc/ops/decoding_attn.cpp:30
+    p.o = a->o;
+    p.o_f32 = a->o_f32;
+    p.lse = a->lse;
+    p.cu_seq_k = a->cu_seq_k;
+    p.kv_pos_offset = a->kv_pos_offset;
+    p.kv_total_len = a->kv_total_len;
+    p.status = st->status_ptr;
+    p.q_row_stride = a->q_row_stride ? a->q_row_stride : a->head_q * a->dim;
+    p.k_row_stride = a->k_row_stride ? a->k_row_stride : a->head_k * a->dim;
+    p.v_row_stride = a->v ? (a->v_row_stride ? a->v_row_stride : a->head_k * a->dim_v) : p.k_row_stride;
+    p.o_row_stride = a->o_row_stride ? a->o_row_stride : a->head_q * a->dim_v;
+    p.head_q = (int)a->head_q;
+    p.head_k = (int)a->head_k;
+    p.group = (int)(a->head_q / a->head_k);
+    p.head_chunks = plan.head_chunks;
+    p.batch = (int)a->batch;
+    p.num_splits = plan.num_splits;
+    p.chunk_keys = plan.chunk_keys;
+    p.is_alibi = a->is_alibi ? 1 : 0;
+    const float scale = a->softmax_scale > 0.0f ? a->softmax_scale : (float)(1.0 / std::sqrt((double)a->dim));
+    p.scale_log2 = scale * kLog2e;
+    if (plan.num_splits > 1) {
+        p.part_o = scratch;
+        p.part_lse = scratch + (size_t)a->batch * a->head_q * plan.num_splits * a->dim_v;
+    }
+    if ((int64_t)p.head_k * p.head_chunks > 65535) {
+        return fail(DA_ERR_INVALID_ARG, "head_k * head chunks exceeds the grid limit");
+    }
+
+    const bool bf16 = a->is_bf16 != 0;
+    cudaError_t e;
+    switch (plan.shape) {
+        case Shape::kD64: e = launch_split_d64(bf16, plan.heads, p, stream); break;
+        case Shape::kD96: e = launch_split_d96(bf16, plan.heads, p, stream); break;
+        case Shape::kD128: e = launch_split_d128(bf16, plan.heads, p, stream); break;
+        case Shape::kD256: e = launch_split_d256(bf16, plan.heads, p, stream); break;
+        case Shape::kMla: e = launch_split_mla_simt(bf16, plan.heads, p, stream); break;
+        default: e = cudaErrorInvalidValue; break;
+    }
+    if (e != cudaSuccess) return fail(DA_ERR_CUDA, "split kernel launch: %s", cudaGetErrorString(e));
+    count_launch();
+
+    if (plan.num_splits > 1) {
+        MergeParams m;
+        memset(&m, 0, sizeof(m));
+        m.part_o = p.part_o;
+        m.part_lse = p.part_lse;
+        m.o = a->o;
+        m.o_f32 = a->o_f32;
+        m.lse = a->lse;
+        m.cu_seq_k = a->cu_seq_k;
+        m.part_stride_o = a->dim_v;
+        m.row_stride_o = (long long)plan.num_splits * a->dim_v;
+        m.part_stride_lse = 1;
+        m.row_stride_lse = plan.num_splits;
+        m.o_row_stride = p.o_row_stride;
+        m.rows = a->batch * a->head_q;
+        m.num_parts = plan.num_splits;
+        m.dim_v = (int)a->dim_v;
+        m.head_q = (int)a->head_q;
+        m.chunk_keys = plan.chunk_keys;
+        m.is_bf16 = bf16;
+        e = launch_merge(m, stream);
+        if (e != cudaSuccess) return fail(DA_ERR_CUDA, "merge kernel launch: %s", cudaGetErrorString(e));
+    }
+    return DA_OK;
+}
+
+int da_decode_fwd_host(const da_decode_args_t *h) {
+    int rc = check_args(h);
+    if (rc != DA_OK) return rc;
+    if (!h->o) return fail(DA_ERR_INVALID_ARG, "o must be given");
+    if (h->o_f32 || h->kv_pos_offset || h->kv_total_len || h->workspace) {
+        return fail(DA_ERR_INVALID_ARG, "o_f32, kv_pos_offset, kv_total_len and workspace are device-only fields");
+    }
+    if (h->q_row_stride || h->k_row_stride || h->v_row_stride || h->o_row_stride) {
+        return fail(DA_ERR_INVALID_ARG, "host tensors must be packed (row strides 0)");
+    }
+    DeviceState *st = nullptr;
+    rc = device_state(&st);
+    if (rc != DA_OK) return rc;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(h->stream);
+    const int64_t total_k = h->cu_seq_k[h->batch];
+    if (total_k < 0) return fail(DA_ERR_INVALID_ARG, "cu_seq_k must not decrease");
+    auto up = [](size_t x) { return (x + 255) / 256 * 256; };
+    const size_t q_b = up((size_t)h->batch * h->head_q * h->dim * 2);
+    const size_t k_b = up((size_t)total_k * h->head_k * h->dim * 2);
+    const size_t v_b = h->v ? up((size_t)total_k * h->head_k * h->dim_v * 2) : 0;
+    const size_t o_b = up((size_t)h->batch * h->head_q * h->dim_v * 2);
+    const size_t cu_b = up((size_t)(h->batch + 1) * 4);
+    const size_t lse_b = h->lse ? up((size_t)h->batch * h->head_q * 4) : 0;
+    const size_t need = q_b + k_b + v_b + o_b + cu_b + lse_b;
+    {
+        std::lock_guard<std::mutex> lock(st->mu);
+        if (st->staging_bytes < need) {
+            if (st->staging) {
+                cudaDeviceSynchronize();
+                cudaFree(st->staging);
+                st->staging = nullptr;
+                st->staging_bytes = 0;
+            }
+            cudaError_t e = cudaMalloc(&st->staging, need);
+            if (e != cudaSuccess) return fail(DA_ERR_WORKSPACE, "cudaMalloc(%zu) staging: %s", need, cudaGetErrorString(e));
+            st->staging_bytes = need;
+        }
+    }
+    char *base = static_cast<char *>(st->staging);
+    da_decode_args_t d = *h;
+    char *dq = base, *dk = dq + q_b, *dv = dk + k_b, *dout = dv + v_b, *dcu = dout + o_b, *dlse = dcu + cu_b;
+    d.q = dq;
+    d.k = dk;
+    d.v = h->v ? dv : nullptr;
+    d.o = dout;
+    d.cu_seq_k = reinterpret_cast<const int32_t *>(dcu);
+    d.lse = h->lse ? reinterpret_cast<float *>(dlse) : nullptr;
+    cudaError_t e = cudaMemcpyAsync(dcu, h->cu_seq_k, (size_t)(h->batch + 1) * 4, cudaMemcpyHostToDevice, stream);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(dq, h->q, (size_t)h->batch * h->head_q * h->dim * 2, cudaMemcpyHostToDevice, stream);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(dk, h->k, (size_t)total_k * h->head_k * h->dim * 2, cudaMemcpyHostToDevice, stream);
+    if (e == cudaSuccess && h->v)
+        e = cudaMemcpyAsync(dv, h->v, (size_t)total_k * h->head_k * h->dim_v * 2, cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return fail(DA_ERR_CUDA, "host-to-device copy: %s", cudaGetErrorString(e));
+    rc = da_decode_fwd(&d);
+    if (rc != DA_OK) return rc;
+    e = cudaMemcpyAsync(h->o, dout, (size_t)h->batch * h->head_q * h->dim_v * 2, cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess && h->lse)
+        e = cudaMemcpyAsync(h->lse, dlse, (size_t)h->batch * h->head_q * 4, cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return fail(DA_ERR_CUDA, "device-to-host copy: %s", cudaGetErrorString(e));
+    return DA_OK;
+}
+
+int da_merge_partials(const float *part_o, const float *part_lse, int32_t num_parts, int64_t rows, int32_t dim_v,
+                      int64_t part_stride_o, int64_t row_stride_o, int64_t part_stride_lse, int64_t row_stride_lse,
+                      void *o, float *o_f32, float *lse, int32_t is_bf16, void *stream) {
+    if (!part_o || !part_lse || (!o && !o_f32)) return fail(DA_ERR_INVALID_ARG, "NULL partials or no output");
+    if (num_parts <= 0 || rows < 0 || dim_v <= 0 || dim_v % 4 != 0 || dim_v > 512) {
+        return fail(DA_ERR_INVALID_ARG, "num_parts > 0, rows >= 0, dim_v in (0, 512] and a multiple of 4 required");
+    }
+    if (((uintptr_t)part_o | (uintptr_t)o | (uintptr_t)o_f32) & 15u || part_stride_o % 4 || row_stride_o % 4) {
+        return fail(DA_ERR_INVALID_ARG, "part_o, o, o_f32 must be 16-byte aligned, strides multiples of 4 floats");
+    }
+    MergeParams m;
+    memset(&m, 0, sizeof(m));
+    m.part_o = part_o;
+    m.part_lse = part_lse;
+    m.o = o;
+    m.o_f32 = o_f32;
+    m.lse = lse;
+    m.part_stride_o = part_stride_o;
+    m.row_stride_o = row_stride_o;
+    m.part_stride_lse = part_stride_lse;
+    m.row_stride_lse = row_stride_lse;
+    m.rows = rows;
+    m.num_parts = num_parts;
+    m.dim_v = dim_v;
+    m.head_q = 1;  // rows are addressed flat: o row i at o + i * dim_v
+    m.o_row_stride = dim_v;
+    m.is_bf16 = is_bf16;
+    cudaError_t e = launch_merge(m, reinterpret_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(DA_ERR_CUDA, "merge kernel launch: %s", cudaGetErrorString(e));
+    return DA_OK;
+}
+
+int da_device_status(void) {
+    DeviceState *st = nullptr;
+    int rc = device_state(&st);
+    if (rc != DA_OK) return rc;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return fail(DA_ERR_CUDA, "cudaDeviceSynchronize: %s", cudaGetErrorString(e));
+    int word = 0;
+    e = cudaMemcpy(&word, st->status_ptr, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fail(DA_ERR_CUDA, "cudaMemcpy(status): %s", cudaGetErrorString(e));
+    if (word != kStatusOk) {
+        int zero = 0;
+        cudaMemcpy(st->status_ptr, &zero, sizeof(int), cudaMemcpyHostToDevice);
+        return fail(DA_ERR_TIMEOUT, "a kernel gave up a bounded wait (status word %d)", word);
+    }
+    return DA_OK;
+}
+
+const char *da_status_string(int status) {
+    switch (status) {
+        case DA_OK: return "ok";
+        case DA_ERR_INVALID_ARG: return "invalid argument";
+        case DA_ERR_UNSUPPORTED: return "unsupported shape";
+        case DA_ERR_WORKSPACE: return "workspace too small or not allocatable";
+        case DA_ERR_CUDA: return "CUDA runtime error";
+        case DA_ERR_TIMEOUT: return "device wait timed out";
+        default: return "unknown status";
+    }
+}
+
+const char *da_last_error(void) { return g_err; }
+
+uint64_t da_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+}  // extern "C"

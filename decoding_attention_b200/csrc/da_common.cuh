@@ -1,0 +1,148 @@
+// Shared device-side building blocks of the sm_100a decode-attention kernels: the kernel parameter
+// block, mbarrier / bulk-copy (TMA) PTX wrappers with bounded waits, and 16-bit -> fp32 unpacking.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace da {
+
+// Device status word values (written by a kernel whose bounded wait ran out; read by the host with
+// da_device_status()).  0 means no kernel reported a problem.
+enum : int { kStatusOk = 0, kStatusWaitTimeout = 1 };
+
+// Arguments of the split-KV kernels.  It plays the role of the reference's DecodingParams
+// (csrc/kernel/decoding_attn/decoding.h:11-51) with the split-KV, LSE and ALiBi-shard extensions.
+struct SplitParams {
+    const void *q;   // [batch, head_q, dim]
+    const void *k;   // [total_k, head_k, dim]
+    const void *v;   // [total_k, head_k, dim_v]; equals k for the latent-KV (MLA) shape
+    void *o;         // [batch, head_q, dim_v] in the input type, or nullptr
+    float *o_f32;    // optional fp32 copy of the result
+    float *lse;      // optional natural-log LSE [batch, head_q]
+    float *part_o;   // split partials [batch, head_q, num_splits, dim_v] (normalised), num_splits > 1
+    float *part_lse; // split partials [batch, head_q, num_splits]
+    const int *cu_seq_k;       // [batch + 1]
+    const int *kv_pos_offset;  // optional [batch]: position of key 0 inside a longer sequence (ALiBi)
+    const int *kv_total_len;   // optional [batch]: length of that longer sequence (ALiBi)
+    int *status;               // device status word
+    long long q_row_stride, k_row_stride, v_row_stride, o_row_stride;  // in elements
+    int head_q, head_k;
+    int group;         // query heads per KV head
+    int head_chunks;   // CTAs that share one KV head (group / heads-per-CTA)
+    int batch;
+    int num_splits;
+    int chunk_keys;    // keys per split (multiple of the tile)
+    int is_alibi;
+    float scale_log2;  // softmax scale * log2(e)
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait.  Every try_wait itself blocks for a hardware-defined slice of time, so the cap
+// below is seconds of wall time, far beyond any legitimate wait; when it runs out (or another
+// thread of the CTA has already given up) the caller records kStatusWaitTimeout and leaves.
+constexpr uint32_t kMaxWaitSpins = 1u << 24;
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+    for (uint32_t spin = 0; spin < kMaxWaitSpins; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+// One row of a K/V tile: global -> shared bulk copy (TMA engine, no tensor map), completion
+// signalled on an mbarrier as transferred bytes.  Addresses and size are multiples of 16 bytes.
+__device__ __forceinline__ void bulk_copy_g2s(void *dst_smem, const void *src_gmem, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst_smem)),
+                 "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_copy_g2s_hint(void *dst_smem, const void *src_gmem, uint32_t bytes,
+                                                   uint64_t *bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::
+            "r"(smem_u32(dst_smem)),
+        "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// Unpack eight 16-bit values (one 16-byte chunk) to fp32.
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4 &raw, float (&f)[8]);
+
+template <>
+__device__ __forceinline__ void unpack8<__half>(const uint4 &raw, float (&f)[8]) {
+    const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 t = __half22float2(h[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+template <>
+__device__ __forceinline__ void unpack8<__nv_bfloat16>(const uint4 &raw, float (&f)[8]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ T from_float(float x);
+template <>
+__device__ __forceinline__ __half from_float<__half>(float x) {
+    return __float2half_rn(x);
+}
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) {
+    return __float2bfloat16_rn(x);
+}
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+}  // namespace da

@@ -1,0 +1,50 @@
+// Host-side declarations shared by the translation units of libdecoding_attn_b200.so.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "da_common.cuh"
+
+namespace da {
+
+// Tiling of one kernel variant, reported to the dispatcher for the split heuristic.
+struct SplitVariantInfo {
+    int tile_keys;    // keys per pipeline stage
+    int heads;        // query heads per CTA (G)
+    int ctas_per_sm;  // resident CTAs per SM the variant is tuned for
+};
+
+// Per-shape launchers (da_split_d*.cu).  `heads` must be one of the values the shape instantiates;
+// returns cudaErrorInvalidValue otherwise.
+cudaError_t launch_split_d64(bool bf16, int heads, const SplitParams &p, cudaStream_t s);
+cudaError_t launch_split_d96(bool bf16, int heads, const SplitParams &p, cudaStream_t s);
+cudaError_t launch_split_d128(bool bf16, int heads, const SplitParams &p, cudaStream_t s);
+cudaError_t launch_split_d256(bool bf16, int heads, const SplitParams &p, cudaStream_t s);
+cudaError_t launch_split_mla_simt(bool bf16, int heads, const SplitParams &p, cudaStream_t s);
+SplitVariantInfo split_info_d64(int heads);
+SplitVariantInfo split_info_d96(int heads);
+SplitVariantInfo split_info_d128(int heads);
+SplitVariantInfo split_info_d256(int heads);
+SplitVariantInfo split_info_mla_simt(int heads);
+
+// Merge of split / shard partials (da_merge.cu).  cu_seq_k and chunk_keys (both optional) limit a
+// row to the splits that cover keys; without them every part is read.
+struct MergeParams {
+    const float *part_o;
+    const float *part_lse;
+    void *o;
+    float *o_f32;
+    float *lse;
+    const int *cu_seq_k;
+    long long part_stride_o, row_stride_o, part_stride_lse, row_stride_lse;
+    long long o_row_stride;  // elements between sequences in o
+    long long rows;
+    int num_parts, dim_v, head_q, chunk_keys, is_bf16;
+};
+cudaError_t launch_merge(const MergeParams &p, cudaStream_t s);
+
+void count_launch(int n = 1);
+
+}  // namespace da

@@ -1,0 +1,35 @@
+// Instantiations of the CUDA-core split-KV kernel for head dims (64, 64).  These replace the
+// reference's per-shape tiling choices (csrc/kernel/decoding_attn/decoding_fwd_hd*.cu).
+#include "da_internal.h"
+#include "da_split_kernel.cuh"
+
+namespace da {
+namespace {
+// lanes per key row, keys per lane-group and tile, consumer warps, pipeline stages
+template <typename T, int G, int KPT>
+using Cfg = SplitCfg<T, 64, 64, 8, G, KPT, 4, 4, false>;
+
+template <typename T>
+cudaError_t launch_t(int heads, const SplitParams &p, cudaStream_t s) {
+    switch (heads) {
+        case 1: return launch_split<Cfg<T, 1, 4>>(p, s);
+        case 2: return launch_split<Cfg<T, 2, 4>>(p, s);
+        case 4: return launch_split<Cfg<T, 4, 4>>(p, s);
+        default: return cudaErrorInvalidValue;
+    }
+}
+}  // namespace
+
+cudaError_t launch_split_d64(bool bf16, int heads, const SplitParams &p, cudaStream_t s) {
+    return bf16 ? launch_t<__nv_bfloat16>(heads, p, s) : launch_t<__half>(heads, p, s);
+}
+
+SplitVariantInfo split_info_d64(int heads) {
+    switch (heads) {
+        case 1: return {Cfg<__half, 1, 4>::TILE, 1, (227 * 1024) / (Cfg<__half, 1, 4>::SMEM_BYTES + 1024)};
+        case 2: return {Cfg<__half, 2, 4>::TILE, 2, (227 * 1024) / (Cfg<__half, 2, 4>::SMEM_BYTES + 1024)};
+        case 4: return {Cfg<__half, 4, 4>::TILE, 4, (227 * 1024) / (Cfg<__half, 4, 4>::SMEM_BYTES + 1024)};
+        default: return {0, 0, 0};
+    }
+}
+}  // namespace da

@@ -1,0 +1,435 @@
+// CUDA-core split-KV decode attention for MHA / GQA / MQA (and a slow all-shapes path for the
+// latent-KV shape), sm_100a.
+//
+// It replaces the reference's single kernel dmha_fwd_kernel
+// (csrc/kernel/decoding_attn/decoding_fwd_kernel.h:13-236), which runs one CTA per (batch, query
+// head), materialises the whole score row in shared memory and re-reads K/V once per query head.
+// Here one CTA owns (sequence, KV head, head chunk, key range):
+//   * a producer warp streams K and V tiles of that key range into a ring of shared-memory stages
+//     with per-row cp.async.bulk copies (TMA engine) that complete on mbarriers;
+//   * NWARPS consumer warps are cut into groups of LANES lanes.  A group owns every NG-th key of a
+//     tile; each lane owns NCH 16-byte chunks of the head dimension for all G query heads of the
+//     CTA, so a K/V element is unpacked to fp32 once and used G times;
+//   * per-lane partial dot products are reduce-scattered inside the group with xor shuffles, the
+//     softmax is kept online per group in fp32 (no CTA-wide synchronisation per tile), and the
+//     groups are merged once at the end;
+//   * the CTA writes either the final row (one split) or a normalised fp32 partial plus its LSE
+//     for the merge kernel (da_merge.cu).
+// Everything that waits does so with a bound (mbar_wait) and reports through the status word.
+#pragma once
+
+#include "da_common.cuh"
+
+namespace da {
+
+template <typename T_, int D_, int DV_, int LANES_, int G_, int KPT_, int NWARPS_, int STAGES_, bool MLA_>
+struct SplitCfg {
+    using T = T_;
+    static constexpr int D = D_, DV = DV_, LANES = LANES_, G = G_, KPT = KPT_, NWARPS = NWARPS_, STAGES = STAGES_;
+    static constexpr bool MLA = MLA_;              // V is the first DV elements of each K row
+    static constexpr int NCH = D / (8 * LANES);    // 16-byte chunks of a K row per lane
+    static constexpr int NCHV = DV / (8 * LANES);  // 16-byte chunks of a V row per lane
+    static constexpr int GPW = 32 / LANES;         // groups per warp
+    static constexpr int NG = NWARPS * GPW;        // groups per CTA
+    static constexpr int TILE = NG * KPT;          // keys per pipeline stage
+    static constexpr int NV = KPT * G;             // scores per group per tile
+    static constexpr int RV = NV >= LANES ? NV / LANES : 1;   // scores a lane holds after the reduce-scatter
+    static constexpr int REP = NV >= LANES ? 1 : LANES / NV;  // lanes holding the same score
+    static constexpr int K_ROW_BYTES = D * 2, V_ROW_BYTES = DV * 2;
+    static constexpr int K_TILE_BYTES = TILE * K_ROW_BYTES;
+    static constexpr int V_TILE_BYTES = MLA ? 0 : TILE * V_ROW_BYTES;
+    static constexpr int THREADS = (NWARPS + 1) * 32;
+    static constexpr int CONSUMERS = NWARPS * 32;
+    // shared memory map
+    static constexpr int OFF_K = 0;
+    static constexpr int OFF_V = OFF_K + STAGES * K_TILE_BYTES;
+    static constexpr int PIPE_BYTES = OFF_V + STAGES * V_TILE_BYTES;
+    static constexpr int MERGE_BYTES = NG * G * (DV + 2) * 4;  // end-of-CTA merge reuses the stage buffers
+    static constexpr int OFF_P = (PIPE_BYTES > MERGE_BYTES ? PIPE_BYTES : MERGE_BYTES);
+    static constexpr int P_BYTES = NG * NV * 4;
+    static constexpr int OFF_BAR = (OFF_P + P_BYTES + 15) / 16 * 16;
+    static constexpr int SMEM_BYTES = OFF_BAR + 4 * STAGES * 8 + 16;
+    static_assert(D % (8 * LANES) == 0 && DV % (8 * LANES) == 0, "head dims must split into 16-byte chunks per lane");
+    static_assert((LANES & (LANES - 1)) == 0 && LANES <= 32, "LANES must be a power of two");
+    static_assert((NV & (NV - 1)) == 0, "KPT*G must be a power of two");
+    static_assert(!MLA || DV <= D, "latent-KV: V is a prefix of the K row");
+};
+
+// Sum v[] over the LANES lanes of a group.  While more than one value is left each step also
+// halves the number of values a lane keeps (reduce-scatter), so NV values cost about NV shuffles
+// instead of NV*log2(LANES).  Afterwards lane c holds the totals of indices (c/REP)*RV .. +RV-1.
+template <int NV, int LANES>
+__device__ __forceinline__ void group_reduce_scatter(float (&v)[NV], int lane_in_group) {
+    int cnt = NV;
+#pragma unroll
+    for (int off = LANES / 2; off >= 1; off >>= 1) {
+        if (cnt > 1) {
+            const int half = cnt / 2;
+            const bool upper = (lane_in_group & off) != 0;
+#pragma unroll
+            for (int j = 0; j < NV / 2; ++j) {
+                if (j < half) {
+                    const float send = upper ? v[j] : v[j + half];
+                    const float keep = upper ? v[j + half] : v[j];
+                    v[j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                }
+            }
+            cnt = half;
+        } else {
+            v[0] += __shfl_xor_sync(0xffffffffu, v[0], off);
+        }
+    }
+}
+
+// arr[idx] for a run-time idx without sending the array to local memory.
+template <int N>
+__device__ __forceinline__ float pick(const float (&arr)[N], int idx) {
+    float x = arr[0];
+#pragma unroll
+    for (int i = 1; i < N; ++i) x = (idx == i) ? arr[i] : x;
+    return x;
+}
+
+template <class C>
+__global__ void __launch_bounds__(C::THREADS) da_split_kernel(const SplitParams p) {
+    using T = typename C::T;
+    constexpr int D = C::D, DV = C::DV, LANES = C::LANES, G = C::G, KPT = C::KPT, NG = C::NG, TILE = C::TILE;
+    constexpr int NCH = C::NCH, NCHV = C::NCHV, NV = C::NV, RV = C::RV, REP = C::REP, STAGES = C::STAGES;
+    extern __shared__ __align__(128) uint8_t smem[];
+
+    const int split = blockIdx.x;
+    const int hk = blockIdx.y / p.head_chunks;
+    const int hc = blockIdx.y % p.head_chunks;
+    const int b = blockIdx.z;
+    const int h0 = hk * p.group + hc * G;  // first query head of this CTA
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31;
+
+    const int seq_begin = p.cu_seq_k[b];
+    const int len = p.cu_seq_k[b + 1] - seq_begin;
+    const int k_begin = split * p.chunk_keys;
+    const int k_end = min(len, k_begin + p.chunk_keys);
+    const float neg_inf = -INFINITY;
+
+    if (k_begin >= k_end) {
+        // Nothing to read.  With several splits the merge kernel skips this one; with a single split
+        // the sequence is empty: the row is defined as zeros with LSE = -inf.
+        if (p.num_splits == 1) {
+            for (int idx = tid; idx < G * DV; idx += C::THREADS) {
+                const int g = idx / DV, d = idx % DV;
+                const size_t off = (size_t)b * p.o_row_stride + (size_t)(h0 + g) * DV + d;
+                if (p.o) reinterpret_cast<T *>(p.o)[off] = from_float<T>(0.0f);
+                if (p.o_f32) p.o_f32[((size_t)b * p.head_q + h0 + g) * DV + d] = 0.0f;
+            }
+            if (p.lse && tid < G) p.lse[(size_t)b * p.head_q + h0 + tid] = neg_inf;
+        }
+        return;
+    }
+
+    uint8_t *ks = smem + C::OFF_K;
+    uint8_t *vs = C::MLA ? ks : smem + C::OFF_V;
+    float *p_s = reinterpret_cast<float *>(smem + C::OFF_P);
+    uint64_t *full_k = reinterpret_cast<uint64_t *>(smem + C::OFF_BAR);
+    uint64_t *empty_k = full_k + STAGES;
+    uint64_t *full_v = empty_k + STAGES;
+    uint64_t *empty_v = full_v + STAGES;
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(empty_v + STAGES);
+
+    if (tid == 0) {
+#pragma unroll
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_k[s], 1);
+            mbar_init(&empty_k[s], C::NWARPS);
+            mbar_init(&full_v[s], 1);
+            mbar_init(&empty_v[s], C::NWARPS);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    const int n_tiles = (k_end - k_begin + TILE - 1) / TILE;
+
+    if (warp == C::NWARPS) {
+        // ---------------- producer warp ----------------
+        const T *kg = reinterpret_cast<const T *>(p.k) + (size_t)hk * D;
+        const T *vg = reinterpret_cast<const T *>(p.v) + (size_t)hk * (C::MLA ? D : DV);
+        bool ok = true;
+        int armed_k = 0, armed_v = 0;  // tiles whose full barrier has been armed
+        for (int t = 0; t < n_tiles; ++t) {
+            const int st = t % STAGES;
+            const uint32_t ph = (uint32_t)(t / STAGES) & 1u;
+            const int key0 = k_begin + t * TILE;
+            const int rows = min(TILE, k_end - key0);
+            const size_t tok0 = (size_t)seq_begin + key0;
+            if (t >= STAGES) ok = mbar_wait(&empty_k[st], ph ^ 1u, abort_flag);
+            if (!ok) break;
+            if (lane == 0) mbar_arrive_expect_tx(&full_k[st], (uint32_t)rows * C::K_ROW_BYTES);
+            __syncwarp();
+            armed_k = t + 1;
+            for (int r = lane; r < rows; r += 32) {
+                bulk_copy_g2s(ks + st * C::K_TILE_BYTES + r * C::K_ROW_BYTES, kg + (tok0 + r) * p.k_row_stride,
+                              C::K_ROW_BYTES, &full_k[st]);
+            }
+            if (!C::MLA) {
+                if (t >= STAGES) ok = mbar_wait(&empty_v[st], ph ^ 1u, abort_flag);
+                if (!ok) break;
+                if (lane == 0) mbar_arrive_expect_tx(&full_v[st], (uint32_t)rows * C::V_ROW_BYTES);
+                __syncwarp();
+                armed_v = t + 1;
+                for (int r = lane; r < rows; r += 32) {
+                    bulk_copy_g2s(vs + st * C::V_TILE_BYTES + r * C::V_ROW_BYTES, vg + (tok0 + r) * p.v_row_stride,
+                                  C::V_ROW_BYTES, &full_v[st]);
+                }
+            }
+        }
+        if (!ok) {
+            // A wait ran out.  Report it, then give the copies that are still in flight a bounded time
+            // to land before this warp (the last user of the stage buffers) retires.
+            if (lane == 0) atomicExch(p.status, kStatusWaitTimeout);
+            for (int back = 1; back <= STAGES; ++back) {
+                const int tk = armed_k - back, tv = armed_v - back;
+                for (uint32_t spin = 0; tk >= 0 && spin < (1u << 20); ++spin)
+                    if (mbar_try_wait(&full_k[tk % STAGES], (uint32_t)(tk / STAGES) & 1u)) break;
+                for (uint32_t spin = 0; tv >= 0 && spin < (1u << 20); ++spin)
+                    if (mbar_try_wait(&full_v[tv % STAGES], (uint32_t)(tv / STAGES) & 1u)) break;
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumer warps ----------------
+    const int c = lane % LANES;                     // lane in group = chunk index
+    const int gi = warp * C::GPW + lane / LANES;    // group in CTA
+    float *p_grp = p_s + gi * NV;
+
+    // Q slice of this lane for the G heads, fp32.
+    float qf[G][NCH][8];
+    {
+        const T *qg = reinterpret_cast<const T *>(p.q) + (size_t)b * p.q_row_stride + (size_t)h0 * D;
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+#pragma unroll
+            for (int n = 0; n < NCH; ++n) {
+                const uint4 raw = *reinterpret_cast<const uint4 *>(qg + g * D + (c + n * LANES) * 8);
+                unpack8<T>(raw, qf[g][n]);
+            }
+        }
+    }
+
+    // Which (key slot, head) pairs this lane owns after the reduce-scatter, and their ALiBi slopes.
+    const int j0 = (c / REP) * RV;
+    float slope2[RV];  // slope * log2(e)
+#pragma unroll
+    for (int r = 0; r < RV; ++r) {
+        const int g = (j0 + r) % G;
+        slope2[r] = p.is_alibi ? exp2f(-8.0f * (float)(h0 + g + 1) / (float)p.head_q) * kLog2e : 0.0f;
+    }
+    const int pos_shift = (p.kv_pos_offset ? p.kv_pos_offset[b] : 0) - ((p.kv_total_len ? p.kv_total_len[b] : len) - 1);
+
+    float m_run[G];      // running max per head (log2 domain), identical in every lane of the group
+    float l_lane[RV];    // running sum of this lane's own probabilities
+    float oacc[G][NCHV][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        m_run[g] = neg_inf;
+#pragma unroll
+        for (int n = 0; n < NCHV; ++n)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) oacc[g][n][e] = 0.0f;
+    }
+#pragma unroll
+    for (int r = 0; r < RV; ++r) l_lane[r] = 0.0f;
+
+    bool ok = true;
+    for (int t = 0; t < n_tiles; ++t) {
+        const int st = t % STAGES;
+        const uint32_t ph = (uint32_t)(t / STAGES) & 1u;
+        const int key0 = k_begin + t * TILE;
+        const int rows = min(TILE, k_end - key0);
+
+        // ---- S = Q K^T for this group's keys ----
+        ok = mbar_wait(&full_k[st], ph, abort_flag);
+        if (!ok) break;
+        float sacc[NV];
+#pragma unroll
+        for (int j = 0; j < NV; ++j) sacc[j] = 0.0f;
+        const uint8_t *kt = ks + st * C::K_TILE_BYTES;
+#pragma unroll
+        for (int i = 0; i < KPT; ++i) {
+            const int kl = i * NG + gi;  // key slot in the tile
+#pragma unroll
+            for (int n = 0; n < NCH; ++n) {
+                const uint4 raw = *reinterpret_cast<const uint4 *>(kt + kl * C::K_ROW_BYTES + (c + n * LANES) * 16);
+                float kf[8];
+                unpack8<T>(raw, kf);
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) sacc[i * G + g] = fmaf(qf[g][n][e], kf[e], sacc[i * G + g]);
+                }
+            }
+        }
+        if (!C::MLA) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_k[st]);
+        }
+        group_reduce_scatter<NV, LANES>(sacc, c);
+
+        // ---- scale, bias, mask; publish the scores of the group ----
+#pragma unroll
+        for (int r = 0; r < RV; ++r) {
+            const int j = j0 + r;
+            const int kl = (j / G) * NG + gi;
+            const int pos = key0 + kl;
+            float s = sacc[r] * p.scale_log2 + slope2[r] * (float)(pos + pos_shift);
+            sacc[r] = (kl < rows) ? s : neg_inf;
+        }
+        __syncwarp();  // the previous tile's readers of p_grp are done
+#pragma unroll
+        for (int r = 0; r < RV; ++r) p_grp[j0 + r] = sacc[r];
+        __syncwarp();
+
+        // ---- online softmax: new running max per head, rescale factors ----
+        float m_new[G], alpha[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) m_new[g] = m_run[g];
+#pragma unroll
+        for (int i = 0; i < KPT; ++i) {
+#pragma unroll
+            for (int g = 0; g < G; ++g) m_new[g] = fmaxf(m_new[g], p_grp[i * G + g]);
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const float m_use = (m_new[g] == neg_inf) ? 0.0f : m_new[g];
+            alpha[g] = exp2f(m_run[g] - m_use);
+            m_run[g] = m_new[g];
+        }
+        __syncwarp();  // everybody has read the raw scores
+#pragma unroll
+        for (int r = 0; r < RV; ++r) {
+            const int g = (j0 + r) % G;
+            const float m_g = pick<G>(m_new, g);
+            const float m_use = (m_g == neg_inf) ? 0.0f : m_g;
+            const float pr = exp2f(sacc[r] - m_use);
+            l_lane[r] = l_lane[r] * pick<G>(alpha, g) + pr;
+            p_grp[j0 + r] = pr;
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+#pragma unroll
+            for (int n = 0; n < NCHV; ++n)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) oacc[g][n][e] *= alpha[g];
+        }
+        __syncwarp();
+
+        // ---- O += P V ----
+        if (!C::MLA) {
+            ok = mbar_wait(&full_v[st], ph, abort_flag);
+            if (!ok) break;
+        }
+        const uint8_t *vt = C::MLA ? kt : vs + st * C::V_TILE_BYTES;
+        constexpr int VROW = C::MLA ? C::K_ROW_BYTES : C::V_ROW_BYTES;
+#pragma unroll
+        for (int i = 0; i < KPT; ++i) {
+            const int kl = i * NG + gi;
+            if (kl < rows) {
+                float pg[G];
+#pragma unroll
+                for (int g = 0; g < G; ++g) pg[g] = p_grp[i * G + g];
+#pragma unroll
+                for (int n = 0; n < NCHV; ++n) {
+                    const uint4 raw = *reinterpret_cast<const uint4 *>(vt + kl * VROW + (c + n * LANES) * 16);
+                    float vf[8];
+                    unpack8<T>(raw, vf);
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) oacc[g][n][e] = fmaf(pg[g], vf[e], oacc[g][n][e]);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(C::MLA ? &empty_k[st] : &empty_v[st]);
+    }
+    if (!ok && lane == 0) atomicExch(p.status, kStatusWaitTimeout);
+
+    // ---------------- merge the groups of the CTA ----------------
+    // Every consumer has passed its last full-barrier wait, so every copy has landed and the stage
+    // buffers can be reused once all consumers are done reading them.
+    named_bar_sync(1, C::CONSUMERS);
+    float *red_m = reinterpret_cast<float *>(smem);  // [NG][G]
+    float *red_l = red_m + NG * G;                    // [NG][G]
+    float *red_o = red_l + NG * G;                    // [NG][G][DV]
+    __syncwarp();
+#pragma unroll
+    for (int r = 0; r < RV; ++r) p_grp[j0 + r] = l_lane[r];
+    __syncwarp();
+    if (c == 0) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float l = 0.0f;
+#pragma unroll
+            for (int i = 0; i < KPT; ++i) l += p_grp[i * G + g];
+            red_m[gi * G + g] = m_run[g];
+            red_l[gi * G + g] = l;
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+#pragma unroll
+        for (int n = 0; n < NCHV; ++n) {
+            float4 *dst = reinterpret_cast<float4 *>(red_o + (size_t)(gi * G + g) * DV + (c + n * LANES) * 8);
+            dst[0] = make_float4(oacc[g][n][0], oacc[g][n][1], oacc[g][n][2], oacc[g][n][3]);
+            dst[1] = make_float4(oacc[g][n][4], oacc[g][n][5], oacc[g][n][6], oacc[g][n][7]);
+        }
+    }
+    named_bar_sync(1, C::CONSUMERS);
+    if (*abort_flag) return;  // a wait ran out somewhere in the CTA: the status word says so
+
+    for (int idx = tid; idx < G * DV; idx += C::CONSUMERS) {
+        const int g = idx / DV, d = idx % DV;
+        float mx = neg_inf;
+#pragma unroll
+        for (int x = 0; x < NG; ++x) mx = fmaxf(mx, red_m[x * G + g]);
+        float l = 0.0f, o = 0.0f;
+#pragma unroll
+        for (int x = 0; x < NG; ++x) {
+            const float w = exp2f(red_m[x * G + g] - mx);  // mx is finite: the key range is not empty
+            l = fmaf(red_l[x * G + g], w, l);
+            o = fmaf(red_o[(size_t)(x * G + g) * DV + d], w, o);
+        }
+        const float out = o / l;
+        const int h = h0 + g;
+        const float lse = (mx + log2f(l)) * kLn2;
+        if (p.num_splits == 1) {
+            if (p.o) reinterpret_cast<T *>(p.o)[(size_t)b * p.o_row_stride + (size_t)h * DV + d] = from_float<T>(out);
+            if (p.o_f32) p.o_f32[((size_t)b * p.head_q + h) * DV + d] = out;
+            if (p.lse && d == 0) p.lse[(size_t)b * p.head_q + h] = lse;
+        } else {
+            const size_t row = ((size_t)b * p.head_q + h) * p.num_splits + split;
+            p.part_o[row * DV + d] = out;
+            if (d == 0) p.part_lse[row] = lse;
+        }
+    }
+}
+
+template <class C>
+cudaError_t launch_split(const SplitParams &p, cudaStream_t stream) {
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    if (dev < 64 && !attr_set[dev]) {
+        err = cudaFuncSetAttribute(da_split_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (err != cudaSuccess) return err;
+        attr_set[dev] = true;
+    }
+    dim3 grid(p.num_splits, p.head_k * p.head_chunks, p.batch);
+    da_split_kernel<C><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace da

@@ -1,0 +1,193 @@
+"""GPU parity tests: the CUDA path, called through the C ABI (ctypes), against the CPU oracle on
+identical seeded inputs.  Tolerance: |out - oracle| <= 2e-3 + 1e-2 |oracle| element-wise (fp32
+accumulation, fp16/bf16 outputs) and the reference suite's mean |diff| <= 5e-3."""
+import pytest
+import torch
+
+from decoding_attention_b200 import synth
+from helpers import assert_close, merge_reference
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def run_cabi(cabi, w, q, k, v, cu, num_splits=0, want_lse=False, softmax_scale=None, pos_offset=None, total_len=None,
+             workspace=None):
+    o = torch.empty(q.shape[0], w.head_q, w.dim_v, dtype=w.dtype, device=q.device)
+    lse = torch.empty(q.shape[0], w.head_q, dtype=torch.float32, device=q.device) if want_lse else None
+    args = cabi.make_args(q, k, v, o, cu, max(w.max_seq_k, 1), w.dim_v, is_alibi=w.is_alibi, lse=lse,
+                          softmax_scale=softmax_scale, num_splits=num_splits, kv_pos_offset=pos_offset,
+                          kv_total_len=total_len, workspace=workspace,
+                          stream=torch.cuda.current_stream().cuda_stream)
+    cabi.decode_fwd(args)
+    torch.cuda.synchronize()
+    assert cabi.device_status() == cabi.DA_OK
+    return (o, lse) if want_lse else o
+
+
+def check(cabi, oracle, w, num_splits=0, **kw):
+    q, k, v, cu = w.make("cpu")
+    expect, lse_e = oracle.attn_cpu(q, k, v, cu, dim_v=w.dim_v, is_alibi=w.is_alibi, return_lse=True,
+                                    softmax_scale=kw.get("softmax_scale"))
+    dq, dk, dv, dcu = q.to(DEV), k.to(DEV), (v.to(DEV) if v is not None else None), cu.to(DEV)
+    before = cabi.launch_count()
+    o, lse = run_cabi(cabi, w, dq, dk, dv, dcu, num_splits=num_splits, want_lse=True, **kw)
+    assert cabi.launch_count() > before, "no kernel of this library was launched"
+    assert_close(o, expect, w.name)
+    fin = torch.isfinite(lse_e)
+    assert (lse.cpu()[fin] - lse_e[fin]).abs().max().item() <= 2e-3 if fin.any() else True
+    assert torch.equal(torch.isinf(lse.cpu()), ~fin)
+    return o
+
+
+# The reference suite's grid (tests/test_decoding_attn.py:61-66), thinned: every dim, both head
+# ratios, both dtypes, the three sequence lengths; batch 16 only for dim 128.
+REF_GRID = [(hq, hk, d, b, s, dt)
+            for d in (64, 96, 128, 256) for (hq, hk) in ((32, 8), (32, 32), (64, 8))
+            for (b, s) in ((1, 1), (2, 128), (2, 512)) for dt in (torch.float16, torch.bfloat16)
+            if not (hq == 64 and d in (96, 256))] + [(32, 8, 128, 16, 128, torch.float16),
+                                                      (64, 32, 128, 16, 512, torch.bfloat16)]
+
+
+@pytest.mark.parametrize("hq,hk,d,b,s,dt", REF_GRID)
+def test_reference_grid_mha_gqa(native_lib, oracle, hq, hk, d, b, s, dt):
+    w = synth.Workload(f"grid_{hq}_{hk}_{d}_{b}_{s}", dt, hq, hk, d, d, [s] * b, dist="normal", seed=11)
+    check(native_lib, oracle, w)
+
+
+@pytest.mark.parametrize("hq", [16, 32, 64, 128])
+@pytest.mark.parametrize("b,s", [(1, 1), (2, 128), (2, 512)])
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+def test_reference_grid_mla(native_lib, oracle, hq, b, s, dt):
+    # tests/test_decoding_attn.py:97-104
+    w = synth.Workload(f"mla_{hq}_{b}_{s}", dt, hq, 1, 576, 512, [s] * b, dist="normal", scale=0.5, mla=True, seed=12)
+    check(native_lib, oracle, w)
+
+
+@pytest.mark.parametrize("lens", [[1], [2], [7], [63], [64], [65], [127, 129], [0, 5], [5, 0, 0, 300], [1000, 3, 64]])
+@pytest.mark.parametrize("splits", [0, 1, 3])
+def test_edges_varlen_and_splits(native_lib, oracle, lens, splits):
+    w = synth.Workload(f"edge_{lens}_{splits}", torch.float16, 8, 2, 128, 128, lens, dist="normal", seed=13)
+    check(native_lib, oracle, w, num_splits=splits)
+
+
+@pytest.mark.parametrize("hq,hk,d", [(32, 32, 128), (32, 8, 128), (32, 1, 128), (16, 4, 64), (12, 4, 96), (8, 2, 256)])
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+def test_alibi(native_lib, oracle, hq, hk, d, dt):
+    w = synth.Workload(f"alibi_{hq}_{hk}_{d}", dt, hq, hk, d, d, [700, 33, 1], is_alibi=True, dist="uniform", seed=14)
+    check(native_lib, oracle, w)
+    check(native_lib, oracle, w, num_splits=4)
+
+
+@pytest.mark.parametrize("group", [1, 2, 3, 4, 6, 8, 16, 32])
+def test_head_ratios(native_lib, oracle, group):
+    w = synth.Workload(f"ratio_{group}", torch.bfloat16, 2 * group, 2, 128, 128, [200, 77], dist="normal", seed=15)
+    check(native_lib, oracle, w)
+
+
+def test_softmax_scale_argument(native_lib, oracle):
+    w = synth.Workload("scale", torch.float16, 8, 2, 128, 128, [150], dist="normal", seed=16)
+    check(native_lib, oracle, w, softmax_scale=0.2)
+
+
+def test_split_count_does_not_change_result_much_and_is_deterministic(native_lib, oracle):
+    w = synth.Workload("det", torch.bfloat16, 32, 8, 128, 128, [3000, 800], dist="normal", scale=0.5, seed=17)
+    q, k, v, cu = [t.to(DEV) for t in w.make("cpu")]
+    a = run_cabi(native_lib, w, q, k, v, cu, num_splits=5)
+    b = run_cabi(native_lib, w, q, k, v, cu, num_splits=5)
+    assert torch.equal(a, b), "same split count must be bit-reproducible"
+    c = run_cabi(native_lib, w, q, k, v, cu, num_splits=1)
+    assert_close(a, c, "splits 5 vs 1")
+
+
+def test_caller_workspace_with_canaries(native_lib, oracle):
+    w = synth.Workload("ws", torch.float16, 16, 4, 128, 128, [900, 100], dist="normal", seed=18)
+    q, k, v, cu = [t.to(DEV) for t in w.make("cpu")]
+    o = torch.empty(2, 16, 128, dtype=w.dtype, device=DEV)
+    args = native_lib.make_args(q, k, v, o, cu, w.max_seq_k, 128, num_splits=4)
+    need = native_lib.workspace_bytes(args)
+    assert need > 0
+    pad = 1024
+    buf = torch.full((need + 2 * pad,), 0x5A, dtype=torch.uint8, device=DEV)
+    ws = buf[pad:pad + need]
+    out = run_cabi(native_lib, w, q, k, v, cu, num_splits=4, workspace=ws)
+    assert (buf[:pad] == 0x5A).all() and (buf[pad + need:] == 0x5A).all(), "wrote outside the workspace"
+    expect = oracle.attn_cpu(*w.make("cpu"))
+    assert_close(out, expect, "workspace")
+    small = buf[pad:pad + need // 2]
+    with pytest.raises(native_lib.DecodingAttnError) as e:
+        run_cabi(native_lib, w, q, k, v, cu, num_splits=4, workspace=small)
+    assert e.value.status == native_lib.DA_ERR_WORKSPACE
+
+
+def test_padded_row_strides(native_lib, oracle):
+    w = synth.Workload("stride", torch.float16, 8, 2, 128, 128, [130, 40], dist="normal", seed=19)
+    q, k, v, cu = w.make("cpu")
+    expect = oracle.attn_cpu(q, k, v, cu)
+    kp = torch.zeros(k.shape[0], 3, 128, dtype=w.dtype, device=DEV)
+    vp = torch.zeros(v.shape[0], 4, 128, dtype=w.dtype, device=DEV)
+    kp[:, :2] = k.to(DEV)
+    vp[:, :2] = v.to(DEV)
+    out = run_cabi(native_lib, w, q.to(DEV), kp[:, :2], vp[:, :2], cu.to(DEV))
+    assert_close(out, expect, "strided rows")
+
+
+def test_key_range_shards_merge(native_lib, oracle):
+    """Key-range sharding as used across GPUs, emulated on one: per-shard (o fp32, lse) with the
+    ALiBi position offset, merged by da_merge_partials, equals the unsharded result."""
+    w = synth.Workload("shard", torch.bfloat16, 32, 32, 128, 128, [5000], is_alibi=True, dist="normal", scale=0.5,
+                       seed=20)
+    q, k, v, cu = w.make("cpu")
+    expect, lse_e = oracle.attn_cpu(q, k, v, cu, is_alibi=True, return_lse=True)
+    dq = q.to(DEV)
+    parts_o, parts_lse = [], []
+    bounds = [0, 1250, 2500, 3750, 5000]
+    for lo, hi in zip(bounds[:-1], bounds[1:]):
+        ks, vs = k[lo:hi].to(DEV), v[lo:hi].to(DEV)
+        cus = torch.tensor([0, hi - lo], dtype=torch.int32, device=DEV)
+        o32 = torch.empty(1, 32, 128, dtype=torch.float32, device=DEV)
+        lse = torch.empty(1, 32, dtype=torch.float32, device=DEV)
+        args = native_lib.make_args(dq, ks, vs, None, cus, hi - lo, 128, is_alibi=True, lse=lse, o_f32=o32,
+                                    kv_pos_offset=torch.tensor([lo], dtype=torch.int32, device=DEV),
+                                    kv_total_len=torch.tensor([5000], dtype=torch.int32, device=DEV))
+        native_lib.decode_fwd(args)
+        parts_o.append(o32.view(32, 128))
+        parts_lse.append(lse.view(32))
+    po, pl = torch.stack(parts_o).contiguous(), torch.stack(parts_lse).contiguous()
+    o = torch.empty(32, 128, dtype=w.dtype, device=DEV)
+    lse = torch.empty(32, dtype=torch.float32, device=DEV)
+    native_lib.check(native_lib.lib().da_merge_partials(po.data_ptr(), pl.data_ptr(), 4, 32, 128, 32 * 128, 128, 32, 1,
+                                                        o.data_ptr(), None, lse.data_ptr(), 1, None))
+    torch.cuda.synchronize()
+    assert_close(o.view(1, 32, 128), expect, "sharded + merged")
+    assert (lse.cpu() - lse_e.view(-1)).abs().max().item() < 2e-3
+    o_chk, _ = merge_reference(po.cpu(), pl.cpu())
+    assert (o.float().cpu() - o_chk.float()).abs().max().item() < 2e-2
+
+
+def test_host_buffer_entry_point(native_lib, oracle):
+    w = synth.Workload("host", torch.float16, 32, 8, 128, 128, [513, 100, 2000], dist="normal", seed=21)
+    q, k, v, cu = [t.pin_memory() for t in w.make("cpu")]
+    o = torch.empty(3, 32, 128, dtype=w.dtype).pin_memory()
+    args = native_lib.make_args(q, k, v, o, cu, w.max_seq_k, 128, packed=True)
+    native_lib.decode_fwd_host(args)
+    assert_close(o, oracle.attn_cpu(q, k, v, cu), "host entry point")
+
+
+def test_argument_errors(native_lib):
+    w = synth.Workload("err", torch.float16, 8, 2, 128, 128, [16], dist="normal", seed=22)
+    q, k, v, cu = [t.to(DEV) for t in w.make("cpu")]
+    o = torch.empty(1, 8, 128, dtype=w.dtype, device=DEV)
+    bad = native_lib.make_args(q, k, v, o, cu, 16, 64)  # (128, 64) is not a supported pair
+    with pytest.raises(native_lib.DecodingAttnError) as e:
+        native_lib.decode_fwd(bad)
+    assert e.value.status == native_lib.DA_ERR_UNSUPPORTED
+    bad = native_lib.make_args(q, k, v, o, cu, 16, 128)
+    bad.head_k = 3
+    with pytest.raises(native_lib.DecodingAttnError) as e:
+        native_lib.decode_fwd(bad)
+    assert e.value.status == native_lib.DA_ERR_INVALID_ARG
+    bad = native_lib.make_args(q, k, v, o, cu, 16, 128)
+    bad.q = None
+    with pytest.raises(native_lib.DecodingAttnError):
+        native_lib.decode_fwd(bad)
