@@ -98,12 +98,82 @@ SplitVariantInfo variant_info(Shape s, int heads) {
     }
 }
 
+// ---- tensor maps -----------------------------------------------------------------------------
+// cuTensorMapEncodeTiled is a driver-API function; it is looked up at run time so that the library
+// links against the CUDA runtime only.
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = []() -> EncodeTiledFn {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess) {
+            return nullptr;
+        }
+        return reinterpret_cast<EncodeTiledFn>(sym);
+    }();
+    return fn;
+}
+
+// Rank-3 map over a K or V tensor seen as [rows][head_k][dim] with box {dim, 1, tile_keys}.  The
+// row extent is not known to the library (only cu_seq_k on the device is), so it is set to the
+// largest value a coordinate can take; the kernels use the map only for tiles that lie wholly
+// inside a sequence and fetch ragged tails row by row.
+constexpr uint64_t kMapRows = 1ull << 31;
+struct MapKey {
+    const void *base;
+    long long row_stride;
+    int head_k, dim, tile, bf16;
+    bool operator==(const MapKey &o) const {
+        return base == o.base && row_stride == o.row_stride && head_k == o.head_k && dim == o.dim && tile == o.tile &&
+               bf16 == o.bf16;
+    }
+};
+struct MapCacheEntry {
+    MapKey key;
+    CUtensorMap map;
+    bool valid = false;
+};
+thread_local MapCacheEntry g_map_cache[8];
+thread_local int g_map_next = 0;
+
+int make_kv_tensor_map(const void *base, long long row_stride, int head_k, int dim, int tile, bool bf16,
+                       CUtensorMap *out) {
+    const MapKey key{base, row_stride, head_k, dim, tile, bf16 ? 1 : 0};
+    for (auto &e : g_map_cache) {
+        if (e.valid && e.key == key) {
+            *out = e.map;
+            return DA_OK;
+        }
+    }
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return fail(DA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    const cuuint64_t dims[3] = {(cuuint64_t)dim, (cuuint64_t)head_k, kMapRows};
+    const cuuint64_t strides[2] = {(cuuint64_t)dim * 2, (cuuint64_t)row_stride * 2};
+    const cuuint32_t box[3] = {(cuuint32_t)dim, 1, (cuuint32_t)tile};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(out, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                    const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(DA_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    MapCacheEntry &slot = g_map_cache[g_map_next];
+    g_map_next = (g_map_next + 1) % 8;
+    slot.key = key;
+    slot.map = *out;
+    slot.valid = true;
+    return DA_OK;
+}
+
 struct Plan {
     Shape shape;
     int heads;       // query heads per CTA
     int head_chunks; // CTAs per KV head
     int num_splits;
     int chunk_keys;
+    int tile_keys;
     size_t scratch_bytes;
 };
 
@@ -154,6 +224,7 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
     plan->head_chunks = group / heads;
     plan->num_splits = (int)splits;
     plan->chunk_keys = (int)(chunk_tiles * tile);
+    plan->tile_keys = tile;
     plan->scratch_bytes =
         splits > 1 ? (size_t)a.batch * a.head_q * splits * ((size_t)a.dim_v + 1) * sizeof(float) : 0;
     return DA_OK;
@@ -298,13 +369,24 @@ int da_decode_fwd(const da_decode_args_t *a) {
     }
 
     const bool bf16 = a->is_bf16 != 0;
+    KvMaps maps;
+    memset(&maps, 0, sizeof(maps));
+    // Tiled TMA needs a global stride that is a multiple of 16 bytes (checked above: 8 elements) and
+    // a box of at most 256 elements per dimension; the latent-KV rows (576) keep the row-wise path.
+    p.use_tmap = (plan.shape != Shape::kMla) && !getenv("DA_NO_TMAP");
+    if (p.use_tmap) {
+        rc = make_kv_tensor_map(p.k, p.k_row_stride, p.head_k, (int)a->dim, plan.tile_keys, bf16, &maps.k);
+        if (rc != DA_OK) return rc;
+        rc = make_kv_tensor_map(p.v, p.v_row_stride, p.head_k, (int)a->dim_v, plan.tile_keys, bf16, &maps.v);
+        if (rc != DA_OK) return rc;
+    }
     cudaError_t e;
     switch (plan.shape) {
-        case Shape::kD64: e = launch_split_d64(bf16, plan.heads, p, stream); break;
-        case Shape::kD96: e = launch_split_d96(bf16, plan.heads, p, stream); break;
-        case Shape::kD128: e = launch_split_d128(bf16, plan.heads, p, stream); break;
-        case Shape::kD256: e = launch_split_d256(bf16, plan.heads, p, stream); break;
-        case Shape::kMla: e = launch_split_mla_simt(bf16, plan.heads, p, stream); break;
+        case Shape::kD64: e = launch_split_d64(bf16, plan.heads, p, maps, stream); break;
+        case Shape::kD96: e = launch_split_d96(bf16, plan.heads, p, maps, stream); break;
+        case Shape::kD128: e = launch_split_d128(bf16, plan.heads, p, maps, stream); break;
+        case Shape::kD256: e = launch_split_d256(bf16, plan.heads, p, maps, stream); break;
+        case Shape::kMla: e = launch_split_mla_simt(bf16, plan.heads, p, maps, stream); break;
         default: e = cudaErrorInvalidValue; break;
     }
     if (e != cudaSuccess) return fail(DA_ERR_CUDA, "split kernel launch: %s", cudaGetErrorString(e));

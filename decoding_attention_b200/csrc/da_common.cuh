@@ -2,6 +2,7 @@
 // block, mbarrier / bulk-copy (TMA) PTX wrappers with bounded waits, and 16-bit -> fp32 unpacking.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -37,6 +38,7 @@ struct SplitParams {
     int num_splits;
     int chunk_keys;    // keys per split (multiple of the tile)
     int is_alibi;
+    int use_tmap;      // full tiles are fetched with one tiled TMA copy through the tensor maps
     float scale_log2;  // softmax scale * log2(e)
 };
 
@@ -96,6 +98,19 @@ __device__ __forceinline__ void bulk_copy_g2s_hint(void *dst_smem, const void *s
             "r"(smem_u32(dst_smem)),
         "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
         : "memory");
+}
+// A whole K/V tile: tiled TMA copy of the box {dim, 1 head, tile rows} at (0, head, row) of the
+// rank-3 tensor map [rows][heads][dim].  One instruction per tile; the engine walks the rows.
+__device__ __forceinline__ void tma_load_tile_3d(void *dst_smem, const CUtensorMap *tmap, int c0, int c1, int c2,
+                                                 uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::
+            "r"(smem_u32(dst_smem)),
+        "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *tmap) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
     uint64_t pol;

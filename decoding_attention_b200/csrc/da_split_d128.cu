@@ -7,21 +7,21 @@ namespace da {
 namespace {
 // lanes per key row, keys per lane-group and tile, consumer warps, pipeline stages
 template <typename T, int G, int KPT>
-using Cfg = SplitCfg<T, 128, 128, 16, G, KPT, 4, 2, false>;
+using Cfg = SplitCfg<T, 128, 128, 16, G, KPT, 4, 3, false>;
 
 template <typename T>
-cudaError_t launch_t(int heads, const SplitParams &p, cudaStream_t s) {
+cudaError_t launch_t(int heads, const SplitParams &p, const KvMaps &m, cudaStream_t s) {
     switch (heads) {
-        case 1: return launch_split<Cfg<T, 1, 8>>(p, s);
-        case 2: return launch_split<Cfg<T, 2, 8>>(p, s);
-        case 4: return launch_split<Cfg<T, 4, 8>>(p, s);
+        case 1: return launch_split<Cfg<T, 1, 8>>(p, m.k, m.v, s);
+        case 2: return launch_split<Cfg<T, 2, 8>>(p, m.k, m.v, s);
+        case 4: return launch_split<Cfg<T, 4, 8>>(p, m.k, m.v, s);
         default: return cudaErrorInvalidValue;
     }
 }
 }  // namespace
 
-cudaError_t launch_split_d128(bool bf16, int heads, const SplitParams &p, cudaStream_t s) {
-    return bf16 ? launch_t<__nv_bfloat16>(heads, p, s) : launch_t<__half>(heads, p, s);
+cudaError_t launch_split_d128(bool bf16, int heads, const SplitParams &p, const KvMaps &m, cudaStream_t s) {
+    return bf16 ? launch_t<__nv_bfloat16>(heads, p, m, s) : launch_t<__half>(heads, p, m, s);
 }
 
 SplitVariantInfo split_info_d128(int heads) {

@@ -10,18 +10,18 @@ template <typename T, int G, int KPT>
 using Cfg = SplitCfg<T, 256, 256, 16, G, KPT, 4, 2, false>;
 
 template <typename T>
-cudaError_t launch_t(int heads, const SplitParams &p, cudaStream_t s) {
+cudaError_t launch_t(int heads, const SplitParams &p, const KvMaps &m, cudaStream_t s) {
     switch (heads) {
-        case 1: return launch_split<Cfg<T, 1, 4>>(p, s);
-        case 2: return launch_split<Cfg<T, 2, 4>>(p, s);
-        case 4: return launch_split<Cfg<T, 4, 4>>(p, s);
+        case 1: return launch_split<Cfg<T, 1, 4>>(p, m.k, m.v, s);
+        case 2: return launch_split<Cfg<T, 2, 4>>(p, m.k, m.v, s);
+        case 4: return launch_split<Cfg<T, 4, 4>>(p, m.k, m.v, s);
         default: return cudaErrorInvalidValue;
     }
 }
 }  // namespace
 
-cudaError_t launch_split_d256(bool bf16, int heads, const SplitParams &p, cudaStream_t s) {
-    return bf16 ? launch_t<__nv_bfloat16>(heads, p, s) : launch_t<__half>(heads, p, s);
+cudaError_t launch_split_d256(bool bf16, int heads, const SplitParams &p, const KvMaps &m, cudaStream_t s) {
+    return bf16 ? launch_t<__nv_bfloat16>(heads, p, m, s) : launch_t<__half>(heads, p, m, s);
 }
 
 SplitVariantInfo split_info_d256(int heads) {

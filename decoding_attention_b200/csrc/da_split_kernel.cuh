@@ -91,7 +91,9 @@ __device__ __forceinline__ float pick(const float (&arr)[N], int idx) {
 }
 
 template <class C>
-__global__ void __launch_bounds__(C::THREADS) da_split_kernel(const SplitParams p) {
+__global__ void __launch_bounds__(C::THREADS) da_split_kernel(const SplitParams p,
+                                                              const __grid_constant__ CUtensorMap tm_k,
+                                                              const __grid_constant__ CUtensorMap tm_v) {
     using T = typename C::T;
     constexpr int D = C::D, DV = C::DV, LANES = C::LANES, G = C::G, KPT = C::KPT, NG = C::NG, TILE = C::TILE;
     constexpr int NCH = C::NCH, NCHV = C::NCHV, NV = C::NV, RV = C::RV, REP = C::REP, STAGES = C::STAGES;
@@ -154,6 +156,10 @@ __global__ void __launch_bounds__(C::THREADS) da_split_kernel(const SplitParams 
         // ---------------- producer warp ----------------
         const T *kg = reinterpret_cast<const T *>(p.k) + (size_t)hk * D;
         const T *vg = reinterpret_cast<const T *>(p.v) + (size_t)hk * (C::MLA ? D : DV);
+        if (p.use_tmap && lane == 0) {
+            tma_prefetch_desc(&tm_k);
+            if (!C::MLA) tma_prefetch_desc(&tm_v);
+        }
         bool ok = true;
         int armed_k = 0, armed_v = 0;  // tiles whose full barrier has been armed
         for (int t = 0; t < n_tiles; ++t) {
@@ -164,22 +170,33 @@ __global__ void __launch_bounds__(C::THREADS) da_split_kernel(const SplitParams 
             const size_t tok0 = (size_t)seq_begin + key0;
             if (t >= STAGES) ok = mbar_wait(&empty_k[st], ph ^ 1u, abort_flag);
             if (!ok) break;
-            if (lane == 0) mbar_arrive_expect_tx(&full_k[st], (uint32_t)rows * C::K_ROW_BYTES);
+            const bool whole = p.use_tmap && rows == TILE;  // a partial tile must not read past the sequence
+            if (lane == 0) {
+                mbar_arrive_expect_tx(&full_k[st], (uint32_t)rows * C::K_ROW_BYTES);
+                if (whole) tma_load_tile_3d(ks + st * C::K_TILE_BYTES, &tm_k, 0, hk, (int)tok0, &full_k[st]);
+            }
             __syncwarp();
             armed_k = t + 1;
-            for (int r = lane; r < rows; r += 32) {
-                bulk_copy_g2s(ks + st * C::K_TILE_BYTES + r * C::K_ROW_BYTES, kg + (tok0 + r) * p.k_row_stride,
-                              C::K_ROW_BYTES, &full_k[st]);
+            if (!whole) {
+                for (int r = lane; r < rows; r += 32) {
+                    bulk_copy_g2s(ks + st * C::K_TILE_BYTES + r * C::K_ROW_BYTES, kg + (tok0 + r) * p.k_row_stride,
+                                  C::K_ROW_BYTES, &full_k[st]);
+                }
             }
             if (!C::MLA) {
                 if (t >= STAGES) ok = mbar_wait(&empty_v[st], ph ^ 1u, abort_flag);
                 if (!ok) break;
-                if (lane == 0) mbar_arrive_expect_tx(&full_v[st], (uint32_t)rows * C::V_ROW_BYTES);
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(&full_v[st], (uint32_t)rows * C::V_ROW_BYTES);
+                    if (whole) tma_load_tile_3d(vs + st * C::V_TILE_BYTES, &tm_v, 0, hk, (int)tok0, &full_v[st]);
+                }
                 __syncwarp();
                 armed_v = t + 1;
-                for (int r = lane; r < rows; r += 32) {
-                    bulk_copy_g2s(vs + st * C::V_TILE_BYTES + r * C::V_ROW_BYTES, vg + (tok0 + r) * p.v_row_stride,
-                                  C::V_ROW_BYTES, &full_v[st]);
+                if (!whole) {
+                    for (int r = lane; r < rows; r += 32) {
+                        bulk_copy_g2s(vs + st * C::V_TILE_BYTES + r * C::V_ROW_BYTES,
+                                      vg + (tok0 + r) * p.v_row_stride, C::V_ROW_BYTES, &full_v[st]);
+                    }
                 }
             }
         }
@@ -416,8 +433,11 @@ __global__ void __launch_bounds__(C::THREADS) da_split_kernel(const SplitParams 
     }
 }
 
+// Host side.  `tm_k` / `tm_v` are rank-3 tensor maps [rows][head_k][dim] with box {dim, 1, TILE}
+// (see make_kv_tensor_map in da_api.cu); they are ignored when p.use_tmap is 0.
 template <class C>
-cudaError_t launch_split(const SplitParams &p, cudaStream_t stream) {
+cudaError_t launch_split(const SplitParams &p, const CUtensorMap &tm_k, const CUtensorMap &tm_v,
+                         cudaStream_t stream) {
     static bool attr_set[64] = {};
     int dev = 0;
     cudaError_t err = cudaGetDevice(&dev);
@@ -428,7 +448,7 @@ cudaError_t launch_split(const SplitParams &p, cudaStream_t stream) {
         attr_set[dev] = true;
     }
     dim3 grid(p.num_splits, p.head_k * p.head_chunks, p.batch);
-    da_split_kernel<C><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(p);
+    da_split_kernel<C><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(p, tm_k, tm_v);
     return cudaGetLastError();
 }
 

@@ -10,16 +10,16 @@ template <typename T, int G, int KPT>
 using Cfg = SplitCfg<T, 576, 512, 8, G, KPT, 4, 3, true>;
 
 template <typename T>
-cudaError_t launch_t(int heads, const SplitParams &p, cudaStream_t s) {
+cudaError_t launch_t(int heads, const SplitParams &p, const KvMaps &m, cudaStream_t s) {
     switch (heads) {
-        case 1: return launch_split<Cfg<T, 1, 2>>(p, s);
+        case 1: return launch_split<Cfg<T, 1, 2>>(p, m.k, m.v, s);
         default: return cudaErrorInvalidValue;
     }
 }
 }  // namespace
 
-cudaError_t launch_split_mla_simt(bool bf16, int heads, const SplitParams &p, cudaStream_t s) {
-    return bf16 ? launch_t<__nv_bfloat16>(heads, p, s) : launch_t<__half>(heads, p, s);
+cudaError_t launch_split_mla_simt(bool bf16, int heads, const SplitParams &p, const KvMaps &m, cudaStream_t s) {
+    return bf16 ? launch_t<__nv_bfloat16>(heads, p, m, s) : launch_t<__half>(heads, p, m, s);
 }
 
 SplitVariantInfo split_info_mla_simt(int heads) {
