@@ -1,0 +1,440 @@
+#!/usr/bin/env python
+"""Benchmark of the decode-attention hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one decode-attention call over the whole batch.  The headline workload is the
+GQA bf16 variable-length batch (256 sequences per GPU, 32/8 heads, dim 128, lengths uniform in
+[512, 4096]); with N GPUs the global batch is 256*N sequences cut into per-rank groups (no
+collective on the data path; weak scaling).  `value` is KV-cache GB/s = algorithmic KV bytes of
+all ranks / (max-over-ranks device time per step), inputs resident in HBM.  `e2e` is the same
+metric through the host-buffer C-ABI call (pinned host tensors; H2D of q, k, v, cu_seq_k and D2H of
+o inside the timed region).  `--impl reference` times the reference project's own CPU attention
+(oracle/_ref, compiled from its tester.h) on a bounded sample of the same workload.
+Prints ONE JSON line on stdout.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from concurrent.futures import ThreadPoolExecutor
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+from decoding_attention_b200 import sharded, synth  # noqa: E402
+
+METRIC = "decode_attention_kv_read_bandwidth"
+UNIT = "GB/s"
+SEQS_PER_GPU = 256
+L2_BYTES = 126 * 1024 * 1024
+
+
+def log(*a):
+    print(*a, file=sys.stderr, flush=True)
+
+
+def load_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ["clocks.sm", "clocks.max.sm", "power.draw", "clocks_event_reasons.hw_slowdown",
+              "clocks_event_reasons.hw_thermal_slowdown", "clocks_event_reasons.sw_thermal_slowdown",
+              "clocks_event_reasons.sw_power_cap"]
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + ",".join(self.FIELDS),
+                 "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL,
+                text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, power, reasons = [], [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) != len(self.FIELDS):
+                continue
+            try:
+                sm.append(float(f[0]))
+                smax.append(float(f[1]))
+                power.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(self.FIELDS[3:], f[3:]):
+                if val.lower().startswith("active"):
+                    reasons.add(name.split(".")[-1])
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------
+
+def make_call(cabi, w, q, k, v, cu, o, **kw):
+    args = cabi.make_args(q, k, v, o, cu, max(w.max_seq_k, 1), w.dim_v, is_alibi=w.is_alibi,
+                          stream=torch.cuda.current_stream().cuda_stream, **kw)
+    return args
+
+
+def time_resident(cabi, args, steps, warmup, barrier, flush=None):
+    """K back-to-back steps between two events (after W warm-ups); also the split kernel alone via the
+    profiling hook.  Returns (seconds per step, seconds per main-kernel launch, launches)."""
+    for _ in range(warmup):
+        cabi.decode_fwd(args)
+    torch.cuda.synchronize()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for a, b in ev:  # create the underlying events
+        a.record()
+        b.record()
+    torch.cuda.synchronize()
+    barrier()
+    torch.cuda.synchronize()
+    l0 = cabi.launch_count()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for a, b in ev:
+        cabi.set_profile_events(a, b)
+        cabi.decode_fwd(args)
+    t1.record()
+    cabi.set_profile_events(None, None)
+    torch.cuda.synchronize()
+    barrier()
+    launches = cabi.launch_count() - l0
+    total = t0.elapsed_time(t1) * 1e-3
+    kern = statistics.mean(a.elapsed_time(b) for a, b in ev) * 1e-3
+    return total / steps, kern, launches
+
+
+def time_flushed(cabi, args, iters, flush_buf):
+    """Per-call events with an L2-sized write between calls (for working sets that fit in L2)."""
+    times = []
+    for i in range(iters + 3):
+        flush_buf.add_(1)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        cabi.decode_fwd(args)
+        b.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            times.append(a.elapsed_time(b) * 1e-3)
+    return statistics.median(times)
+
+
+def time_e2e(cabi, w, host, steps, warmup, barrier):
+    q, k, v, cu, o = host
+    args = cabi.make_args(q, k, v, o, cu, max(w.max_seq_k, 1), w.dim_v, is_alibi=w.is_alibi, packed=True,
+                          stream=torch.cuda.current_stream().cuda_stream)
+    for _ in range(warmup):
+        cabi.decode_fwd_host(args)
+    torch.cuda.synchronize()
+    barrier()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        cabi.decode_fwd_host(args)
+    t1.record()
+    torch.cuda.synchronize()
+    barrier()
+    h2d = sum(t.numel() * t.element_size() for t in (q, k, v, cu) if t is not None)
+    d2h = o.numel() * o.element_size()
+    return t0.elapsed_time(t1) * 1e-3 / steps, h2d, d2h
+
+
+def cpu_reference_sample(w, budget_s, threads):
+    """The reference's CPU attention (oracle/_ref) on the first sequences of the workload, one Tester
+    instance per sequence (its harness needs equal lengths inside a batch), spread over `threads`
+    host threads.  Falls back to the oracle restatement when oracle/_ref is not built."""
+    from oracle import attn_oracle
+    kind = "reference" if attn_oracle.ref_available() else "port"
+
+    def run_seq(b):
+        q, k, v, cu = w.make("cpu", seqs=[b])
+        t = time.perf_counter()
+        if kind == "reference":
+            attn_oracle.ref_attn_cpu(q, k, v, w.seq_lens[b], dim_v=w.dim_v, is_alibi=w.is_alibi, threads=1)
+        else:
+            attn_oracle.attn_cpu(q, k, v, cu, dim_v=w.dim_v, is_alibi=w.is_alibi, threads=1)
+        return time.perf_counter() - t
+
+    t_one = run_seq(0)
+    per_key = t_one / max(w.seq_lens[0], 1)
+    n, keys = 0, 0
+    while n < w.batch and (keys * per_key / threads < budget_s or n < threads):
+        keys += w.seq_lens[n]
+        n += 1
+    seqs = list(range(n))
+    data = [w.make("cpu", seqs=[b]) for b in seqs]  # generation is not part of the timed region
+
+    def run_prepared(i):
+        q, k, v, cu = data[i]
+        if kind == "reference":
+            attn_oracle.ref_attn_cpu(q, k, v, w.seq_lens[i], dim_v=w.dim_v, is_alibi=w.is_alibi, threads=1)
+        else:
+            attn_oracle.attn_cpu(q, k, v, cu, dim_v=w.dim_v, is_alibi=w.is_alibi, threads=1)
+
+    def timed():
+        t = time.perf_counter()
+        with ThreadPoolExecutor(max_workers=threads) as pool:
+            list(pool.map(run_prepared, range(n)))
+        return time.perf_counter() - t
+
+    kv = w.kv_bytes(seq_lens=[w.seq_lens[b] for b in seqs])
+    return kind, n, kv, timed
+
+
+def run_ours(opt):
+    from decoding_attention_b200 import cabi
+    cabi.lib()  # fail loudly if the CUDA library is missing
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if opt.gpus != world:
+        log(f"note: --gpus {opt.gpus} but WORLD_SIZE {world}; using WORLD_SIZE")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    def sum_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return t.item()
+
+    hbm_peak, peak_kind = load_peaks()
+    w = synth.config_gqa_varlen(batch=SEQS_PER_GPU * world)
+    mine = sharded.partition_batch(w.seq_lens, world)[rank]
+    my_lens = [w.seq_lens[b] for b in mine]
+    q, k, v, cu = w.make(dev, seqs=mine)
+    o = torch.empty(len(mine), w.head_q, w.dim_v, dtype=w.dtype, device=dev)
+    local = synth.Workload(w.name, w.dtype, w.head_q, w.head_k, w.dim, w.dim_v, my_lens, dist=w.dist, scale=w.scale)
+    args = make_call(cabi, local, q, k, v, cu, o)
+    my_bytes = local.kv_bytes()
+    total_bytes = sum_over_ranks(my_bytes)
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    sec, kern_sec, launches = time_resident(cabi, args, opt.steps, opt.warmup, barrier)
+    clocks = sampler.stop()
+    sec_max = max_over_ranks(sec)
+    status = cabi.device_status()
+    assert status == cabi.DA_OK, "a kernel reported a timed-out wait"
+
+    # end to end through the host-buffer entry point
+    host = [t.cpu().pin_memory() if t is not None else None for t in (q, k, v, cu)]
+    host.append(torch.empty_like(o, device="cpu").pin_memory())
+    e2e_steps = max(1, min(opt.steps, 10))
+    e2e_sec, h2d, d2h = time_e2e(cabi, local, host, e2e_steps, min(opt.warmup, 3), barrier)
+    e2e_sec = max_over_ranks(e2e_sec)
+    e2e_ok = torch.equal(host[4].to(dev), o)
+
+    out = {
+        "metric": METRIC, "value": round(total_bytes / sec_max / 1e9, 2), "unit": UNIT, "n_gpus": world,
+        "steps": opt.steps, "warmup": opt.warmup, "ms_per_step": round(sec_max * 1e3, 4),
+        "us_per_call": round(sec_max * 1e6, 2), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 in/out, fp32 accumulate", "data": "synthetic (seeded, decoding_attention_b200.synth)",
+        "config": {"workload": "GQA decode bf16, batch-sharded: 256 sequences per GPU, head_q 32, head_k 8, "
+                               "dim 128, seq_k ~ U[512,4096], N(0,1)*0.5, ALiBi off (BASELINE config 2)",
+                   "sequences": w.batch, "total_keys": w.total_k, "kv_bytes": int(total_bytes),
+                   "l2": "inputs (%.2f GB per GPU) larger than the 126 MB L2" % (my_bytes / 1e9),
+                   "num_splits": cabi.num_splits(args)},
+        "clocks": clocks,
+        "e2e": {"value": round(total_bytes / e2e_sec / 1e9, 3), "unit": UNIT, "h2d_bytes_per_step": int(h2d),
+                "d2h_bytes_per_step": int(d2h), "ms_per_step": round(e2e_sec * 1e3, 3), "steps": e2e_steps,
+                "matches_resident_result": bool(e2e_ok),
+                "call": "da_decode_fwd_host (pinned host q, k, v, cu_seq_k -> device, kernels, o -> host)"},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "hbm", "achieved": round(my_bytes / kern_sec / 1e9, 2), "peak": hbm_peak,
+                     "unit": "GB/s", "frac": round(my_bytes / kern_sec / 1e9 / hbm_peak, 4), "of": peak_kind,
+                     "frac_of_nominal_8000": round(my_bytes / kern_sec / 1e9 / 8000.0, 4),
+                     "kernel": "da_split_kernel (GQA, dim 128, 4 heads per CTA)",
+                     "kernel_us": round(kern_sec * 1e6, 2), "algorithmic_bytes": int(my_bytes),
+                     "traffic": opt.traffic},
+    }
+
+    if rank == 0 and world == 1 and not opt.no_cpu:
+        threads = os.cpu_count() or 1
+        kind, n, kv, timed = cpu_reference_sample(w, 12.0, threads)
+        t = timed()
+        out["cpu_baseline"] = {"value": round(kv / t / 1e9, 4), "unit": UNIT, "cores": threads, "kind": kind,
+                               "seconds": round(t, 2),
+                               "sample": f"first {n} of {w.batch} sequences ({kv / 1e6:.0f} MB of KV), one "
+                                         f"single-threaded attn_cpu per sequence over {threads} host threads"}
+    if not opt.no_extra:
+        try:
+            out["other_configs"] = other_configs(cabi, dev, world, rank, barrier, max_over_ranks, hbm_peak)
+        except Exception as e:  # the headline line must survive a failure in the extras
+            out["other_configs"] = {"error": repr(e)}
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+
+
+def other_configs(cabi, dev, world, rank, barrier, max_over_ranks, hbm_peak):
+    """The remaining BASELINE configurations: 1-GPU numbers (rank 0 of a 1-GPU run) and the key-range
+    sharded long sequence at every N."""
+    res = {}
+    flush = torch.zeros(256 * 1024 * 1024 // 4, dtype=torch.float32, device=dev)
+
+    def one(name, w, flushed):
+        q, k, v, cu = w.make(dev)
+        o = torch.empty(w.batch, w.head_q, w.dim_v, dtype=w.dtype, device=dev)
+        args = make_call(cabi, w, q, k, v, cu, o)
+        for _ in range(3):
+            cabi.decode_fwd(args)
+        torch.cuda.synchronize()
+        if flushed:
+            sec = time_flushed(cabi, args, 20, flush)
+        else:
+            sec, _, _ = time_resident(cabi, args, 20, 3, lambda: None)
+        res[name] = {"us_per_call": round(sec * 1e6, 2), "kv_GBps": round(w.kv_bytes() / sec / 1e9, 1),
+                     "frac_of_hbm_peak": round(w.kv_bytes() / sec / 1e9 / hbm_peak, 4),
+                     "ref_tflops": round(w.ref_flops() / sec / 1e12, 3), "num_splits": cabi.num_splits(args),
+                     "timing": "median of 20 calls, 256 MB L2 flush between calls" if flushed else
+                               "20 back-to-back calls, inputs larger than L2"}
+        del q, k, v, o
+
+    if world == 1:
+        one("mha_fp16_b4_sk1024", synth.config_mha_small(), True)
+        one("mqa_alibi_fp16_b128_sk2048", synth.config_mqa_alibi(), True)
+        for b in (1, 8, 32, 128):
+            one(f"mla_bf16_b{b}_sk4096", synth.config_mla(batch=b), b <= 8)
+
+    # key-range sharded long sequence (strong scaling: 131072 keys in total at every N)
+    w = synth.config_long_mha()
+    lo, hi = sharded.key_range(w.seq_lens[0], rank, world)
+    q, k, v, cu = w.make(dev, key_range=(lo, hi))
+    dec = sharded.KeyRangeShardedDecoder(1, w.head_q, w.dim_v, w.dtype, dev)
+    off = torch.tensor([lo], dtype=torch.int32, device=dev)
+    tot = torch.tensor([w.seq_lens[0]], dtype=torch.int32, device=dev)
+    for _ in range(5):
+        dec.step(q, k, v, cu, hi - lo, kv_pos_offset=off, kv_total_len=tot)
+    torch.cuda.synchronize()
+    barrier()
+    steps = 50
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        dec.step(q, k, v, cu, hi - lo, kv_pos_offset=off, kv_total_len=tot)
+    t1.record()
+    torch.cuda.synchronize()
+    barrier()
+    sec = max_over_ranks(t0.elapsed_time(t1) * 1e-3 / steps)
+    res["mha_bf16_b1_sk131072_key_range_sharded"] = {
+        "n_gpus": world, "us_per_call": round(sec * 1e6, 2), "kv_GBps": round(w.kv_bytes() / sec / 1e9, 1),
+        "frac_of_hbm_peak_per_gpu": round(w.kv_bytes() / world / sec / 1e9 / hbm_peak, 4), "scaling": "strong",
+        "steps": "local partial (o fp32, lse) -> all-gather of %d-byte records -> on-device LSE merge" % (
+            dec.rec.numel() * 4)}
+    return res
+
+
+# ------------------------------------------------------------------------------------------------
+# reference arm
+# ------------------------------------------------------------------------------------------------
+
+def run_reference(opt):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    w = synth.config_gqa_varlen(batch=SEQS_PER_GPU * world)
+    budget = max(0.5, min(4.0, 150.0 / (opt.steps + opt.warmup)))
+    kind, n, kv, timed = cpu_reference_sample(w, budget, threads)
+    for _ in range(opt.warmup):
+        timed()
+    t = time.perf_counter()
+    for _ in range(opt.steps):
+        timed()
+    sec = (time.perf_counter() - t) / opt.steps
+    val = round(kv / sec / 1e9, 4)
+    sample = (f"first {n} of {w.batch} sequences ({kv / 1e6:.0f} MB of KV) per step, one single-threaded attn_cpu "
+              f"(the reference's csrc/common/tester.h:133-259, compiled unmodified) per sequence over {threads} "
+              "host threads")
+    out = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": world, "steps": opt.steps,
+           "warmup": opt.warmup, "ms_per_step": round(sec * 1e3, 3), "higher_is_better": True, "scaling": "weak",
+           "vs_baseline": None, "dtype": "bf16 in/out, fp32 accumulate", "data": "synthetic (seeded)",
+           "config": {"workload": "GQA decode bf16, batch-sharded: 256 sequences per GPU, head_q 32, head_k 8, "
+                                  "dim 128, seq_k ~ U[512,4096], N(0,1)*0.5, ALiBi off (BASELINE config 2)",
+                      "sequences": w.batch, "total_keys": w.total_k},
+           "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
+           "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+           "gpu_launches": 0}
+    print(json.dumps(out), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extra", action="store_true", help="skip the other BASELINE configurations")
+    ap.add_argument("--traffic", type=float, default=None,
+                    help="DRAM bytes per launch of the dominant kernel from an ncu capture (see profiles/)")
+    opt = ap.parse_args()
+    opt.warmup = max(opt.warmup, 3)
+    if opt.traffic is None:
+        try:
+            with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
+                opt.traffic = json.load(f).get("da_split_kernel_gqa_bytes_per_launch_full_workload")
+        except Exception:
+            opt.traffic = None
+    if opt.impl == "reference":
+        run_reference(opt)
+    else:
+        run_ours(opt)
+
+
+if __name__ == "__main__":
+    main()

@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(_PKG, "libdecoding_attn_b200.so")
 DA_OK, DA_ERR_INVALID_ARG, DA_ERR_UNSUPPORTED, DA_ERR_WORKSPACE, DA_ERR_CUDA, DA_ERR_TIMEOUT = range(6)
 
 EXPORTS = ["da_decode_fwd", "da_decode_fwd_host", "da_decode_workspace_bytes", "da_decode_num_splits",
-           "da_merge_partials", "da_device_status", "da_status_string", "da_last_error", "da_launch_count"]
+           "da_merge_partials", "da_set_profile_events", "da_device_status", "da_status_string", "da_last_error", "da_launch_count"]
 
 
 class DecodeArgs(ctypes.Structure):
@@ -64,6 +64,8 @@ def lib():
                                         ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                         ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                         ctypes.c_int32, ctypes.c_void_p]
+        l.da_set_profile_events.restype = None
+        l.da_set_profile_events.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
         l.da_device_status.restype = ctypes.c_int
         l.da_status_string.restype = ctypes.c_char_p
         l.da_status_string.argtypes = [ctypes.c_int]
@@ -133,3 +135,9 @@ def device_status():
 
 def launch_count():
     return lib().da_launch_count()
+
+
+def set_profile_events(start=None, stop=None):
+    """torch.cuda.Event objects (already recorded once, so that they exist) or None."""
+    lib().da_set_profile_events(start.cuda_event if start is not None else None,
+                                stop.cuda_event if stop is not None else None)

@@ -18,6 +18,7 @@ namespace da {
 namespace {
 
 thread_local char g_err[512] = "";
+thread_local cudaEvent_t g_prof_start = nullptr, g_prof_stop = nullptr;
 std::atomic<uint64_t> g_launches{0};
 
 int fail(int code, const char *fmt, ...) {
@@ -381,6 +382,7 @@ int da_decode_fwd(const da_decode_args_t *a) {
         if (rc != DA_OK) return rc;
     }
     cudaError_t e;
+    if (g_prof_start) cudaEventRecord(g_prof_start, stream);
     switch (plan.shape) {
         case Shape::kD64: e = launch_split_d64(bf16, plan.heads, p, maps, stream); break;
         case Shape::kD96: e = launch_split_d96(bf16, plan.heads, p, maps, stream); break;
@@ -391,6 +393,7 @@ int da_decode_fwd(const da_decode_args_t *a) {
     }
     if (e != cudaSuccess) return fail(DA_ERR_CUDA, "split kernel launch: %s", cudaGetErrorString(e));
     count_launch();
+    if (g_prof_stop) cudaEventRecord(g_prof_stop, stream);
 
     if (plan.num_splits > 1) {
         MergeParams m;
@@ -513,6 +516,11 @@ int da_merge_partials(const float *part_o, const float *part_lse, int32_t num_pa
     cudaError_t e = launch_merge(m, reinterpret_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail(DA_ERR_CUDA, "merge kernel launch: %s", cudaGetErrorString(e));
     return DA_OK;
+}
+
+void da_set_profile_events(void *start_event, void *stop_event) {
+    g_prof_start = reinterpret_cast<cudaEvent_t>(start_event);
+    g_prof_stop = reinterpret_cast<cudaEvent_t>(stop_event);
 }
 
 int da_device_status(void) {

@@ -1,0 +1,108 @@
+"""Multi-GPU use of the decode-attention library: one process per GPU, torch.distributed for the
+plumbing.  The reference is single-GPU (its only device handling is cudaSetDevice(gpu_rank),
+benchmarks/cpp/benchmark_decoding_attn.cpp:27, :43), so both modes below are additions:
+
+* batch sharding -- sequences are independent, so a batch is cut into per-rank groups of
+  sequences with balanced key counts and every rank runs the ordinary kernel on its own packed
+  K/V.  No collective on the data path.
+* key-range sharding -- one long sequence's KV cache lives in contiguous key ranges, one per rank.
+  Every rank computes a partial (o fp32, lse) over its range, the fixed-size records are
+  all-gathered (NCCL over NVLink; tiny, latency-bound) and every rank merges them on its device
+  with da_merge_partials.
+"""
+from typing import List, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def partition_batch(seq_lens: Sequence[int], world: int) -> List[List[int]]:
+    """Greedy longest-first assignment of sequences to ``world`` ranks balancing total keys.
+    Deterministic; every rank's list is sorted by sequence index."""
+    order = sorted(range(len(seq_lens)), key=lambda i: (-seq_lens[i], i))
+    loads = [0] * world
+    out: List[List[int]] = [[] for _ in range(world)]
+    for i in order:
+        r = min(range(world), key=lambda j: (loads[j], j))
+        out[r].append(i)
+        loads[r] += seq_lens[i]
+    return [sorted(x) for x in out]
+
+
+def key_range(seq_len: int, rank: int, world: int, align: int = 64) -> Tuple[int, int]:
+    """Contiguous key range of ``rank``: equal shares rounded up to ``align`` keys (the kernels'
+    tile), the last ranks possibly shorter or empty."""
+    share = -(-seq_len // world)
+    share = -(-share // align) * align
+    lo = min(rank * share, seq_len)
+    return lo, min(lo + share, seq_len)
+
+
+def record_floats(rows: int, dim_v: int) -> int:
+    """Length of one rank's record: rows*dim_v floats of o, then rows floats of lse, padded to 4."""
+    return -(-(rows * (dim_v + 1)) // 4) * 4
+
+
+def record_views(rec: torch.Tensor, rows: int, dim_v: int):
+    """(o view [rows, dim_v], lse view [rows]) into a record buffer (or into each of a stack)."""
+    o = rec[..., :rows * dim_v].unflatten(-1, (rows, dim_v))
+    lse = rec[..., rows * dim_v:rows * dim_v + rows]
+    return o, lse
+
+
+def gather_records(rec: torch.Tensor, group=None) -> torch.Tensor:
+    """All-gather equal-size records: [n] -> [world, n].  Works on CUDA (NCCL) and CPU (gloo)."""
+    world = dist.get_world_size(group)
+    out = torch.empty(world, rec.numel(), dtype=rec.dtype, device=rec.device)
+    if rec.is_cuda:
+        dist.all_gather_into_tensor(out, rec, group=group)
+    else:
+        dist.all_gather(list(out.unbind(0)), rec, group=group)
+    return out
+
+
+class KeyRangeShardedDecoder:
+    """Decode attention for sequences whose KV cache is sharded by key range over the ranks of a
+    process group.  Construct once per (batch, head_q, dim_v); ``step`` is then allocation-free."""
+
+    def __init__(self, batch, head_q, dim_v, out_dtype, device, group=None):
+        from . import cabi
+        self.cabi = cabi
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rows, self.dim_v, self.head_q, self.batch = batch * head_q, dim_v, head_q, batch
+        n = record_floats(self.rows, dim_v)
+        self.rec = torch.zeros(n, dtype=torch.float32, device=device)
+        self.gathered = torch.zeros(self.world, n, dtype=torch.float32, device=device)
+        self.out = torch.empty(batch, head_q, dim_v, dtype=out_dtype, device=device)
+        self.lse = torch.empty(batch, head_q, dtype=torch.float32, device=device)
+        self.rec_o, self.rec_lse = record_views(self.rec, self.rows, dim_v)
+
+    def local_partial(self, q, k, v, cu_seq_k, max_seq_k, is_alibi, kv_pos_offset, kv_total_len, softmax_scale=None):
+        a = self.cabi.make_args(q, k, v, None, cu_seq_k, max_seq_k, self.dim_v, is_alibi=is_alibi,
+                                softmax_scale=softmax_scale, lse=self.rec_lse, o_f32=self.rec_o,
+                                kv_pos_offset=kv_pos_offset, kv_total_len=kv_total_len,
+                                stream=torch.cuda.current_stream().cuda_stream)
+        self.cabi.decode_fwd(a)
+
+    def exchange(self):
+        if self.world == 1:
+            self.gathered[0].copy_(self.rec)
+        else:
+            dist.all_gather_into_tensor(self.gathered, self.rec, group=self.group)
+
+    def merge(self):
+        n = self.rec.numel()
+        lse_base = self.gathered.data_ptr() + self.rows * self.dim_v * 4
+        self.cabi.check(self.cabi.lib().da_merge_partials(
+            self.gathered.data_ptr(), lse_base, self.world, self.rows, self.dim_v, n, self.dim_v, n, 1,
+            self.out.data_ptr(), None, self.lse.data_ptr(), int(self.out.dtype == torch.bfloat16),
+            torch.cuda.current_stream().cuda_stream))
+        return self.out
+
+    def step(self, q, k, v, cu_seq_k, max_seq_k, is_alibi=False, kv_pos_offset=None, kv_total_len=None,
+             softmax_scale=None):
+        """q replicated; k, v this rank's key range; returns the full result on every rank."""
+        self.local_partial(q, k, v, cu_seq_k, max_seq_k, is_alibi, kv_pos_offset, kv_total_len, softmax_scale)
+        self.exchange()
+        return self.merge()

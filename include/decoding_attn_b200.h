@@ -110,6 +110,12 @@ int da_merge_partials(const float *part_o, const float *part_lse, int32_t num_pa
                       int64_t part_stride_o, int64_t row_stride_o, int64_t part_stride_lse, int64_t row_stride_lse,
                       void *o, float *o_f32, float *lse, int32_t is_bf16, void *stream);
 
+/* Profiling hook for the calling thread: while both are non-NULL, da_decode_fwd records the CUDA
+ * event `start_event` on the stream just before its main (key-streaming) kernel and `stop_event`
+ * just after it, so a benchmark can time that kernel apart from the merge kernel.  Pass NULLs to
+ * switch it off.  The reference times whole calls only (CudaTimer, csrc/common/cuda_timer.h:10-52). */
+void da_set_profile_events(void *start_event, void *stop_event);
+
 /* Reads and clears the current device's kernel status word (synchronises the device).  Returns
  * DA_OK, or DA_ERR_TIMEOUT if a kernel gave up a bounded wait since the last call.  The reference
  * has no counterpart: its kernel has no waits and its host checks exit() (common.h:17-49). */

@@ -27,6 +27,7 @@
 #include <functional>
 #include <limits>
 #include <memory>
+#include <mutex>
 #include <numeric>
 #include <string>
 #include <thread>
@@ -38,6 +39,30 @@
 #undef private
 
 namespace {
+
+// The harness logs every allocation to stderr (tensor.h:40).  While any call is in flight stderr is
+// parked on /dev/null; calls may overlap (one per host thread), hence the count.
+std::mutex g_quiet_mu;
+int g_quiet_users = 0, g_saved_err = -1;
+void quiet_enter() {
+    std::lock_guard<std::mutex> lock(g_quiet_mu);
+    if (g_quiet_users++ == 0) {
+        fflush(stderr);
+        g_saved_err = dup(2);
+        int devnull = open("/dev/null", O_WRONLY);
+        if (g_saved_err >= 0 && devnull >= 0) dup2(devnull, 2);
+        if (devnull >= 0) close(devnull);
+    }
+}
+void quiet_leave() {
+    std::lock_guard<std::mutex> lock(g_quiet_mu);
+    if (--g_quiet_users == 0 && g_saved_err >= 0) {
+        fflush(stderr);
+        dup2(g_saved_err, 2);
+        close(g_saved_err);
+        g_saved_err = -1;
+    }
+}
 
 template <typename T>
 void run_slice(const uint16_t *q, const uint16_t *k, const uint16_t *v, uint16_t *o, size_t b0, size_t nb,
@@ -60,11 +85,7 @@ extern "C" int ref_attn_cpu(const uint16_t *q, const uint16_t *k, const uint16_t
     if (!q || !k || !o || batch <= 0 || seq_k <= 0) return 1;
     if ((dim == dim_v) != (v != nullptr)) return 2;  // tester.h:66 builds V only when dim == dim_v
     int n = std::max(1, std::min<int>(threads, (int)batch));
-    // The harness logs every allocation to stderr (tensor.h:40); park stderr on /dev/null meanwhile.
-    fflush(stderr);
-    int saved_err = dup(2);
-    int devnull = open("/dev/null", O_WRONLY);
-    if (saved_err >= 0 && devnull >= 0) dup2(devnull, 2);
+    quiet_enter();
     std::vector<std::thread> pool;
     for (int i = 0; i < n; ++i) {
         size_t b0 = (size_t)batch * i / n, b1 = (size_t)batch * (i + 1) / n;
@@ -83,11 +104,6 @@ extern "C" int ref_attn_cpu(const uint16_t *q, const uint16_t *k, const uint16_t
         }
     }
     for (auto &t : pool) t.join();
-    fflush(stderr);
-    if (saved_err >= 0) {
-        dup2(saved_err, 2);
-        close(saved_err);
-    }
-    if (devnull >= 0) close(devnull);
+    quiet_leave();
     return 0;
 }
