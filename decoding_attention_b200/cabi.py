@@ -8,7 +8,7 @@ import ctypes
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libdecoding_attn_b200.so")
+LIB_PATH = os.environ.get("DA_LIB_PATH") or os.path.join(_PKG, "libdecoding_attn_b200.so")
 
 DA_OK, DA_ERR_INVALID_ARG, DA_ERR_UNSUPPORTED, DA_ERR_WORKSPACE, DA_ERR_CUDA, DA_ERR_TIMEOUT = range(6)
 

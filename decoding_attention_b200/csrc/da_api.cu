@@ -200,7 +200,8 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
     const int64_t max_len = a.max_seq_k > 0 ? a.max_seq_k : 1;
     const int64_t tiles_per_unit = (max_len + tile - 1) / tile;
 
-    constexpr int kMinTiles = 4, kMaxTiles = 16, kWaves = 4;
+    const int kMinTiles = 4, kWaves = 4;
+    const int kMaxTiles = getenv("DA_MAX_TILES") ? atoi(getenv("DA_MAX_TILES")) : 32;
     int64_t splits;
     const char *env = getenv("DA_NUM_SPLITS");
     if (a.num_splits > 0) {

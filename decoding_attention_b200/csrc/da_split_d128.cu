@@ -1,5 +1,12 @@
 // Instantiations of the CUDA-core split-KV kernel for head dims (128, 128).  These replace the
 // reference's per-shape tiling choices (csrc/kernel/decoding_attn/decoding_fwd_hd*.cu).
+#ifndef DA_D128_STAGES
+#define DA_D128_STAGES 2
+#define DA_D128_MINB 3
+#endif
+#ifndef DA_D128_KPT
+#define DA_D128_KPT 8
+#endif
 #include "da_internal.h"
 #include "da_split_kernel.cuh"
 
@@ -7,14 +14,14 @@ namespace da {
 namespace {
 // lanes per key row, keys per lane-group and tile, consumer warps, pipeline stages
 template <typename T, int G, int KPT>
-using Cfg = SplitCfg<T, 128, 128, 16, G, KPT, 4, 3, false>;
+using Cfg = SplitCfg<T, 128, 128, 16, G, KPT, 4, DA_D128_STAGES, false, DA_D128_MINB>;
 
 template <typename T>
 cudaError_t launch_t(int heads, const SplitParams &p, const KvMaps &m, cudaStream_t s) {
     switch (heads) {
-        case 1: return launch_split<Cfg<T, 1, 8>>(p, m.k, m.v, s);
-        case 2: return launch_split<Cfg<T, 2, 8>>(p, m.k, m.v, s);
-        case 4: return launch_split<Cfg<T, 4, 8>>(p, m.k, m.v, s);
+        case 1: return launch_split<Cfg<T, 1, DA_D128_KPT>>(p, m.k, m.v, s);
+        case 2: return launch_split<Cfg<T, 2, DA_D128_KPT>>(p, m.k, m.v, s);
+        case 4: return launch_split<Cfg<T, 4, DA_D128_KPT>>(p, m.k, m.v, s);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -26,9 +33,9 @@ cudaError_t launch_split_d128(bool bf16, int heads, const SplitParams &p, const 
 
 SplitVariantInfo split_info_d128(int heads) {
     switch (heads) {
-        case 1: return {Cfg<__half, 1, 8>::TILE, 1, (227 * 1024) / (Cfg<__half, 1, 8>::SMEM_BYTES + 1024)};
-        case 2: return {Cfg<__half, 2, 8>::TILE, 2, (227 * 1024) / (Cfg<__half, 2, 8>::SMEM_BYTES + 1024)};
-        case 4: return {Cfg<__half, 4, 8>::TILE, 4, (227 * 1024) / (Cfg<__half, 4, 8>::SMEM_BYTES + 1024)};
+        case 1: return {Cfg<__half, 1, DA_D128_KPT>::TILE, 1, (227 * 1024) / (Cfg<__half, 1, DA_D128_KPT>::SMEM_BYTES + 1024)};
+        case 2: return {Cfg<__half, 2, DA_D128_KPT>::TILE, 2, (227 * 1024) / (Cfg<__half, 2, DA_D128_KPT>::SMEM_BYTES + 1024)};
+        case 4: return {Cfg<__half, 4, DA_D128_KPT>::TILE, 4, (227 * 1024) / (Cfg<__half, 4, DA_D128_KPT>::SMEM_BYTES + 1024)};
         default: return {0, 0, 0};
     }
 }

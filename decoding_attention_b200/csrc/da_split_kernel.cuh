@@ -22,11 +22,12 @@
 
 namespace da {
 
-template <typename T_, int D_, int DV_, int LANES_, int G_, int KPT_, int NWARPS_, int STAGES_, bool MLA_>
+template <typename T_, int D_, int DV_, int LANES_, int G_, int KPT_, int NWARPS_, int STAGES_, bool MLA_, int MINB_ = 1>
 struct SplitCfg {
     using T = T_;
     static constexpr int D = D_, DV = DV_, LANES = LANES_, G = G_, KPT = KPT_, NWARPS = NWARPS_, STAGES = STAGES_;
-    static constexpr bool MLA = MLA_;              // V is the first DV elements of each K row
+    static constexpr bool MLA = MLA_;
+    static constexpr int MINB = MINB_;             // resident CTAs per SM the register budget must allow              // V is the first DV elements of each K row
     static constexpr int NCH = D / (8 * LANES);    // 16-byte chunks of a K row per lane
     static constexpr int NCHV = DV / (8 * LANES);  // 16-byte chunks of a V row per lane
     static constexpr int GPW = 32 / LANES;         // groups per warp
@@ -91,7 +92,7 @@ __device__ __forceinline__ float pick(const float (&arr)[N], int idx) {
 }
 
 template <class C>
-__global__ void __launch_bounds__(C::THREADS) da_split_kernel(const SplitParams p,
+__global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const SplitParams p,
                                                               const __grid_constant__ CUtensorMap tm_k,
                                                               const __grid_constant__ CUtensorMap tm_v) {
     using T = typename C::T;
