@@ -62,7 +62,7 @@ int device_state(DeviceState **out) {
     return DA_OK;
 }
 
-enum class Shape { kD64, kD96, kD128, kD256, kMla, kNone };
+enum class Shape { kD64, kD96, kD128, kD256, kMla, kMlaTc, kNone };
 
 Shape shape_of(int64_t dim, int64_t dim_v, bool has_v) {
     if (has_v) {
@@ -76,8 +76,16 @@ Shape shape_of(int64_t dim, int64_t dim_v, bool has_v) {
     return Shape::kNone;
 }
 
+// The tensor-core kernel covers the shape the latent-KV layout exists for: 128 query heads over one
+// KV head.  Other head counts of (576, 512) run on the CUDA-core kernel.
+bool mla_on_tensor_cores(const da_decode_args_t &a) {
+    return a.v == nullptr && a.dim == 576 && a.dim_v == 512 && a.head_q == 128 && a.head_k == 1 &&
+           !getenv("DA_MLA_SIMT");
+}
+
 int heads_per_cta(Shape s, int group) {
     if (s == Shape::kMla) return 1;
+    if (s == Shape::kMlaTc) return 128;
     const char *env = getenv("DA_HEADS_PER_CTA");
     if (env) {
         int g = atoi(env);
@@ -95,6 +103,7 @@ SplitVariantInfo variant_info(Shape s, int heads) {
         case Shape::kD128: return split_info_d128(heads);
         case Shape::kD256: return split_info_d256(heads);
         case Shape::kMla: return split_info_mla_simt(heads);
+        case Shape::kMlaTc: return split_info_mla_tc();
         default: return {0, 0, 0};
     }
 }
@@ -125,12 +134,10 @@ EncodeTiledFn encode_tiled_fn() {
 constexpr uint64_t kMapRows = 1ull << 31;
 struct MapKey {
     const void *base;
-    long long row_stride;
-    int head_k, dim, tile, bf16;
-    bool operator==(const MapKey &o) const {
-        return base == o.base && row_stride == o.row_stride && head_k == o.head_k && dim == o.dim && tile == o.tile &&
-               bf16 == o.bf16;
-    }
+    uint64_t dims[3];
+    uint64_t strides[2];
+    uint32_t box[3];
+    int rank, swizzle128, bf16;
 };
 struct MapCacheEntry {
     MapKey key;
@@ -140,25 +147,41 @@ struct MapCacheEntry {
 thread_local MapCacheEntry g_map_cache[8];
 thread_local int g_map_next = 0;
 
-int make_kv_tensor_map(const void *base, long long row_stride, int head_k, int dim, int tile, bool bf16,
-                       CUtensorMap *out) {
-    const MapKey key{base, row_stride, head_k, dim, tile, bf16 ? 1 : 0};
+// Tiled tensor map over 16-bit elements; dims/strides/box innermost first, strides in bytes for
+// dimensions 1.. (dimension 0 is contiguous).  Recently built maps are kept per thread.
+int make_tensor_map(const void *base, int rank, const uint64_t *dims, const uint64_t *strides, const uint32_t *box,
+                    bool swizzle128, bool bf16, CUtensorMap *out) {
+    MapKey key;
+    memset(&key, 0, sizeof(key));
+    key.base = base;
+    key.rank = rank;
+    key.swizzle128 = swizzle128;
+    key.bf16 = bf16;
+    for (int i = 0; i < rank; ++i) {
+        key.dims[i] = dims[i];
+        key.box[i] = box[i];
+        if (i + 1 < rank) key.strides[i] = strides[i];
+    }
     for (auto &e : g_map_cache) {
-        if (e.valid && e.key == key) {
+        if (e.valid && memcmp(&e.key, &key, sizeof(key)) == 0) {
             *out = e.map;
             return DA_OK;
         }
     }
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return fail(DA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-    const cuuint64_t dims[3] = {(cuuint64_t)dim, (cuuint64_t)head_k, kMapRows};
-    const cuuint64_t strides[2] = {(cuuint64_t)dim * 2, (cuuint64_t)row_stride * 2};
-    const cuuint32_t box[3] = {(cuuint32_t)dim, 1, (cuuint32_t)tile};
     const cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = fn(out, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
-                    const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    cuuint64_t d[3], st[2];
+    cuuint32_t bx[3];
+    for (int i = 0; i < rank; ++i) {
+        d[i] = dims[i];
+        bx[i] = box[i];
+        if (i + 1 < rank) st[i] = strides[i];
+    }
+    CUresult r = fn(out, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)rank,
+                    const_cast<void *>(base), d, st, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(DA_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
     MapCacheEntry &slot = g_map_cache[g_map_next];
     g_map_next = (g_map_next + 1) % 8;
@@ -166,6 +189,14 @@ int make_kv_tensor_map(const void *base, long long row_stride, int head_k, int d
     slot.map = *out;
     slot.valid = true;
     return DA_OK;
+}
+
+int make_kv_tensor_map(const void *base, long long row_stride, int head_k, int dim, int tile, bool bf16,
+                       CUtensorMap *out) {
+    const uint64_t dims[3] = {(uint64_t)dim, (uint64_t)head_k, kMapRows};
+    const uint64_t strides[2] = {(uint64_t)dim * 2, (uint64_t)row_stride * 2};
+    const uint32_t box[3] = {(uint32_t)dim, 1, (uint32_t)tile};
+    return make_tensor_map(base, 3, dims, strides, box, false, bf16, out);
 }
 
 struct Plan {
@@ -192,16 +223,19 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
                     "with v and (576,512) without",
                     (long long)a.dim, (long long)a.dim_v, has_v ? "given" : "NULL");
     }
+    if (shape == Shape::kMla && mla_on_tensor_cores(a)) shape = Shape::kMlaTc;
     const int group = (int)(a.head_q / a.head_k);
     const int heads = heads_per_cta(shape, group);
     const SplitVariantInfo info = variant_info(shape, heads);
     const int tile = info.tile_keys;
-    const int64_t units = a.batch * a.head_k * (group / heads);
+    // The tensor-core MLA kernel runs two CTAs (one per half of the output columns) per key range.
+    const int64_t units = shape == Shape::kMlaTc ? a.batch * 2 : a.batch * a.head_k * (group / heads);
     const int64_t max_len = a.max_seq_k > 0 ? a.max_seq_k : 1;
     const int64_t tiles_per_unit = (max_len + tile - 1) / tile;
 
-    const int kMinTiles = 4, kWaves = 4;
-    const int kMaxTiles = getenv("DA_MAX_TILES") ? atoi(getenv("DA_MAX_TILES")) : 32;
+    // A tensor-core MLA CTA first stages 144 KB of Q: give it at least 256 keys to amortise that.
+    const int kMinTiles = shape == Shape::kMlaTc ? 8 : 4, kWaves = shape == Shape::kMlaTc ? 2 : 4;
+    const int kMaxTiles = getenv("DA_MAX_TILES") ? atoi(getenv("DA_MAX_TILES")) : (shape == Shape::kMlaTc ? 64 : 32);
     int64_t splits;
     const char *env = getenv("DA_NUM_SPLITS");
     if (a.num_splits > 0) {
@@ -375,7 +409,21 @@ int da_decode_fwd(const da_decode_args_t *a) {
     memset(&maps, 0, sizeof(maps));
     // Tiled TMA needs a global stride that is a multiple of 16 bytes (checked above: 8 elements) and
     // a box of at most 256 elements per dimension; the latent-KV rows (576) keep the row-wise path.
-    p.use_tmap = (plan.shape != Shape::kMla) && !getenv("DA_NO_TMAP");
+    p.use_tmap = (plan.shape != Shape::kMla) && (plan.shape != Shape::kMlaTc) && !getenv("DA_NO_TMAP");
+    if (plan.shape == Shape::kMlaTc) {
+        // q as [batch][128][576] in boxes {64, 128, 1}; the latent cache as [rows][576] in boxes
+        // {64, tile}; both land 128-byte-swizzled, the layout the UMMA descriptors name.
+        const uint64_t qd[3] = {576, 128, (uint64_t)a->batch};
+        const uint64_t qs[2] = {576 * 2, (uint64_t)p.q_row_stride * 2};
+        const uint32_t qb[3] = {64, 128, 1};
+        rc = make_tensor_map(p.q, 3, qd, qs, qb, true, bf16, &maps.k);
+        if (rc != DA_OK) return rc;
+        const uint64_t kd[2] = {576, kMapRows};
+        const uint64_t ks[1] = {(uint64_t)p.k_row_stride * 2};
+        const uint32_t kb[2] = {64, (uint32_t)plan.tile_keys};
+        rc = make_tensor_map(p.k, 2, kd, ks, kb, true, bf16, &maps.v);
+        if (rc != DA_OK) return rc;
+    }
     if (p.use_tmap) {
         rc = make_kv_tensor_map(p.k, p.k_row_stride, p.head_k, (int)a->dim, plan.tile_keys, bf16, &maps.k);
         if (rc != DA_OK) return rc;
@@ -390,6 +438,7 @@ int da_decode_fwd(const da_decode_args_t *a) {
         case Shape::kD128: e = launch_split_d128(bf16, plan.heads, p, maps, stream); break;
         case Shape::kD256: e = launch_split_d256(bf16, plan.heads, p, maps, stream); break;
         case Shape::kMla: e = launch_split_mla_simt(bf16, plan.heads, p, maps, stream); break;
+        case Shape::kMlaTc: e = launch_mla_tc(bf16, p, maps.k, maps.v, stream); break;
         default: e = cudaErrorInvalidValue; break;
     }
     if (e != cudaSuccess) return fail(DA_ERR_CUDA, "split kernel launch: %s", cudaGetErrorString(e));

@@ -70,14 +70,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Bounded wait.  Every try_wait itself blocks for a hardware-defined slice of time, so the cap
-// below is seconds of wall time, far beyond any legitimate wait; when it runs out (or another
-// thread of the CTA has already given up) the caller records kStatusWaitTimeout and leaves.
-constexpr uint32_t kMaxWaitSpins = 1u << 24;
+// Bounded wait.  A legitimate wait here lasts microseconds; after kMaxWaitCycles SM clocks (about
+// a quarter of a second) the waiter gives up, raises the CTA's abort flag so that the other
+// waiters of the CTA leave too, and the caller records kStatusWaitTimeout.
+constexpr long long kMaxWaitCycles = 500ll * 1000 * 1000;
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
-    for (uint32_t spin = 0; spin < kMaxWaitSpins; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t spin = 1;; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 1023u) == 1023u && *abort_flag) return false;
+        if ((spin & 63u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > kMaxWaitCycles) break;
+        }
     }
     *abort_flag = 1;
     return false;

@@ -32,6 +32,13 @@ SplitVariantInfo split_info_d128(int heads);
 SplitVariantInfo split_info_d256(int heads);
 SplitVariantInfo split_info_mla_simt(int heads);
 
+// Tensor-core (tcgen05 / TMEM) kernel for 128 query heads over one latent KV head (da_mla_sm100.cu).
+// tm_q: rank-3 map of q, box {64, 128, 1}; tm_k: rank-2 map of the latent cache, box {64, tile keys};
+// both with the 128-byte swizzle.
+cudaError_t launch_mla_tc(bool bf16, const SplitParams &p, const CUtensorMap &tm_q, const CUtensorMap &tm_k,
+                          cudaStream_t s);
+SplitVariantInfo split_info_mla_tc();
+
 // Merge of split / shard partials (da_merge.cu).  cu_seq_k and chunk_keys (both optional) limit a
 // row to the splits that cover keys; without them every part is read.
 struct MergeParams {

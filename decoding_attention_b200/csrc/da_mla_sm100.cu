@@ -1,0 +1,448 @@
+// Latent-KV (MLA) decode attention on the sm_100a tensor cores: tcgen05.mma with accumulators in
+// tensor memory (TMEM), operands staged by TMA.
+//
+// Shape: 128 query heads share one KV head whose rows hold 576 values; V is the first 512 of them
+// (the reference runs this shape through its generic kernel, one CTA per query head:
+// csrc/kernel/decoding_attn/decoding_fwd_hd576_hdv512.cu:9-17, so every K row is fetched 128
+// times).  Here the 128 heads are the M dimension of two dense contractions per key tile:
+//     S[128 x N]   = Q[128 x 576] . K_tile[N x 576]^T          (both operands K-major)
+//     O[128 x 256] += P[128 x N]  . V_tile[N x 256]             (V = the same smem tile, MN-major)
+// TMEM holds 128 lanes x 512 fp32 columns, which the 128 x 512 output alone would fill, so one CTA
+// owns one half of the output columns (256 TMEM columns) plus two S buffers; the two CTAs of a
+// (sequence, key range) each compute S themselves and never talk to each other.
+//
+// Warp roles (192 threads): warps 0-3 = softmax/epilogue, thread r owns TMEM lane r = head r, so
+// row maxima, sums and the rare rescale of O need no cross-thread traffic; warp 4 = TMA producer;
+// warp 5 = TMEM allocation and MMA issue (one elected lane).
+// Online softmax with a lazy reference: the running reference max m_ref of a row is only raised
+// when a score exceeds it by more than 8 (log2 domain), so O is rescaled a handful of times.
+// Every wait is bounded; on expiry the CTA records kStatusWaitTimeout and still frees its TMEM.
+#include <type_traits>
+
+#include "da_internal.h"
+
+namespace da {
+namespace {
+
+constexpr int kHeads = 128;       // M of both contractions
+constexpr int kDim = 576;         // K of S = Q K^T
+constexpr int kDimV = 512;
+constexpr int kHalfV = 256;       // output columns per CTA
+constexpr int kTile = 32;         // keys per tile (N of S, K of O)
+constexpr int kStages = 2;
+constexpr int kBlocks = kDim / 64;                    // 64-element (128-byte) column blocks of a row
+constexpr int kQBlockBytes = kHeads * 128;            // 16 KB: [128 heads x 64 dims], 128B-swizzled
+constexpr int kKBlockBytes = kTile * 128;             // 4 KB: [32 keys x 64 dims], 128B-swizzled
+constexpr int kKStageBytes = kBlocks * kKBlockBytes;  // 36 KB
+constexpr int kPBytes = kHeads * kTile * 2;           // 8 KB, core-matrix (no swizzle) K-major
+constexpr int kOffQ = 0;
+constexpr int kOffK = kOffQ + kBlocks * kQBlockBytes;
+constexpr int kOffP = kOffK + kStages * kKStageBytes;
+constexpr int kOffBar = kOffP + kPBytes;
+constexpr int kNumBars = 1 + 2 * kStages + 2 + 2 + 2;  // q_full, k_full/k_empty, s_full[2], s_empty[2], p_full, pv_done
+constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16 + 1024;  // + tmem slot/abort flag + alignment slack
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 512;
+constexpr int kColS = 0;      // two S buffers of kTile columns
+constexpr int kColO = 64;     // 256 output columns
+constexpr float kRescaleThreshold = 8.0f;
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t *slot_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot_smem)),
+                 "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc], issued by one thread.
+__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        :
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+// The mbarrier receives one arrival when every tcgen05.mma issued so far by this thread has finished.
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, "
+        "%15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        :
+        : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]),
+          "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]),
+          "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *tm, int c0, int c1, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
+            "r"(smem_u32(dst)),
+        "l"(tm), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// Shared-memory matrix descriptor of tcgen05.mma: start address, leading / stride byte offsets (all
+// in 16-byte units), descriptor version 1, swizzle mode in bits 61-63 (0 = none, 2 = 128 bytes).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t swizzle) {
+    return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+           ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | ((uint64_t)swizzle << 61);
+}
+// Instruction descriptor for kind::f16: fp32 accumulate, A/B type (0 = fp16, 1 = bf16), majorness
+// (0 = K-major, 1 = MN-major), N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t ab_fmt, uint32_t b_mn_major, uint32_t m, uint32_t n) {
+    return (1u << 4) | (ab_fmt << 7) | (ab_fmt << 10) | (b_mn_major << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+struct MlaParams {
+    SplitParams sp;  // q/k/o pointers, strides, split geometry, scale, status
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+
+    const int split = blockIdx.x;
+    const int half = blockIdx.y;  // which 256 output columns
+    const int b = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int seq_begin = p.cu_seq_k[b];
+    const int len = p.cu_seq_k[b + 1] - seq_begin;
+    const int k_begin = split * p.chunk_keys;
+    const int k_end = min(len, k_begin + p.chunk_keys);
+    T *o_out = reinterpret_cast<T *>(p.o);
+    if (*reinterpret_cast<volatile int *>(p.status) != kStatusOk) return;  // an earlier CTA timed out: do not pile up
+
+    if (k_begin >= k_end) {
+        if (p.num_splits == 1) {  // empty sequence: zero row, LSE = -inf
+            for (int idx = tid; idx < kHeads * kHalfV; idx += kThreads) {
+                const int h = idx / kHalfV, d = half * kHalfV + idx % kHalfV;
+                if (o_out) o_out[(size_t)b * p.o_row_stride + (size_t)h * kDimV + d] = from_float<T>(0.0f);
+                if (p.o_f32) p.o_f32[((size_t)b * p.head_q + h) * kDimV + d] = 0.0f;
+            }
+            if (p.lse && half == 0 && tid < kHeads) p.lse[(size_t)b * p.head_q + tid] = -INFINITY;
+        }
+        return;
+    }
+    const int n_tiles = (k_end - k_begin + kTile - 1) / kTile;
+
+    uint8_t *q_s = smem + kOffQ;
+    uint8_t *k_s = smem + kOffK;
+    uint8_t *p_s = smem + kOffP;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBar);
+    uint64_t *q_full = bars;
+    uint64_t *k_full = bars + 1;
+    uint64_t *k_empty = k_full + kStages;
+    uint64_t *s_full = k_empty + kStages;
+    uint64_t *s_empty = s_full + 2;
+    uint64_t *p_full = s_empty + 2;
+    uint64_t *pv_done = p_full + 1;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kNumBars);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    if (tid == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&k_full[s], 1);
+            mbar_init(&k_empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&s_full[s], 1);
+            mbar_init(&s_empty[s], kHeads);
+        }
+        mbar_init(p_full, kHeads);
+        mbar_init(pv_done, 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 5) tmem_alloc(tmem_slot, kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    constexpr uint32_t kFmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+    constexpr uint32_t kIdescQK = instr_desc(kFmt, 0, kHeads, kTile);
+    constexpr uint32_t kIdescPV = instr_desc(kFmt, 1, kHeads, kHalfV);
+    bool ok = true;
+
+    if (warp == 4) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_q);
+            tma_prefetch_desc(&tm_k);
+            mbar_arrive_expect_tx(q_full, kBlocks * kQBlockBytes);
+            for (int kb = 0; kb < kBlocks; ++kb) tma_load_tile_3d(q_s + kb * kQBlockBytes, &tm_q, kb * 64, 0, b, q_full);
+        }
+        const T *k_g = reinterpret_cast<const T *>(p.k);
+        for (int t = 0; t < n_tiles && ok; ++t) {
+            const int st = t % kStages;
+            const uint32_t ph = (uint32_t)(t / kStages) & 1u;
+            const int key0 = k_begin + t * kTile;
+            const int rows = min(kTile, k_end - key0);
+            const size_t tok0 = (size_t)seq_begin + key0;
+            if (t >= kStages) ok = mbar_wait(&k_empty[st], ph ^ 1u, abort_flag);
+            if (!ok) break;
+            uint8_t *dst = k_s + st * kKStageBytes;
+            if (rows == kTile) {
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(&k_full[st], kKStageBytes);
+                    for (int kb = 0; kb < kBlocks; ++kb) tma_load_2d(dst + kb * kKBlockBytes, &tm_k, kb * 64, (int)tok0, &k_full[st]);
+                }
+            } else {
+                // Ragged tail: plain loads into the 128-byte-swizzled layout, rows past the end zeroed
+                // (the tensor map must not be asked for rows beyond the sequence).
+                for (int i = lane; i < kTile * (kDim / 8); i += 32) {
+                    const int r = i / (kDim / 8), c = i % (kDim / 8);
+                    uint4 v = make_uint4(0, 0, 0, 0);
+                    if (r < rows) v = *reinterpret_cast<const uint4 *>(k_g + (tok0 + r) * p.k_row_stride + c * 8);
+                    const int kb = c >> 3, cc = c & 7;
+                    *reinterpret_cast<uint4 *>(dst + kb * kKBlockBytes + r * 128 + ((cc ^ (r & 7)) << 4)) = v;
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&k_full[st]);
+            }
+            __syncwarp();
+        }
+    } else if (warp == 5) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t q_addr = smem_u32(q_s), k_addr = smem_u32(k_s), p_addr = smem_u32(p_s);
+            auto issue_qk = [&](int t) {
+                const int st = t % kStages;
+                const uint32_t d = tmem_base + kColS + (t & 1) * kTile;
+#pragma unroll 1
+                for (int kb = 0; kb < kBlocks; ++kb) {
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        const uint64_t a = smem_desc(q_addr + kb * kQBlockBytes + ks * 32, 16, 1024, 2);
+                        const uint64_t bd = smem_desc(k_addr + st * kKStageBytes + kb * kKBlockBytes + ks * 32, 16, 1024, 2);
+                        umma_ss(d, a, bd, kIdescQK, (kb | ks) ? 1u : 0u);
+                    }
+                }
+                umma_commit(&s_full[t & 1]);
+            };
+            ok = mbar_wait(q_full, 0, abort_flag);
+            if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag);
+            if (ok) {
+                tc_fence_after();
+                issue_qk(0);
+            }
+            for (int t = 0; t < n_tiles && ok; ++t) {
+                if (t + 1 < n_tiles) {
+                    const int t1 = t + 1;
+                    ok = mbar_wait(&k_full[t1 % kStages], (uint32_t)(t1 / kStages) & 1u, abort_flag);
+                    if (ok && t1 >= 2) ok = mbar_wait(&s_empty[t1 & 1], ((uint32_t)(t1 / 2) & 1u) ^ 1u, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_qk(t1);
+                }
+                ok = mbar_wait(p_full, (uint32_t)t & 1u, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const int st = t % kStages;
+                const uint32_t d = tmem_base + kColO;
+#pragma unroll
+                for (int ks = 0; ks < kTile / 16; ++ks) {
+                    // A = P: core matrices of 8 rows x 16 bytes, 8-row groups 128 B apart, 8-key chunks 2 KB apart.
+                    const uint64_t a = smem_desc(p_addr + ks * 2 * (kHeads * 16), kHeads * 16, 128, 0);
+                    // B = V, MN-major: 64-column blocks kKBlockBytes apart (LBO), 8-key groups 1 KB apart (SBO).
+                    const uint64_t bd = smem_desc(k_addr + st * kKStageBytes + (half * 4) * kKBlockBytes + ks * 16 * 128,
+                                                  kKBlockBytes, 1024, 2);
+                    umma_ss(d, a, bd, kIdescPV, (t | ks) ? 1u : 0u);
+                }
+                umma_commit(&k_empty[st]);
+                umma_commit(pv_done);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------- softmax / epilogue: thread r <-> TMEM lane r <-> head r ----------------
+        const int r = tid;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+        const float slope2 = p.is_alibi ? exp2f(-8.0f * (float)(r + 1) / (float)p.head_q) * kLog2e : 0.0f;
+        const int pos_shift = (p.kv_pos_offset ? p.kv_pos_offset[b] : 0) - ((p.kv_total_len ? p.kv_total_len[b] : len) - 1);
+        float m_ref = -INFINITY, l = 0.0f;
+        uint32_t buf[32];
+        for (int t = 0; t < n_tiles; ++t) {
+            const int key0 = k_begin + t * kTile;
+            const int rows = min(kTile, k_end - key0);
+            ok = mbar_wait(&s_full[t & 1], (uint32_t)(t / 2) & 1u, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            tmem_ld32(lane_base + kColS + (t & 1) * kTile, buf);
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(&s_empty[t & 1]);
+
+            float s[32];
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float x = __uint_as_float(buf[j]) * p.scale_log2 + slope2 * (float)(key0 + j + pos_shift);
+                s[j] = (j < rows) ? x : -INFINITY;
+                mx = fmaxf(mx, s[j]);
+            }
+            const bool raise = mx > m_ref + kRescaleThreshold;
+            float alpha = 1.0f;
+            if (raise) {
+                alpha = exp2f(m_ref - mx);  // 0 on the first tile
+                m_ref = mx;
+                l *= alpha;
+            }
+            if (t >= 1) {
+                // P and O are free again once the previous tile's P.V has completed.
+                ok = mbar_wait(pv_done, (uint32_t)(t - 1) & 1u, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, raise)) {
+#pragma unroll 1
+                    for (int c = 0; c < kHalfV / 32; ++c) {
+                        tmem_ld32(lane_base + kColO + c * 32, buf);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) buf[j] = __float_as_uint(__uint_as_float(buf[j]) * alpha);
+                        tmem_st32(lane_base + kColO + c * 32, buf);
+                    }
+                    tmem_wait_st();
+                }
+            }
+            // P = exp2(S - m_ref), rounded to the input type, into the A-operand layout.
+            float sum = 0.0f;
+#pragma unroll
+            for (int c = 0; c < kTile / 8; ++c) {
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float p0 = exp2f(s[c * 8 + 2 * j] - m_ref), p1 = exp2f(s[c * 8 + 2 * j + 1] - m_ref);
+                    sum += p0 + p1;
+                    if (std::is_same<T, __nv_bfloat16>::value) {
+                        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                        w[j] = *reinterpret_cast<uint32_t *>(&h);
+                    } else {
+                        __half2 h = __floats2half2_rn(p0, p1);
+                        w[j] = *reinterpret_cast<uint32_t *>(&h);
+                    }
+                }
+                *reinterpret_cast<uint4 *>(p_s + c * (kHeads * 16) + r * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            l += sum;
+            fence_proxy_async();
+            tc_fence_before();
+            mbar_arrive(p_full);
+        }
+        if (ok) ok = mbar_wait(pv_done, (uint32_t)(n_tiles - 1) & 1u, abort_flag);
+        if (ok) {
+            tc_fence_after();
+            const float inv = 1.0f / l;
+            const float lse = (m_ref + log2f(l)) * kLn2;
+            const size_t row = ((size_t)b * p.head_q + r) * p.num_splits + split;
+#pragma unroll 1
+            for (int c = 0; c < kHalfV / 32; ++c) {
+                tmem_ld32(lane_base + kColO + c * 32, buf);
+                tmem_wait_ld();
+                const int d0 = half * kHalfV + c * 32;
+                if (p.num_splits > 1) {
+                    float4 *dst = reinterpret_cast<float4 *>(p.part_o + row * kDimV + d0);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        dst[j] = make_float4(__uint_as_float(buf[4 * j]) * inv, __uint_as_float(buf[4 * j + 1]) * inv,
+                                             __uint_as_float(buf[4 * j + 2]) * inv, __uint_as_float(buf[4 * j + 3]) * inv);
+                    }
+                } else {
+                    if (o_out) {
+                        uint4 *dst = reinterpret_cast<uint4 *>(o_out + (size_t)b * p.o_row_stride + (size_t)r * kDimV + d0);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            alignas(16) T tmp[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) tmp[e] = from_float<T>(__uint_as_float(buf[8 * j + e]) * inv);
+                            dst[j] = *reinterpret_cast<uint4 *>(tmp);
+                        }
+                    }
+                    if (p.o_f32) {
+                        float *dst = p.o_f32 + ((size_t)b * p.head_q + r) * kDimV + d0;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) dst[j] = __uint_as_float(buf[j]) * inv;
+                    }
+                }
+            }
+            if (half == 0) {
+                if (p.num_splits > 1) {
+                    p.part_lse[row] = lse;
+                } else if (p.lse) {
+                    p.lse[(size_t)b * p.head_q + r] = lse;
+                }
+            }
+            tc_fence_before();
+        }
+    }
+
+    if (!ok && lane == 0) atomicExch(p.status, kStatusWaitTimeout);
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+}  // namespace
+
+SplitVariantInfo split_info_mla_tc() { return {kTile, kHeads, 1}; }
+
+// tm_q: rank-3 map over q [batch][128][576], box {64, 128, 1}, 128-byte swizzle;
+// tm_k: rank-2 map over the latent cache [rows][576], box {64, kTile}, 128-byte swizzle.
+cudaError_t launch_mla_tc(bool bf16, const SplitParams &p, const CUtensorMap &tm_q, const CUtensorMap &tm_k,
+                          cudaStream_t stream) {
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    if (dev < 64 && !attr_set[dev]) {
+        err = cudaFuncSetAttribute(da_mla_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (err != cudaSuccess) return err;
+        err = cudaFuncSetAttribute(da_mla_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   kSmemBytes);
+        if (err != cudaSuccess) return err;
+        attr_set[dev] = true;
+    }
+    dim3 grid(p.num_splits, 2, p.batch);
+    if (bf16) {
+        da_mla_tc_kernel<__nv_bfloat16><<<grid, kThreads, kSmemBytes, stream>>>(p, tm_q, tm_k);
+    } else {
+        da_mla_tc_kernel<__half><<<grid, kThreads, kSmemBytes, stream>>>(p, tm_q, tm_k);
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace da
