@@ -234,14 +234,33 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
     const int64_t tiles_per_unit = (max_len + tile - 1) / tile;
 
     // A tensor-core MLA CTA first stages 144 KB of Q: give it at least 256 keys to amortise that.
-    const int kMinTiles = shape == Shape::kMlaTc ? 8 : 4, kWaves = shape == Shape::kMlaTc ? 2 : 4;
-    const int kMaxTiles = getenv("DA_MAX_TILES") ? atoi(getenv("DA_MAX_TILES")) : (shape == Shape::kMlaTc ? 64 : 32);
+    const int kMinTiles = 4, kWaves = shape == Shape::kMlaTc ? 2 : 4;
+    const int kMaxTiles = getenv("DA_MAX_TILES") ? atoi(getenv("DA_MAX_TILES")) : 32;
     int64_t splits;
     const char *env = getenv("DA_NUM_SPLITS");
     if (a.num_splits > 0) {
         splits = a.num_splits;
     } else if (env && atoi(env) > 0) {
         splits = atoi(env);
+    } else if (shape == Shape::kMlaTc) {
+        // One CTA per SM and long-running CTAs: pick the split count whose CTA total fills whole
+        // waves best (a slight penalty on more splits: more partials to merge).
+        const int64_t slots = sm_count;
+        double best = -1.0;
+        splits = 1;
+        for (int64_t s = 1; s <= tiles_per_unit && s <= 64; ++s) {
+            const int64_t tpc = (tiles_per_unit + s - 1) / s;
+            if (s > 1 && tpc < kMinTiles) break;
+            const int64_t s_eff = (tiles_per_unit + tpc - 1) / tpc;
+            if (s_eff != s) continue;
+            const int64_t total = units * s_eff;
+            const int64_t waves = (total + slots - 1) / slots;
+            const double score = (double)total / (double)(waves * slots) - 0.004 * (double)s;
+            if (score > best) {
+                best = score;
+                splits = s;
+            }
+        }
     } else {
         const int64_t slots = (int64_t)sm_count * (info.ctas_per_sm > 0 ? info.ctas_per_sm : 1);
         int64_t tiles_per_cta = (units * tiles_per_unit) / (slots * kWaves);

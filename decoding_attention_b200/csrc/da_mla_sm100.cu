@@ -28,23 +28,33 @@ constexpr int kHeads = 128;       // M of both contractions
 constexpr int kDim = 576;         // K of S = Q K^T
 constexpr int kDimV = 512;
 constexpr int kHalfV = 256;       // output columns per CTA
-constexpr int kTile = 32;         // keys per tile (N of S, K of O)
-constexpr int kStages = 2;
+#ifndef DA_MLA_TILE
+#define DA_MLA_TILE 64
+#endif
+constexpr int kTile = DA_MLA_TILE;                // keys per tile (N of S, K of O): 32 or 64
+constexpr int kStages = kTile == 32 ? 4 : 2;      // K tiles in flight
+constexpr int kSBufs = kTile == 32 ? 2 : 1;       // S accumulators in TMEM (64 columns in total)
+constexpr int kQTmemBlocks = 6;   // column blocks of Q kept in TMEM (A operand read from TMEM)
+constexpr int kQSmemBlocks = 3;   // the remaining ones stay in shared memory
 constexpr int kBlocks = kDim / 64;                    // 64-element (128-byte) column blocks of a row
 constexpr int kQBlockBytes = kHeads * 128;            // 16 KB: [128 heads x 64 dims], 128B-swizzled
-constexpr int kKBlockBytes = kTile * 128;             // 4 KB: [32 keys x 64 dims], 128B-swizzled
-constexpr int kKStageBytes = kBlocks * kKBlockBytes;  // 36 KB
-constexpr int kPBytes = kHeads * kTile * 2;           // 8 KB, core-matrix (no swizzle) K-major
+constexpr int kKBlockBytes = kTile * 128;             // [kTile keys x 64 dims], 128B-swizzled
+constexpr int kKStageBytes = kBlocks * kKBlockBytes;
+constexpr int kPBytes = kHeads * kTile * 2;           // core-matrix (no swizzle) K-major
 constexpr int kOffQ = 0;
-constexpr int kOffK = kOffQ + kBlocks * kQBlockBytes;
+constexpr int kOffK = kOffQ + kQSmemBlocks * kQBlockBytes;
 constexpr int kOffP = kOffK + kStages * kKStageBytes;
-constexpr int kOffBar = kOffP + kPBytes;
-constexpr int kNumBars = 1 + 2 * kStages + 2 + 2 + 2;  // q_full, k_full/k_empty, s_full[2], s_empty[2], p_full, pv_done
+constexpr int kOffBar = kOffP + 2 * kPBytes;
+// q_full, q_tmem, k_full/k_empty[kStages], s_full[2], s_empty[2], p_full[2], pv_done[2]
+constexpr int kNumBars = 2 + 2 * kStages + 2 + 2 + 2 + 2;
 constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16 + 1024;  // + tmem slot/abort flag + alignment slack
 constexpr int kThreads = 192;
 constexpr int kTmemCols = 512;
-constexpr int kColS = 0;      // two S buffers of kTile columns
+constexpr int kColS = 0;      // kSBufs S buffers of kTile columns
 constexpr int kColO = 64;     // 256 output columns
+constexpr int kColQ = 320;    // kQTmemBlocks * 32 columns: Q as packed 16-bit pairs, row r in lane r
+static_assert(kColQ + kQTmemBlocks * 32 <= kTmemCols && kQTmemBlocks + kQSmemBlocks == kBlocks, "TMEM / Q split");
+static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 constexpr float kRescaleThreshold = 8.0f;
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -68,8 +78,17 @@ __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
         :
-        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
-        : "memory");
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u));
+}
+// Same with the A operand read from tensor memory (row r in lane r, 16-bit values packed in pairs).
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        :
+        : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u));
 }
 // The mbarrier receives one arrival when every tcgen05.mma issued so far by this thread has finished.
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
@@ -121,6 +140,18 @@ __host__ __device__ constexpr uint32_t instr_desc(uint32_t ab_fmt, uint32_t b_mn
     return (1u << 4) | (ab_fmt << 7) | (ab_fmt << 10) | (b_mn_major << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
+#ifdef DA_MLA_PROFILE
+// Development aid (not compiled into the shipped library): cycles CTA (0,0,0) spends in each wait.
+__device__ long long g_mla_prof[64];
+#define PROF_DECL long long prof_t0 = 0; (void)prof_t0
+#define PROF_BEGIN() prof_t0 = clock64()
+#define PROF_END(slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0) g_mla_prof[slot] += clock64() - prof_t0; } while (0)
+#else
+#define PROF_DECL
+#define PROF_BEGIN()
+#define PROF_END(slot)
+#endif
+
 struct MlaParams {
     SplitParams sp;  // q/k/o pointers, strides, split geometry, scale, status
 };
@@ -160,17 +191,19 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
     uint8_t *p_s = smem + kOffP;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBar);
     uint64_t *q_full = bars;
-    uint64_t *k_full = bars + 1;
+    uint64_t *q_tmem = bars + 1;
+    uint64_t *k_full = bars + 2;
     uint64_t *k_empty = k_full + kStages;
     uint64_t *s_full = k_empty + kStages;
     uint64_t *s_empty = s_full + 2;
     uint64_t *p_full = s_empty + 2;
-    uint64_t *pv_done = p_full + 1;
+    uint64_t *pv_done = p_full + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kNumBars);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     if (tid == 0) {
         mbar_init(q_full, 1);
+        mbar_init(q_tmem, kHeads);
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&k_full[s], 1);
             mbar_init(&k_empty[s], 1);
@@ -178,9 +211,9 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
         for (int s = 0; s < 2; ++s) {
             mbar_init(&s_full[s], 1);
             mbar_init(&s_empty[s], kHeads);
+            mbar_init(&p_full[s], kHeads);
+            mbar_init(&pv_done[s], 1);
         }
-        mbar_init(p_full, kHeads);
-        mbar_init(pv_done, 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -200,17 +233,22 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
         if (lane == 0) {
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_k);
-            mbar_arrive_expect_tx(q_full, kBlocks * kQBlockBytes);
-            for (int kb = 0; kb < kBlocks; ++kb) tma_load_tile_3d(q_s + kb * kQBlockBytes, &tm_q, kb * 64, 0, b, q_full);
+            mbar_arrive_expect_tx(q_full, kQSmemBlocks * kQBlockBytes);
+            for (int kb = 0; kb < kQSmemBlocks; ++kb) {
+                tma_load_tile_3d(q_s + kb * kQBlockBytes, &tm_q, (kQTmemBlocks + kb) * 64, 0, b, q_full);
+            }
         }
         const T *k_g = reinterpret_cast<const T *>(p.k);
+        PROF_DECL;
         for (int t = 0; t < n_tiles && ok; ++t) {
             const int st = t % kStages;
             const uint32_t ph = (uint32_t)(t / kStages) & 1u;
             const int key0 = k_begin + t * kTile;
             const int rows = min(kTile, k_end - key0);
             const size_t tok0 = (size_t)seq_begin + key0;
+            PROF_BEGIN();
             if (t >= kStages) ok = mbar_wait(&k_empty[st], ph ^ 1u, abort_flag);
+            PROF_END(0);
             if (!ok) break;
             uint8_t *dst = k_s + st * kKStageBytes;
             if (rows == kTile) {
@@ -238,22 +276,41 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             const uint32_t q_addr = smem_u32(q_s), k_addr = smem_u32(k_s), p_addr = smem_u32(p_s);
+            // Descriptors differ from tile to tile only in their start-address field (low 14 bits, in
+            // 16-byte units): build them once and add constant offsets, so that the unrolled issue
+            // sequence is one add per operand and the MMA itself.  (A single thread issues these;
+            // every extra dependent instruction here is tensor-pipe idle time.)
+            const uint64_t q_desc0 = smem_desc(q_addr, 16, 1024, 2);
+            const uint64_t k_desc0 = smem_desc(k_addr, 16, 1024, 2);
+            const uint64_t v_desc0 = smem_desc(k_addr + (half * 4) * kKBlockBytes, kKBlockBytes, 1024, 2);
+            const uint64_t p_desc0 = smem_desc(p_addr, kHeads * 16, 128, 0);
+            const uint32_t q_tmem_addr = tmem_base + kColQ;
             auto issue_qk = [&](int t) {
-                const int st = t % kStages;
-                const uint32_t d = tmem_base + kColS + (t & 1) * kTile;
-#pragma unroll 1
+                const uint64_t kd = k_desc0 + (uint64_t)(((t % kStages) * kKStageBytes) >> 4);
+                const uint32_t d = tmem_base + kColS + (t % kSBufs) * kTile;
+#pragma unroll
                 for (int kb = 0; kb < kBlocks; ++kb) {
 #pragma unroll
                     for (int ks = 0; ks < 4; ++ks) {
-                        const uint64_t a = smem_desc(q_addr + kb * kQBlockBytes + ks * 32, 16, 1024, 2);
-                        const uint64_t bd = smem_desc(k_addr + st * kKStageBytes + kb * kKBlockBytes + ks * 32, 16, 1024, 2);
-                        umma_ss(d, a, bd, kIdescQK, (kb | ks) ? 1u : 0u);
+                        const uint64_t bd = kd + (uint64_t)((kb * kKBlockBytes + ks * 32) >> 4);
+                        if (kb < kQTmemBlocks) {
+                            umma_ts(d, q_tmem_addr + kb * 32 + ks * 8, bd, kIdescQK, (kb | ks) ? 1u : 0u);
+                        } else {
+                            umma_ss(d, q_desc0 + (uint64_t)(((kb - kQTmemBlocks) * kQBlockBytes + ks * 32) >> 4), bd,
+                                    kIdescQK, 1u);
+                        }
                     }
                 }
-                umma_commit(&s_full[t & 1]);
+                umma_commit(&s_full[t % kSBufs]);
             };
+            PROF_DECL;
+            PROF_BEGIN();
             ok = mbar_wait(q_full, 0, abort_flag);
+            if (ok) ok = mbar_wait(q_tmem, 0, abort_flag);
+            PROF_END(8);
+            PROF_BEGIN();
             if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag);
+            PROF_END(9);
             if (ok) {
                 tc_fence_after();
                 issue_qk(0);
@@ -261,28 +318,36 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             for (int t = 0; t < n_tiles && ok; ++t) {
                 if (t + 1 < n_tiles) {
                     const int t1 = t + 1;
+                    PROF_BEGIN();
                     ok = mbar_wait(&k_full[t1 % kStages], (uint32_t)(t1 / kStages) & 1u, abort_flag);
-                    if (ok && t1 >= 2) ok = mbar_wait(&s_empty[t1 & 1], ((uint32_t)(t1 / 2) & 1u) ^ 1u, abort_flag);
+                    PROF_END(10);
+                    PROF_BEGIN();
+                    if (ok && t1 >= kSBufs) ok = mbar_wait(&s_empty[t1 % kSBufs], ((uint32_t)(t1 / kSBufs) & 1u) ^ 1u, abort_flag);
+                    PROF_END(11);
                     if (!ok) break;
                     tc_fence_after();
+                    PROF_BEGIN();
                     issue_qk(t1);
+                    PROF_END(12);
                 }
-                ok = mbar_wait(p_full, (uint32_t)t & 1u, abort_flag);
+                PROF_BEGIN();
+                ok = mbar_wait(&p_full[t & 1], (uint32_t)(t / 2) & 1u, abort_flag);
+                PROF_END(13);
                 if (!ok) break;
                 tc_fence_after();
                 const int st = t % kStages;
                 const uint32_t d = tmem_base + kColO;
+                // A = P: core matrices of 8 rows x 16 bytes, 8-row groups 128 B apart, 8-key chunks 2 KB apart.
+                // B = V, MN-major: 64-column blocks kKBlockBytes apart (LBO), 8-key groups 1 KB apart (SBO).
+                const uint64_t pd = p_desc0 + (uint64_t)(((t & 1) * kPBytes) >> 4);
+                const uint64_t vd = v_desc0 + (uint64_t)((st * kKStageBytes) >> 4);
 #pragma unroll
                 for (int ks = 0; ks < kTile / 16; ++ks) {
-                    // A = P: core matrices of 8 rows x 16 bytes, 8-row groups 128 B apart, 8-key chunks 2 KB apart.
-                    const uint64_t a = smem_desc(p_addr + ks * 2 * (kHeads * 16), kHeads * 16, 128, 0);
-                    // B = V, MN-major: 64-column blocks kKBlockBytes apart (LBO), 8-key groups 1 KB apart (SBO).
-                    const uint64_t bd = smem_desc(k_addr + st * kKStageBytes + (half * 4) * kKBlockBytes + ks * 16 * 128,
-                                                  kKBlockBytes, 1024, 2);
-                    umma_ss(d, a, bd, kIdescPV, (t | ks) ? 1u : 0u);
+                    umma_ss(d, pd + (uint64_t)((ks * 2 * (kHeads * 16)) >> 4), vd + (uint64_t)((ks * 16 * 128) >> 4), kIdescPV,
+                            (t | ks) ? 1u : 0u);
                 }
                 umma_commit(&k_empty[st]);
-                umma_commit(pv_done);
+                umma_commit(&pv_done[t & 1]);
             }
         }
         __syncwarp();
@@ -294,25 +359,49 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
         const int pos_shift = (p.kv_pos_offset ? p.kv_pos_offset[b] : 0) - ((p.kv_total_len ? p.kv_total_len[b] : len) - 1);
         float m_ref = -INFINITY, l = 0.0f;
         uint32_t buf[32];
+        PROF_DECL;
+        const long long prof_start = clock64();
+        (void)prof_start;
+        {
+            // Q columns [0, 64 * kQTmemBlocks) of this thread's head go to TMEM as packed 16-bit pairs.
+            const T *q_row = reinterpret_cast<const T *>(p.q) + (size_t)b * p.q_row_stride + (size_t)r * kDim;
+#pragma unroll 1
+            for (int kb = 0; kb < kQTmemBlocks; ++kb) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const uint4 v = *reinterpret_cast<const uint4 *>(q_row + kb * 64 + j * 8);
+                    buf[4 * j] = v.x, buf[4 * j + 1] = v.y, buf[4 * j + 2] = v.z, buf[4 * j + 3] = v.w;
+                }
+                tmem_st32(lane_base + kColQ + kb * 32, buf);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(q_tmem);
+        }
         for (int t = 0; t < n_tiles; ++t) {
             const int key0 = k_begin + t * kTile;
             const int rows = min(kTile, k_end - key0);
-            ok = mbar_wait(&s_full[t & 1], (uint32_t)(t / 2) & 1u, abort_flag);
+            PROF_BEGIN();
+            ok = mbar_wait(&s_full[t % kSBufs], (uint32_t)(t / kSBufs) & 1u, abort_flag);
+            PROF_END(16 + warp);
             if (!ok) break;
             tc_fence_after();
-            tmem_ld32(lane_base + kColS + (t & 1) * kTile, buf);
-            tmem_wait_ld();
-            tc_fence_before();
-            mbar_arrive(&s_empty[t & 1]);
-
-            float s[32];
+            PROF_BEGIN();
+            float s[kTile];
             float mx = -INFINITY;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const float x = __uint_as_float(buf[j]) * p.scale_log2 + slope2 * (float)(key0 + j + pos_shift);
-                s[j] = (j < rows) ? x : -INFINITY;
-                mx = fmaxf(mx, s[j]);
+            for (int c0 = 0; c0 < kTile; c0 += 32) {
+                tmem_ld32(lane_base + kColS + (t % kSBufs) * kTile + c0, buf);
+                tmem_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const float x = __uint_as_float(buf[j]) * p.scale_log2 + slope2 * (float)(key0 + c0 + j + pos_shift);
+                    s[c0 + j] = (c0 + j < rows) ? x : -INFINITY;
+                    mx = fmaxf(mx, s[c0 + j]);
+                }
             }
+            tc_fence_before();
+            mbar_arrive(&s_empty[t % kSBufs]);
             const bool raise = mx > m_ref + kRescaleThreshold;
             float alpha = 1.0f;
             if (raise) {
@@ -320,22 +409,30 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                 m_ref = mx;
                 l *= alpha;
             }
-            if (t >= 1) {
-                // P and O are free again once the previous tile's P.V has completed.
-                ok = mbar_wait(pv_done, (uint32_t)(t - 1) & 1u, abort_flag);
+            PROF_END(20 + warp);
+            PROF_BEGIN();
+            if (t >= 2) {
+                // The P buffer of this tile was last read by the P.V of tile t-2.
+                ok = mbar_wait(&pv_done[t & 1], ((uint32_t)(t / 2) & 1u) ^ 1u, abort_flag);
+                if (!ok) break;
+            }
+            PROF_END(24 + warp);
+            PROF_BEGIN();
+            if (t >= 1 && __any_sync(0xffffffffu, raise)) {
+                // Rare: the reference max of some row in this warp moved.  O must be idle (P.V of tile
+                // t-1 complete) while its rows are rescaled in place.
+                ok = mbar_wait(&pv_done[(t - 1) & 1], (uint32_t)((t - 1) / 2) & 1u, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, raise)) {
 #pragma unroll 1
-                    for (int c = 0; c < kHalfV / 32; ++c) {
-                        tmem_ld32(lane_base + kColO + c * 32, buf);
-                        tmem_wait_ld();
+                for (int c = 0; c < kHalfV / 32; ++c) {
+                    tmem_ld32(lane_base + kColO + c * 32, buf);
+                    tmem_wait_ld();
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) buf[j] = __float_as_uint(__uint_as_float(buf[j]) * alpha);
-                        tmem_st32(lane_base + kColO + c * 32, buf);
-                    }
-                    tmem_wait_st();
+                    for (int j = 0; j < 32; ++j) buf[j] = __float_as_uint(__uint_as_float(buf[j]) * alpha);
+                    tmem_st32(lane_base + kColO + c * 32, buf);
                 }
+                tmem_wait_st();
             }
             // P = exp2(S - m_ref), rounded to the input type, into the A-operand layout.
             float sum = 0.0f;
@@ -354,14 +451,23 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                         w[j] = *reinterpret_cast<uint32_t *>(&h);
                     }
                 }
-                *reinterpret_cast<uint4 *>(p_s + c * (kHeads * 16) + r * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+                *reinterpret_cast<uint4 *>(p_s + (t & 1) * kPBytes + c * (kHeads * 16) + r * 16) =
+                    make_uint4(w[0], w[1], w[2], w[3]);
             }
             l += sum;
             fence_proxy_async();
             tc_fence_before();
-            mbar_arrive(p_full);
+            mbar_arrive(&p_full[t & 1]);
+            PROF_END(28 + warp);
         }
-        if (ok) ok = mbar_wait(pv_done, (uint32_t)(n_tiles - 1) & 1u, abort_flag);
+#ifdef DA_MLA_PROFILE
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0) {
+            g_mla_prof[32] += clock64() - prof_start;
+            g_mla_prof[33] += n_tiles;
+        }
+        PROF_BEGIN();
+#endif
+        if (ok) ok = mbar_wait(&pv_done[(n_tiles - 1) & 1], (uint32_t)((n_tiles - 1) / 2) & 1u, abort_flag);
         if (ok) {
             tc_fence_after();
             const float inv = 1.0f / l;
@@ -406,6 +512,9 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             }
             tc_fence_before();
         }
+#ifdef DA_MLA_PROFILE
+        PROF_END(36 + warp);
+#endif
     }
 
     if (!ok && lane == 0) atomicExch(p.status, kStatusWaitTimeout);
@@ -417,6 +526,17 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
 }
 
 }  // namespace
+
+#ifdef DA_MLA_PROFILE
+extern "C" void da_debug_mla_prof(long long *out, int reset) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, g_mla_prof, sizeof(long long) * 64);
+    if (reset) {
+        long long z[64] = {};
+        cudaMemcpyToSymbol(g_mla_prof, z, sizeof(z));
+    }
+}
+#endif
 
 SplitVariantInfo split_info_mla_tc() { return {kTile, kHeads, 1}; }
 
