@@ -29,7 +29,7 @@ constexpr int kDim = 576;         // K of S = Q K^T
 constexpr int kDimV = 512;
 constexpr int kHalfV = 256;       // output columns per CTA
 #ifndef DA_MLA_TILE
-#define DA_MLA_TILE 64
+#define DA_MLA_TILE 32
 #endif
 constexpr int kTile = DA_MLA_TILE;                // keys per tile (N of S, K of O): 32 or 64
 constexpr int kStages = kTile == 32 ? 4 : 2;      // K tiles in flight
@@ -71,29 +71,46 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
 // D[tmem] (+)= A[smem desc] * B[smem desc], issued by one thread.
+// `leader` is non-zero in exactly one lane of the issuing warp (elect_one): the whole warp walks
+// the issue sequence so that descriptors and addresses stay warp-uniform, one lane issues.
 __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                        uint32_t accumulate) {
+                                        uint32_t accumulate, uint32_t leader) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
+        "{\n\t.reg .pred p, q;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        "setp.ne.b32 q, %6, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
         :
-        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u));
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(leader));
 }
 // Same with the A operand read from tensor memory (row r in lane r, 16-bit values packed in pairs).
 __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                        uint32_t accumulate) {
+                                        uint32_t accumulate, uint32_t leader) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
+        "{\n\t.reg .pred p, q;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        "setp.ne.b32 q, %6, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
         :
-        : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u));
+        : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(leader));
 }
 // The mbarrier receives one arrival when every tcgen05.mma issued so far by this thread has finished.
-__device__ __forceinline__ void umma_commit(uint64_t *bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-                 : "memory");
+__device__ __forceinline__ void umma_commit(uint64_t *bar, uint32_t leader) {
+    asm volatile(
+        "{\n\t.reg .pred q;\n\t"
+        "setp.ne.b32 q, %1, 0;\n\t"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(smem_u32(bar)),
+        "r"(leader)
+        : "memory");
+}
+__device__ __forceinline__ uint32_t elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "elect.sync _|P, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t}"
+        : "=r"(pred));
+    return pred;
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
@@ -274,7 +291,8 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
         }
     } else if (warp == 5) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0) {
+        {
+            const uint32_t leader = elect_one();
             const uint32_t q_addr = smem_u32(q_s), k_addr = smem_u32(k_s), p_addr = smem_u32(p_s);
             // Descriptors differ from tile to tile only in their start-address field (low 14 bits, in
             // 16-byte units): build them once and add constant offsets, so that the unrolled issue
@@ -294,14 +312,14 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                     for (int ks = 0; ks < 4; ++ks) {
                         const uint64_t bd = kd + (uint64_t)((kb * kKBlockBytes + ks * 32) >> 4);
                         if (kb < kQTmemBlocks) {
-                            umma_ts(d, q_tmem_addr + kb * 32 + ks * 8, bd, kIdescQK, (kb | ks) ? 1u : 0u);
+                            umma_ts(d, q_tmem_addr + kb * 32 + ks * 8, bd, kIdescQK, (kb | ks) ? 1u : 0u, leader);
                         } else {
                             umma_ss(d, q_desc0 + (uint64_t)(((kb - kQTmemBlocks) * kQBlockBytes + ks * 32) >> 4), bd,
-                                    kIdescQK, 1u);
+                                    kIdescQK, 1u, leader);
                         }
                     }
                 }
-                umma_commit(&s_full[t % kSBufs]);
+                umma_commit(&s_full[t % kSBufs], leader);
             };
             PROF_DECL;
             PROF_BEGIN();
@@ -344,10 +362,10 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
 #pragma unroll
                 for (int ks = 0; ks < kTile / 16; ++ks) {
                     umma_ss(d, pd + (uint64_t)((ks * 2 * (kHeads * 16)) >> 4), vd + (uint64_t)((ks * 16 * 128) >> 4), kIdescPV,
-                            (t | ks) ? 1u : 0u);
+                            (t | ks) ? 1u : 0u, leader);
                 }
-                umma_commit(&k_empty[st]);
-                umma_commit(&pv_done[t & 1]);
+                umma_commit(&k_empty[st], leader);
+                umma_commit(&pv_done[t & 1], leader);
             }
         }
         __syncwarp();
