@@ -12,7 +12,7 @@ LIB_PATH = os.environ.get("DA_LIB_PATH") or os.path.join(_PKG, "libdecoding_attn
 
 DA_OK, DA_ERR_INVALID_ARG, DA_ERR_UNSUPPORTED, DA_ERR_WORKSPACE, DA_ERR_CUDA, DA_ERR_TIMEOUT = range(6)
 
-EXPORTS = ["da_decode_fwd", "da_decode_fwd_host", "da_decode_workspace_bytes", "da_decode_num_splits",
+EXPORTS = ["da_decode_fwd", "da_decode_fwd_host", "da_decode_fwd_static", "da_static_scratch_bytes", "da_decode_workspace_bytes", "da_decode_num_splits",
            "da_merge_partials", "da_set_profile_events", "da_device_status", "da_status_string", "da_last_error", "da_launch_count"]
 
 
@@ -55,6 +55,9 @@ def lib():
         l.da_decode_fwd.argtypes = [ctypes.POINTER(DecodeArgs)]
         l.da_decode_fwd_host.restype = ctypes.c_int
         l.da_decode_fwd_host.argtypes = [ctypes.POINTER(DecodeArgs)]
+        l.da_decode_fwd_static.restype = ctypes.c_int
+        l.da_decode_fwd_static.argtypes = [ctypes.POINTER(DecodeArgs)]
+        l.da_static_scratch_bytes.restype = ctypes.c_size_t
         l.da_decode_workspace_bytes.restype = ctypes.c_size_t
         l.da_decode_workspace_bytes.argtypes = [ctypes.POINTER(DecodeArgs)]
         l.da_decode_num_splits.restype = ctypes.c_int
@@ -119,6 +122,10 @@ def decode_fwd(args):
 
 def decode_fwd_host(args):
     check(lib().da_decode_fwd_host(ctypes.byref(args)))
+
+
+def decode_fwd_static(args):
+    check(lib().da_decode_fwd_static(ctypes.byref(args)))
 
 
 def workspace_bytes(args):

@@ -323,6 +323,8 @@ int check_args(const da_decode_args_t *a) {
 
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
 
+int report_error(int code, const char *msg) { return fail(code, "%s", msg); }
+
 }  // namespace da
 
 using namespace da;

@@ -57,4 +57,7 @@ cudaError_t launch_merge(const MergeParams &p, cudaStream_t s);
 
 void count_launch(int n = 1);
 
+// Records `msg` as the calling thread's last error (da_last_error) and returns `code`.
+int report_error(int code, const char *msg);
+
 }  // namespace da

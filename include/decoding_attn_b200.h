@@ -91,6 +91,21 @@ int da_decode_fwd(const da_decode_args_t *args);
  * (csrc/common/tensor.h:26-38, :74-83; csrc/common/tester.h:98-119). */
 int da_decode_fwd_host(const da_decode_args_t *host_args);
 
+/* da_decode_fwd for a caller that cannot allocate device memory and has no buffer to lend: the
+ * split partials go to a fixed 16 MiB array inside the library image (da_static_scratch_bytes()),
+ * present on every GPU that loads the library.  Meant for hosts whose memory is fully planned by
+ * someone else -- an engine that gave all of HBM to its KV-cache pool, code running where calls
+ * into the CUDA allocator are forbidden.  Leave args->workspace NULL.  Returns DA_ERR_WORKSPACE,
+ * without launching anything, when the call would need more than the array holds (num_splits = 1
+ * never needs scratch).  It calls no cudaMalloc / cudaFree.  The first call on a device looks up
+ * the array's device address (cudaGetSymbolAddress); make that first call outside any stream
+ * capture.  All calls on a device share the array, which keeps the previous call's bytes (nothing
+ * in it needs clearing): calls that overlap on the GPU race, so keep them on one stream.
+ * This entry point has no counterpart in the reference, whose kernel keeps its only scratch in
+ * shared memory. */
+int da_decode_fwd_static(const da_decode_args_t *args);
+size_t da_static_scratch_bytes(void);
+
 /* Scratch bytes da_decode_fwd needs for these arguments (0 when it will not split).  No reference
  * counterpart: the reference kernel keeps its only scratch, the score row, in shared memory
  * (decoding_fwd_launch_template.h:14-18). */
