@@ -249,7 +249,7 @@ def run_ours(opt):
         return t.item()
 
     hbm_peak, peak_kind = load_peaks()
-    w = synth.config_gqa_varlen(batch=SEQS_PER_GPU * world)
+    w = synth.config_gqa_varlen(batch=opt.seqs * world)
     mine = sharded.partition_batch(w.seq_lens, world)[rank]
     my_lens = [w.seq_lens[b] for b in mine]
     q, k, v, cu = w.make(dev, seqs=mine)
@@ -268,20 +268,23 @@ def run_ours(opt):
     assert status == cabi.DA_OK, "a kernel reported a timed-out wait"
 
     # end to end through the host-buffer entry point
-    host = [t.cpu().pin_memory() if t is not None else None for t in (q, k, v, cu)]
-    host.append(torch.empty_like(o, device="cpu").pin_memory())
     e2e_steps = max(1, min(opt.steps, 10))
-    e2e_sec, h2d, d2h = time_e2e(cabi, local, host, e2e_steps, min(opt.warmup, 3), barrier)
-    e2e_sec = max_over_ranks(e2e_sec)
-    e2e_ok = torch.equal(host[4].to(dev), o)
+    if opt.no_e2e:
+        e2e_sec, h2d, d2h, e2e_ok = float("nan"), 0, 0, False
+    else:
+        host = [t.cpu().pin_memory() if t is not None else None for t in (q, k, v, cu)]
+        host.append(torch.empty_like(o, device="cpu").pin_memory())
+        e2e_sec, h2d, d2h = time_e2e(cabi, local, host, e2e_steps, min(opt.warmup, 3), barrier)
+        e2e_sec = max_over_ranks(e2e_sec)
+        e2e_ok = torch.equal(host[4].to(dev), o)
 
     out = {
         "metric": METRIC, "value": round(total_bytes / sec_max / 1e9, 2), "unit": UNIT, "n_gpus": world,
         "steps": opt.steps, "warmup": opt.warmup, "ms_per_step": round(sec_max * 1e3, 4),
         "us_per_call": round(sec_max * 1e6, 2), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16 in/out, fp32 accumulate", "data": "synthetic (seeded, decoding_attention_b200.synth)",
-        "config": {"workload": "GQA decode bf16, batch-sharded: 256 sequences per GPU, head_q 32, head_k 8, "
-                               "dim 128, seq_k ~ U[512,4096], N(0,1)*0.5, ALiBi off (BASELINE config 2)",
+        "config": {"workload": "GQA decode bf16, batch-sharded: %d sequences per GPU, head_q 32, head_k 8, "
+                               "dim 128, seq_k ~ U[512,4096], N(0,1)*0.5, ALiBi off (BASELINE config 2)" % opt.seqs,
                    "sequences": w.batch, "total_keys": w.total_k, "kv_bytes": int(total_bytes),
                    "l2": "inputs (%.2f GB per GPU) larger than the 126 MB L2" % (my_bytes / 1e9),
                    "num_splits": cabi.num_splits(args)},
@@ -387,7 +390,7 @@ def run_reference(opt):
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    w = synth.config_gqa_varlen(batch=SEQS_PER_GPU * world)
+    w = synth.config_gqa_varlen(batch=opt.seqs * world)
     budget = max(0.5, min(4.0, 150.0 / (opt.steps + opt.warmup)))
     kind, n, kv, timed = cpu_reference_sample(w, budget, threads)
     for _ in range(opt.warmup):
@@ -418,6 +421,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--seqs", type=int, default=SEQS_PER_GPU,
+                    help="sequences per GPU (256 = the benchmark workload; smaller values are for profiler captures)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extra", action="store_true", help="skip the other BASELINE configurations")
     ap.add_argument("--traffic", type=float, default=None,
