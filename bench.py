@@ -415,10 +415,33 @@ def run_reference(opt):
     print(json.dumps(out), flush=True)
 
 
+def run_profile_config(opt):
+    """A few calls of one configuration, nothing else: the command line that ncu captures wrap."""
+    from decoding_attention_b200 import cabi
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    make = synth.CONFIGS[opt.profile_config]
+    if opt.profile_batch is None:
+        w = make()
+    elif opt.profile_config == "long_mha":
+        w = make(seq_k=opt.profile_batch)
+    elif opt.profile_config == "mha_small":
+        w = make()
+    else:
+        w = make(batch=opt.profile_batch)
+    q, k, v, cu = w.make(dev)
+    o = torch.empty(w.batch, w.head_q, w.dim_v, dtype=w.dtype, device=dev)
+    args = make_call(cabi, w, q, k, v, cu, o)
+    sec, kern, launches = time_resident(cabi, args, opt.steps, opt.warmup, lambda: None)
+    print(json.dumps({"config": w.name, "kv_bytes": w.kv_bytes(), "us_per_call": round(sec * 1e6, 2),
+                      "main_kernel_us": round(kern * 1e6, 2), "kv_GBps": round(w.kv_bytes() / sec / 1e9, 1),
+                      "num_splits": cabi.num_splits(args), "launches": int(launches)}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seqs", type=int, default=SEQS_PER_GPU,
@@ -426,6 +449,9 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extra", action="store_true", help="skip the other BASELINE configurations")
+    ap.add_argument("--profile-config", default=None, choices=sorted(synth.CONFIGS),
+                    help="run only this BASELINE configuration for --steps calls on one GPU (for ncu captures)")
+    ap.add_argument("--profile-batch", type=int, default=None, help="batch (or seq_k for long_mha) of that run")
     ap.add_argument("--traffic", type=float, default=None,
                     help="DRAM bytes per launch of the dominant kernel from an ncu capture (see profiles/)")
     opt = ap.parse_args()
@@ -436,7 +462,9 @@ def main():
                 opt.traffic = json.load(f).get("da_split_kernel_gqa_bytes_per_launch_full_workload")
         except Exception:
             opt.traffic = None
-    if opt.impl == "reference":
+    if opt.profile_config:
+        run_profile_config(opt)
+    elif opt.impl == "reference":
         run_reference(opt)
     else:
         run_ours(opt)
