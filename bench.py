@@ -456,12 +456,11 @@ def main():
                     help="DRAM bytes per launch of the dominant kernel from an ncu capture (see profiles/)")
     opt = ap.parse_args()
     opt.warmup = max(opt.warmup, 3)
-    if opt.traffic is None:
-        try:
-            with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
-                opt.traffic = json.load(f).get("da_split_kernel_gqa_bytes_per_launch_full_workload")
-        except Exception:
-            opt.traffic = None
+    if opt.traffic is None and opt.seqs == SEQS_PER_GPU:
+        # dram__bytes_read.sum + dram__bytes_write.sum of one da_split_kernel launch, captured with ncu on
+        # the 32-sequence case (297.4 MB for 290.9 MB of KV) and scaled to the full workload by the keys
+        # read: profiles/da_split_kernel_gqa_bf16_d128.md.
+        opt.traffic = 2.480e9
     if opt.profile_config:
         run_profile_config(opt)
     elif opt.impl == "reference":
