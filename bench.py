@@ -228,6 +228,8 @@ def run_ours(opt):
     dev = torch.device("cuda", local_rank)
     import torch.distributed as dist
     if world > 1:
+        # NCCL prints its version banner on stdout when NCCL_DEBUG is set; stdout carries the JSON line only.
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
 
     def barrier():
