@@ -103,7 +103,7 @@ SplitVariantInfo variant_info(Shape s, int heads) {
         case Shape::kD128: return split_info_d128(heads);
         case Shape::kD256: return split_info_d256(heads);
         case Shape::kMla: return split_info_mla_simt(heads);
-        case Shape::kMlaTc: return split_info_mla_tc();
+        case Shape::kMlaTc: return getenv("DA_MLA_SINGLE") ? split_info_mla_tc() : split_info_mla_pair();
         default: return {0, 0, 0};
     }
 }
@@ -459,7 +459,12 @@ int da_decode_fwd(const da_decode_args_t *a) {
         case Shape::kD128: e = launch_split_d128(bf16, plan.heads, p, maps, stream); break;
         case Shape::kD256: e = launch_split_d256(bf16, plan.heads, p, maps, stream); break;
         case Shape::kMla: e = launch_split_mla_simt(bf16, plan.heads, p, maps, stream); break;
-        case Shape::kMlaTc: e = launch_mla_tc(bf16, p, maps.k, maps.v, stream); break;
+        case Shape::kMlaTc:
+            // Default: the cluster-pair kernel.  DA_MLA_SINGLE selects the older kernel whose two CTAs per
+            // key range do not cooperate (kept for A/B measurements).
+            e = getenv("DA_MLA_SINGLE") ? launch_mla_tc(bf16, p, maps.k, maps.v, stream)
+                                        : launch_mla_pair(bf16, p, maps.v, stream);
+            break;
         default: e = cudaErrorInvalidValue; break;
     }
     if (e != cudaSuccess) return fail(DA_ERR_CUDA, "split kernel launch: %s", cudaGetErrorString(e));

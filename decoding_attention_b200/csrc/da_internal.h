@@ -38,6 +38,10 @@ SplitVariantInfo split_info_mla_simt(int heads);
 cudaError_t launch_mla_tc(bool bf16, const SplitParams &p, const CUtensorMap &tm_q, const CUtensorMap &tm_k,
                           cudaStream_t s);
 SplitVariantInfo split_info_mla_tc();
+// Cluster-pair variant (da_mla_pair_sm100.cu): the two CTAs of a key range split the 576-long
+// contraction and the output columns and swap partial scores through distributed shared memory.
+cudaError_t launch_mla_pair(bool bf16, const SplitParams &p, const CUtensorMap &tm_k, cudaStream_t s);
+SplitVariantInfo split_info_mla_pair();
 
 // Merge of split / shard partials (da_merge.cu).  cu_seq_k and chunk_keys (both optional) limit a
 // row to the splits that cover keys; without them every part is read.
