@@ -96,6 +96,13 @@ int heads_per_cta(Shape s, int group) {
     return 1;
 }
 
+// Which tensor-core MLA kernel runs: the cluster-pair kernel (DA_MLA_PAIR=1) or the one whose two
+// CTAs per key range work independently (default until the pair kernel is the faster one).
+bool mla_pair_enabled() {
+    const char *e = getenv("DA_MLA_PAIR");
+    return e && e[0] == '1';
+}
+
 SplitVariantInfo variant_info(Shape s, int heads) {
     switch (s) {
         case Shape::kD64: return split_info_d64(heads);
@@ -103,7 +110,7 @@ SplitVariantInfo variant_info(Shape s, int heads) {
         case Shape::kD128: return split_info_d128(heads);
         case Shape::kD256: return split_info_d256(heads);
         case Shape::kMla: return split_info_mla_simt(heads);
-        case Shape::kMlaTc: return getenv("DA_MLA_SINGLE") ? split_info_mla_tc() : split_info_mla_pair();
+        case Shape::kMlaTc: return mla_pair_enabled() ? split_info_mla_pair() : split_info_mla_tc();
         default: return {0, 0, 0};
     }
 }
@@ -460,10 +467,8 @@ int da_decode_fwd(const da_decode_args_t *a) {
         case Shape::kD256: e = launch_split_d256(bf16, plan.heads, p, maps, stream); break;
         case Shape::kMla: e = launch_split_mla_simt(bf16, plan.heads, p, maps, stream); break;
         case Shape::kMlaTc:
-            // Default: the cluster-pair kernel.  DA_MLA_SINGLE selects the older kernel whose two CTAs per
-            // key range do not cooperate (kept for A/B measurements).
-            e = getenv("DA_MLA_SINGLE") ? launch_mla_tc(bf16, p, maps.k, maps.v, stream)
-                                        : launch_mla_pair(bf16, p, maps.v, stream);
+            e = mla_pair_enabled() ? launch_mla_pair(bf16, p, maps.v, stream)
+                                   : launch_mla_tc(bf16, p, maps.k, maps.v, stream);
             break;
         default: e = cudaErrorInvalidValue; break;
     }

@@ -60,6 +60,20 @@ static_assert(kColQ + kLocalBlocks * 32 <= kTmemCols, "TMEM budget");
 static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 constexpr float kRescaleThreshold = 8.0f;
 
+#ifdef DA_MLA_PROFILE
+// Development aid (not compiled into the shipped library): cycles CTA (0,0,0) spends in each step.
+__device__ long long g_mla_prof[64];
+#define PROF_DECL long long prof_t0 = 0, prof_acc[16] = {}; (void)prof_t0
+#define PROF_BEGIN() prof_t0 = clock64()
+#define PROF_END(slot) do { long long now_ = clock64(); prof_acc[(slot) & 15] += now_ - prof_t0; prof_t0 = now_; } while (0)
+#define PROF_FLUSH(base) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0) { for (int i_ = 0; i_ < 16; ++i_) g_mla_prof[(base) + i_] += prof_acc[i_]; } } while (0)
+#else
+#define PROF_DECL
+#define PROF_BEGIN()
+#define PROF_END(slot)
+#define PROF_FLUSH(base)
+#endif
+
 template <typename T>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 da_mla_pair_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_k) {
@@ -207,16 +221,22 @@ da_mla_pair_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_k
             tc_fence_after();
             issue_qk(0);
         }
+        PROF_DECL;
         for (int t = 0; t < n_tiles && ok; ++t) {
+            PROF_BEGIN();
             if (t + 1 < n_tiles) {
                 const int t1 = t + 1;
                 ok = mbar_wait(&k_full[t1 % kStages], (uint32_t)(t1 / kStages) & 1u, abort_flag);
+                PROF_END(10);
                 if (ok) ok = mbar_wait(s_empty, (uint32_t)t & 1u, abort_flag);  // S of tile t has been read out
+                PROF_END(11);
                 if (!ok) break;
                 tc_fence_after();
                 issue_qk(t1);
+                PROF_END(12);
             }
             ok = mbar_wait(&p_full[t & 1], (uint32_t)(t / 2) & 1u, abort_flag);
+            PROF_END(13);
             if (!ok) break;
             tc_fence_after();
             const int st = t % kStages;
@@ -229,7 +249,9 @@ da_mla_pair_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_k
             }
             umma_commit(&k_empty[st], leader);
             umma_commit(&pv_done[t & 1], leader);
+            PROF_END(14);
         }
+        PROF_FLUSH(0);
         __syncwarp();
     } else {
         // ------- exchange / softmax / epilogue: thread r <-> TMEM lane r <-> head r -------
@@ -237,10 +259,12 @@ da_mla_pair_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_k
         const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
         const uint32_t peer = rank ^ 1u;
         // Row r of the peer's exchange buffer and the peer's two exchange barriers, as cluster addresses.
-        const uint32_t x_row_remote = map_to_cta(smem_u32(x_s) + r * kXRowBytes, peer);
+        // Exchange buffer layout: 16-byte chunk c of row r at c * (128 * 16) + r * 16, so that one warp-wide
+        // store covers 512 contiguous bytes of the peer's shared memory and local reads are conflict-free.
+        const uint32_t x_row_remote = map_to_cta(smem_u32(x_s) + r * 16, peer);
         const uint32_t x_full_remote = map_to_cta(smem_u32(x_full), peer);
         const uint32_t x_free_remote = map_to_cta(smem_u32(x_free), peer);
-        const uint8_t *x_row_local = x_s + r * kXRowBytes;
+        const uint8_t *x_row_local = x_s + r * 16;
         const float slope2 = p.is_alibi ? exp2f(-8.0f * (float)(r + 1) / (float)p.head_q) * kLog2e : 0.0f;
         const int pos_shift = (p.kv_pos_offset ? p.kv_pos_offset[b] : 0) - ((p.kv_total_len ? p.kv_total_len[b] : len) - 1);
         float m_ref = -INFINITY, l = 0.0f;
@@ -263,10 +287,13 @@ da_mla_pair_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_k
             tc_fence_before();
             mbar_arrive(q_tmem);
         }
+        PROF_DECL;
         for (int t = 0; t < n_tiles; ++t) {
             const int key0 = k_begin + t * kTile;
             const int rows = min(kTile, k_end - key0);
+            PROF_BEGIN();
             ok = mbar_wait(s_full, (uint32_t)t & 1u, abort_flag);
+            PROF_END(16);
             if (!ok) break;
             tc_fence_after();
             float s[kTile];
@@ -279,25 +306,30 @@ da_mla_pair_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_k
             }
             tc_fence_before();
             mbar_arrive(s_empty);
+            PROF_END(17);
 
             // ---- swap partial rows with the peer and add ----
             if (t >= 1) {
                 ok = mbar_wait_cluster(x_free, (uint32_t)(t - 1) & 1u, abort_flag);  // peer consumed my last row
                 if (!ok) break;
             }
+            PROF_END(18);
 #pragma unroll
             for (int c = 0; c < kTile / 4; ++c) {
-                st_cluster_v4(x_row_remote + ((c ^ (r & 7)) << 4), s[4 * c], s[4 * c + 1], s[4 * c + 2], s[4 * c + 3]);
+                st_cluster_v4(x_row_remote + c * (kHeads * 16), s[4 * c], s[4 * c + 1], s[4 * c + 2], s[4 * c + 3]);
             }
             mbar_arrive_remote(x_full_remote);
+            PROF_END(19);
             ok = mbar_wait_cluster(x_full, (uint32_t)t & 1u, abort_flag);
+            PROF_END(20);
             if (!ok) break;
 #pragma unroll
             for (int c = 0; c < kTile / 4; ++c) {
-                const float4 o4 = *reinterpret_cast<const float4 *>(x_row_local + ((c ^ (r & 7)) << 4));
+                const float4 o4 = *reinterpret_cast<const float4 *>(x_row_local + c * (kHeads * 16));
                 s[4 * c] += o4.x, s[4 * c + 1] += o4.y, s[4 * c + 2] += o4.z, s[4 * c + 3] += o4.w;
             }
             mbar_arrive_remote(x_free_remote);
+            PROF_END(21);
 
             float mx = -INFINITY;
 #pragma unroll
@@ -313,11 +345,13 @@ da_mla_pair_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_k
                 m_ref = mx;
                 l *= alpha;
             }
+            PROF_END(22);
             if (t >= 2) {
                 // The P buffer of this tile was last read by the P.V of tile t-2.
                 ok = mbar_wait(&pv_done[t & 1], ((uint32_t)(t / 2) & 1u) ^ 1u, abort_flag);
                 if (!ok) break;
             }
+            PROF_END(23);
             if (t >= 1 && __any_sync(0xffffffffu, raise)) {
                 // Rare: the reference max of some row in this warp moved.  O must be idle (P.V of tile
                 // t-1 complete) while its rows are rescaled in place.
@@ -358,7 +392,12 @@ da_mla_pair_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_k
             fence_proxy_async();
             tc_fence_before();
             mbar_arrive(&p_full[t & 1]);
+            PROF_END(24);
+#ifdef DA_MLA_PROFILE
+            if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0) g_mla_prof[33] += 1;
+#endif
         }
+        if (warp == 0) PROF_FLUSH(16);
         if (ok) ok = mbar_wait(&pv_done[(n_tiles - 1) & 1], (uint32_t)((n_tiles - 1) / 2) & 1u, abort_flag);
         if (ok) {
             tc_fence_after();
@@ -418,6 +457,17 @@ da_mla_pair_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_k
 }
 
 }  // namespace
+
+#ifdef DA_MLA_PROFILE
+extern "C" void da_debug_mla_prof(long long *out, int reset) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, g_mla_prof, sizeof(long long) * 64);
+    if (reset) {
+        long long z[64] = {};
+        cudaMemcpyToSymbol(g_mla_prof, z, sizeof(z));
+    }
+}
+#endif
 
 SplitVariantInfo split_info_mla_pair() { return {kTile, kHeads, 1}; }
 
