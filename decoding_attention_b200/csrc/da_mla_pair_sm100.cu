@@ -37,21 +37,23 @@ constexpr int kDim = 576;
 constexpr int kDimV = 512;
 constexpr int kHalfV = 256;                           // output columns per CTA
 constexpr int kTile = 64;                             // keys per tile
-constexpr int kStages = 4;                            // K tiles in flight per CTA
+constexpr int kStages = 3;                            // K tiles in flight per CTA
 constexpr int kLocalBlocks = 5;                       // 64-wide column blocks a CTA streams per key
 constexpr int kKBlockBytes = kTile * 128;             // [64 keys x 64 dims], 128-byte swizzle
 constexpr int kKStageBytes = kLocalBlocks * kKBlockBytes;
 constexpr int kPBytes = kHeads * kTile * 2;           // P tile, core-matrix (no swizzle) K-major
 constexpr int kXRowBytes = kTile * 4;                 // one row of a partial S tile (fp32)
-constexpr int kXBytes = kHeads * kXRowBytes;          // exchange buffer, written by the peer CTA
+constexpr int kXBytes = kHeads * kXRowBytes;          // receive buffer (written by the peer's bulk copy) and send staging
 constexpr int kOffK = 0;
 constexpr int kOffP = kOffK + kStages * kKStageBytes;
-constexpr int kOffX = kOffP + 2 * kPBytes;
-constexpr int kOffBar = kOffX + kXBytes;
-// q_tmem, k_full/k_empty[kStages], s_full, s_empty, p_full[2], pv_done[2], x_full, x_free
-constexpr int kNumBars = 1 + 2 * kStages + 2 + 2 + 2 + 2;
+constexpr int kOffX = kOffP + 2 * kPBytes;            // peer's partial S lands here; the full S is formed in place
+constexpr int kOffY = kOffX + kXBytes;                // this CTA's partial S, source of the copy to the peer
+constexpr int kOffBar = kOffY + kXBytes;
+// q_tmem, k_full/k_empty[kStages], s_full, s_empty, p_full[2], pv_done[2], x_full, x_free, s_ready
+constexpr int kNumBars = 1 + 2 * kStages + 2 + 2 + 2 + 3;
 constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16 + 1024;  // + tmem slot/abort flag + alignment slack
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;   // warps 0-3 softmax, 4-7 exchange, 8 TMA producer, 9 MMA issuer
+constexpr int kProducerWarp = 8, kMmaWarp = 9;
 constexpr int kTmemCols = 512;
 constexpr int kColS = 0;      // 64 columns
 constexpr int kColO = 64;     // 256 columns
@@ -108,6 +110,7 @@ da_mla_pair_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_k
     uint8_t *k_s = smem + kOffK;
     uint8_t *p_s = smem + kOffP;
     uint8_t *x_s = smem + kOffX;
+    uint8_t *y_s = smem + kOffY;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBar);
     uint64_t *q_tmem = bars;
     uint64_t *k_full = bars + 1;
@@ -118,6 +121,7 @@ da_mla_pair_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_k
     uint64_t *pv_done = p_full + 2;
     uint64_t *x_full = pv_done + 2;   // the peer has written its partial S of a tile into x_s
     uint64_t *x_free = x_full + 1;    // the peer has read what this CTA wrote into the peer's x_s
+    uint64_t *s_ready = x_free + 1;   // the full S of a tile is in x_s
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kNumBars);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
@@ -133,12 +137,13 @@ da_mla_pair_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_k
             mbar_init(&p_full[s], kHeads);
             mbar_init(&pv_done[s], 1);
         }
-        mbar_init(x_full, kHeads);
-        mbar_init(x_free, kHeads);
+        mbar_init(x_full, 1);       // one arrive.expect_tx from the peer per tile, then the copy's bytes
+        mbar_init(x_free, 1);       // one remote arrival per tile (remote arrivals are expensive: keep them few)
+        mbar_init(s_ready, kHeads);
         *abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == 5) tmem_alloc(tmem_slot, kTmemCols);
+    if (warp == kMmaWarp) tmem_alloc(tmem_slot, kTmemCols);
     tc_fence_before();
     __syncthreads();
     cluster_sync_all();  // the peer's barriers exist before anybody arrives on them remotely
@@ -152,7 +157,7 @@ da_mla_pair_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_k
     const int qk_begin = (int)rank;          // local blocks [qk_begin, 5) enter S (CTA 1 skips block 4)
     bool ok = true;
 
-    if (warp == 4) {
+    if (warp == kProducerWarp) {
         // ---------------- TMA producer ----------------
         if (lane == 0) tma_prefetch_desc(&tm_k);
         const T *k_g = reinterpret_cast<const T *>(p.k) + first_block * 64;
@@ -189,7 +194,7 @@ da_mla_pair_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_k
             }
             __syncwarp();
         }
-    } else if (warp == 5) {
+    } else if (warp == kMmaWarp) {
         // ---------------- MMA issuer ----------------
         const uint32_t leader = elect_one();
         const uint32_t k_addr = smem_u32(k_s), p_addr = smem_u32(p_s);
@@ -253,21 +258,20 @@ da_mla_pair_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_k
         }
         PROF_FLUSH(0);
         __syncwarp();
-    } else {
-        // ------- exchange / softmax / epilogue: thread r <-> TMEM lane r <-> head r -------
-        const int r = tid;
-        const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+    } else if (warp >= 4) {
+        // ------- exchange warps: thread (tid - 128) <-> TMEM lane r <-> head r -------
+        // Per tile: read this CTA's partial S row from TMEM, stage it, one bulk copy ships the whole
+        // 32 KB tile into the peer's receive buffer; when the peer's tile has landed here, add the own
+        // row in place: x_s then holds the full S for the softmax warps.
+        const int r = tid - 128;
+        const uint32_t lane_base = tmem_base + ((uint32_t)((warp - 4) * 32) << 16);
         const uint32_t peer = rank ^ 1u;
-        // Row r of the peer's exchange buffer and the peer's two exchange barriers, as cluster addresses.
-        // Exchange buffer layout: 16-byte chunk c of row r at c * (128 * 16) + r * 16, so that one warp-wide
-        // store covers 512 contiguous bytes of the peer's shared memory and local reads are conflict-free.
-        const uint32_t x_row_remote = map_to_cta(smem_u32(x_s) + r * 16, peer);
+        const uint32_t x_remote = map_to_cta(smem_u32(x_s), peer);
         const uint32_t x_full_remote = map_to_cta(smem_u32(x_full), peer);
-        const uint32_t x_free_remote = map_to_cta(smem_u32(x_free), peer);
-        const uint8_t *x_row_local = x_s + r * 16;
-        const float slope2 = p.is_alibi ? exp2f(-8.0f * (float)(r + 1) / (float)p.head_q) * kLog2e : 0.0f;
-        const int pos_shift = (p.kv_pos_offset ? p.kv_pos_offset[b] : 0) - ((p.kv_total_len ? p.kv_total_len[b] : len) - 1);
-        float m_ref = -INFINITY, l = 0.0f;
+        // 16-byte chunk c of row r sits at c * (128 * 16) + r * 16 in both buffers: warp-wide accesses
+        // are contiguous and conflict-free.
+        uint8_t *y_row = y_s + r * 16;
+        uint8_t *x_row = x_s + r * 16;
         uint32_t buf[32];
         {
             // This CTA's share of head r's query (CTA 0: dims 0..319, CTA 1: dims 320..575) goes to TMEM
@@ -289,48 +293,88 @@ da_mla_pair_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_k
         }
         PROF_DECL;
         for (int t = 0; t < n_tiles; ++t) {
+            PROF_BEGIN();
+            ok = __all_sync(0xffffffffu, mbar_wait(s_full, (uint32_t)t & 1u, abort_flag));
+            PROF_END(0);
+            float s[kTile];
+            if (ok) {
+                tc_fence_after();
+#pragma unroll
+                for (int c0 = 0; c0 < kTile; c0 += 32) {
+                    tmem_ld32(lane_base + kColS + c0, buf);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) s[c0 + j] = __uint_as_float(buf[j]);
+                }
+                tc_fence_before();
+                mbar_arrive(s_empty);
+            }
+            PROF_END(1);
+            // The peer has read tile t-1 out of its receive buffer, so the copy that fed it is over
+            // and the staging buffer may be rewritten.
+            if (ok && t >= 1) ok = mbar_wait_cluster(x_free, (uint32_t)(t - 1) & 1u, abort_flag);
+            PROF_END(2);
+            if (ok) {
+#pragma unroll
+                for (int c = 0; c < kTile / 4; ++c) {
+                    *reinterpret_cast<float4 *>(y_row + c * (kHeads * 16)) =
+                        make_float4(s[4 * c], s[4 * c + 1], s[4 * c + 2], s[4 * c + 3]);
+                }
+                fence_proxy_async();
+            }
+            // Every exchange thread reaches this barrier, also after a wait has run out somewhere
+            // (the abort flag then ends the loop for all of them just behind it).
+            named_bar_sync(2, 128);
+            if (*abort_flag) {
+                ok = false;
+                break;
+            }
+            if (r == 0) {
+                mbar_arrive_expect_tx_remote(x_full_remote, kXBytes);
+                bulk_copy_s2peer(x_remote, y_s, kXBytes, x_full_remote);
+            }
+            PROF_END(3);
+            ok = mbar_wait_cluster(x_full, (uint32_t)t & 1u, abort_flag);
+            PROF_END(4);
+            if (!ok) break;
+#pragma unroll
+            for (int c = 0; c < kTile / 4; ++c) {
+                float4 *px = reinterpret_cast<float4 *>(x_row + c * (kHeads * 16));
+                float4 o4 = *px;
+                o4.x += s[4 * c], o4.y += s[4 * c + 1], o4.z += s[4 * c + 2], o4.w += s[4 * c + 3];
+                *px = o4;
+            }
+            mbar_arrive(s_ready);
+            PROF_END(5);
+        }
+        PROF_FLUSH(32);
+    } else {
+        // ------- softmax / epilogue warps: thread r <-> TMEM lane r <-> head r -------
+        const int r = tid;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+        const uint32_t x_free_remote = map_to_cta(smem_u32(x_free), rank ^ 1u);
+        const uint8_t *x_row = x_s + r * 16;
+        const float slope2 = p.is_alibi ? exp2f(-8.0f * (float)(r + 1) / (float)p.head_q) * kLog2e : 0.0f;
+        const int pos_shift = (p.kv_pos_offset ? p.kv_pos_offset[b] : 0) - ((p.kv_total_len ? p.kv_total_len[b] : len) - 1);
+        float m_ref = -INFINITY, l = 0.0f;
+        uint32_t buf[32];
+        PROF_DECL;
+        for (int t = 0; t < n_tiles; ++t) {
             const int key0 = k_begin + t * kTile;
             const int rows = min(kTile, k_end - key0);
             PROF_BEGIN();
-            ok = mbar_wait(s_full, (uint32_t)t & 1u, abort_flag);
+            ok = mbar_wait(s_ready, (uint32_t)t & 1u, abort_flag);
             PROF_END(16);
             if (!ok) break;
-            tc_fence_after();
             float s[kTile];
 #pragma unroll
-            for (int c0 = 0; c0 < kTile; c0 += 32) {
-                tmem_ld32(lane_base + kColS + c0, buf);
-                tmem_wait_ld();
-#pragma unroll
-                for (int j = 0; j < 32; ++j) s[c0 + j] = __uint_as_float(buf[j]);
-            }
-            tc_fence_before();
-            mbar_arrive(s_empty);
-            PROF_END(17);
-
-            // ---- swap partial rows with the peer and add ----
-            if (t >= 1) {
-                ok = mbar_wait_cluster(x_free, (uint32_t)(t - 1) & 1u, abort_flag);  // peer consumed my last row
-                if (!ok) break;
-            }
-            PROF_END(18);
-#pragma unroll
             for (int c = 0; c < kTile / 4; ++c) {
-                st_cluster_v4(x_row_remote + c * (kHeads * 16), s[4 * c], s[4 * c + 1], s[4 * c + 2], s[4 * c + 3]);
+                const float4 o4 = *reinterpret_cast<const float4 *>(x_row + c * (kHeads * 16));
+                s[4 * c] = o4.x, s[4 * c + 1] = o4.y, s[4 * c + 2] = o4.z, s[4 * c + 3] = o4.w;
             }
-            mbar_arrive_remote(x_full_remote);
-            PROF_END(19);
-            ok = mbar_wait_cluster(x_full, (uint32_t)t & 1u, abort_flag);
-            PROF_END(20);
-            if (!ok) break;
-#pragma unroll
-            for (int c = 0; c < kTile / 4; ++c) {
-                const float4 o4 = *reinterpret_cast<const float4 *>(x_row_local + c * (kHeads * 16));
-                s[4 * c] += o4.x, s[4 * c + 1] += o4.y, s[4 * c + 2] += o4.z, s[4 * c + 3] += o4.w;
-            }
-            mbar_arrive_remote(x_free_remote);
+            named_bar_sync(3, 128);             // all 128 rows have been read ...
+            if (r == 0) mbar_arrive_remote(x_free_remote);  // ... the peer may send its next tile
             PROF_END(21);
-
             float mx = -INFINITY;
 #pragma unroll
             for (int j = 0; j < kTile; ++j) {
@@ -394,7 +438,7 @@ da_mla_pair_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_k
             mbar_arrive(&p_full[t & 1]);
             PROF_END(24);
 #ifdef DA_MLA_PROFILE
-            if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0) g_mla_prof[33] += 1;
+            if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0) g_mla_prof[63] += 1;
 #endif
         }
         if (warp == 0) PROF_FLUSH(16);
@@ -450,7 +494,7 @@ da_mla_pair_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_k
     // The peer may still be writing into this CTA's exchange buffer or arriving on its barriers:
     // nobody leaves (and no shared memory is released) before both CTAs are here.
     cluster_sync_all();
-    if (warp == 5) {
+    if (warp == kMmaWarp) {
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
     }

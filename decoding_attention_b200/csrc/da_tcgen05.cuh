@@ -125,6 +125,20 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, float a, fl
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_bar_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar_addr) : "memory");
 }
+// one arrival plus `bytes` of expected transfer on an mbarrier of another CTA
+__device__ __forceinline__ void mbar_arrive_expect_tx_remote(uint32_t cluster_bar_addr, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_bar_addr),
+                 "r"(bytes)
+                 : "memory");
+}
+// bulk copy from this CTA's shared memory into another CTA's, bytes counted on an mbarrier over there
+__device__ __forceinline__ void bulk_copy_s2peer(uint32_t dst_cluster_addr, const void *src_smem, uint32_t bytes,
+                                                 uint32_t cluster_bar_addr) {
+    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     dst_cluster_addr),
+                 "r"(smem_u32(src_smem)), "r"(bytes), "r"(cluster_bar_addr)
+                 : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(

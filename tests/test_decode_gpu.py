@@ -64,6 +64,18 @@ def test_reference_grid_mla(native_lib, oracle, hq, b, s, dt):
     check(native_lib, oracle, w)
 
 
+@pytest.mark.parametrize("lens", [[64], [33], [1], [700, 0, 129], [2100]])
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+def test_mla_cluster_pair_kernel(native_lib, oracle, monkeypatch, lens, dt):
+    """The opt-in MLA kernel whose two CTAs per key range form a cluster, split the 576-long contraction
+    and swap partial scores through distributed shared memory (DA_MLA_PAIR=1)."""
+    monkeypatch.setenv("DA_MLA_PAIR", "1")
+    w = synth.Workload(f"mla_pair_{lens}", dt, 128, 1, 576, 512, lens, is_alibi=(len(lens) > 1), dist="normal",
+                       scale=0.3, mla=True, seed=23)
+    check(native_lib, oracle, w)
+    check(native_lib, oracle, w, num_splits=3)
+
+
 @pytest.mark.parametrize("lens", [[1], [2], [7], [63], [64], [65], [127, 129], [0, 5], [5, 0, 0, 300], [1000, 3, 64]])
 @pytest.mark.parametrize("splits", [0, 1, 3])
 def test_edges_varlen_and_splits(native_lib, oracle, lens, splits):
