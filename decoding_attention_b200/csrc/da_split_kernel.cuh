@@ -56,23 +56,36 @@ struct SplitCfg {
     static_assert(!MLA || DV <= D, "latent-KV: V is a prefix of the K row");
 };
 
+constexpr int ilog2(int x) { return x <= 1 ? 0 : 1 + ilog2(x / 2); }
+
 // Sum v[] over the LANES lanes of a group.  While more than one value is left each step also
 // halves the number of values a lane keeps (reduce-scatter), so NV values cost about NV shuffles
 // instead of NV*log2(LANES).  Afterwards lane c holds the totals of indices (c/REP)*RV .. +RV-1.
-template <int NV, int LANES>
+// v[] is indexed (key slot, head) = slot*G + head.  A step that halves over a key-slot bit needs no
+// selects: the lanes with that lane bit set have walked their key slots in an order with that slot
+// bit flipped (key_slot_permutation), so every lane keeps its lower register half and sends the
+// upper one.  Steps over head bits select per lane.
+template <int NV, int LANES, int G>
 __device__ __forceinline__ void group_reduce_scatter(float (&v)[NV], int lane_in_group) {
     int cnt = NV;
 #pragma unroll
     for (int off = LANES / 2; off >= 1; off >>= 1) {
         if (cnt > 1) {
             const int half = cnt / 2;
-            const bool upper = (lane_in_group & off) != 0;
+            if (half >= G) {  // a key-slot bit
 #pragma unroll
-            for (int j = 0; j < NV / 2; ++j) {
-                if (j < half) {
-                    const float send = upper ? v[j] : v[j + half];
-                    const float keep = upper ? v[j + half] : v[j];
-                    v[j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                for (int j = 0; j < NV / 2; ++j) {
+                    if (j < half) v[j] += __shfl_xor_sync(0xffffffffu, v[j + half], off);
+                }
+            } else {
+                const bool upper = (lane_in_group & off) != 0;
+#pragma unroll
+                for (int j = 0; j < NV / 2; ++j) {
+                    if (j < half) {
+                        const float send = upper ? v[j] : v[j + half];
+                        const float keep = upper ? v[j + half] : v[j];
+                        v[j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                    }
                 }
             }
             cnt = half;
@@ -80,6 +93,20 @@ __device__ __forceinline__ void group_reduce_scatter(float (&v)[NV], int lane_in
             v[0] += __shfl_xor_sync(0xffffffffu, v[0], off);
         }
     }
+}
+// XOR mask a lane applies to its key-slot index i (register slot i holds key slot i ^ mask).
+template <int NV, int LANES, int G>
+__device__ __forceinline__ int key_slot_permutation(int lane_in_group) {
+    int perm = 0, cnt = NV;
+#pragma unroll
+    for (int off = LANES / 2; off >= 1; off >>= 1) {
+        if (cnt > 1) {
+            const int half = cnt / 2;
+            if (half >= G && (lane_in_group & off)) perm |= half / G;
+            cnt = half;
+        }
+    }
+    return perm;
 }
 
 // arr[idx] for a run-time idx without sending the array to local memory.
@@ -90,6 +117,8 @@ __device__ __forceinline__ float pick(const float (&arr)[N], int idx) {
     for (int i = 1; i < N; ++i) x = (idx == i) ? arr[i] : x;
     return x;
 }
+
+constexpr float kLazyRaise = 8.0f;
 
 template <class C>
 __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const SplitParams p,
@@ -237,6 +266,7 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
 
     // Which (key slot, head) pairs this lane owns after the reduce-scatter, and their ALiBi slopes.
     const int j0 = (c / REP) * RV;
+    const int slot_perm = key_slot_permutation<NV, LANES, G>(c);
     float slope2[RV];  // slope * log2(e)
 #pragma unroll
     for (int r = 0; r < RV; ++r) {
@@ -275,7 +305,7 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
         const uint8_t *kt = ks + st * C::K_TILE_BYTES;
 #pragma unroll
         for (int i = 0; i < KPT; ++i) {
-            const int kl = i * NG + gi;  // key slot in the tile
+            const int kl = (i ^ slot_perm) * NG + gi;  // key slot in the tile (register slot i)
 #pragma unroll
             for (int n = 0; n < NCH; ++n) {
                 const uint4 raw = *reinterpret_cast<const uint4 *>(kt + kl * C::K_ROW_BYTES + (c + n * LANES) * 16);
@@ -292,7 +322,7 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty_k[st]);
         }
-        group_reduce_scatter<NV, LANES>(sacc, c);
+        group_reduce_scatter<NV, LANES, G>(sacc, c);
 
         // ---- scale, bias, mask; publish the scores of the group ----
 #pragma unroll
@@ -303,42 +333,45 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
             float s = sacc[r] * p.scale_log2 + slope2[r] * (float)(pos + pos_shift);
             sacc[r] = (kl < rows) ? s : neg_inf;
         }
-        __syncwarp();  // the previous tile's readers of p_grp are done
+        // ---- online softmax with a lazy reference: m_run is raised (and O, l rescaled) only when some
+        // score of the group exceeds it by more than 2^kLazyRaise; otherwise p = 2^(s - m_run) <= 2^kLazyRaise.
+        bool raise = false;
 #pragma unroll
-        for (int r = 0; r < RV; ++r) p_grp[j0 + r] = sacc[r];
-        __syncwarp();
-
-        // ---- online softmax: new running max per head, rescale factors ----
-        float m_new[G], alpha[G];
+        for (int r = 0; r < RV; ++r) raise |= sacc[r] > pick<G>(m_run, (j0 + r) % G) + kLazyRaise;
+        const unsigned grp_mask = LANES == 32 ? 0xffffffffu : (((1u << LANES) - 1u) << ((lane / LANES) * LANES));
+        // the ballot also orders this tile's writes to p_grp after the previous tile's reads
+        const bool grp_raise = (__ballot_sync(0xffffffffu, raise) & grp_mask) != 0u;
+        if (grp_raise) {
 #pragma unroll
-        for (int g = 0; g < G; ++g) m_new[g] = m_run[g];
+            for (int r = 0; r < RV; ++r) p_grp[j0 + r] = sacc[r];
+            __syncwarp(grp_mask);
+            float alpha[G];
 #pragma unroll
-        for (int i = 0; i < KPT; ++i) {
+            for (int g = 0; g < G; ++g) {
+                float m_new = m_run[g];
 #pragma unroll
-            for (int g = 0; g < G; ++g) m_new[g] = fmaxf(m_new[g], p_grp[i * G + g]);
+                for (int i = 0; i < KPT; ++i) m_new = fmaxf(m_new, p_grp[i * G + g]);
+                const float m_use = (m_new == neg_inf) ? 0.0f : m_new;
+                alpha[g] = exp2f(m_run[g] - m_use);
+                m_run[g] = m_new;
+            }
+            __syncwarp(grp_mask);  // everybody of the group has read the raw scores
+#pragma unroll
+            for (int r = 0; r < RV; ++r) l_lane[r] *= pick<G>(alpha, (j0 + r) % G);
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+#pragma unroll
+                for (int n = 0; n < NCHV; ++n)
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) oacc[g][n][e] *= alpha[g];
+            }
         }
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            const float m_use = (m_new[g] == neg_inf) ? 0.0f : m_new[g];
-            alpha[g] = exp2f(m_run[g] - m_use);
-            m_run[g] = m_new[g];
-        }
-        __syncwarp();  // everybody has read the raw scores
 #pragma unroll
         for (int r = 0; r < RV; ++r) {
-            const int g = (j0 + r) % G;
-            const float m_g = pick<G>(m_new, g);
-            const float m_use = (m_g == neg_inf) ? 0.0f : m_g;
-            const float pr = exp2f(sacc[r] - m_use);
-            l_lane[r] = l_lane[r] * pick<G>(alpha, g) + pr;
+            const float m_g = pick<G>(m_run, (j0 + r) % G);
+            const float pr = exp2f(sacc[r] - ((m_g == neg_inf) ? 0.0f : m_g));
+            l_lane[r] += pr;
             p_grp[j0 + r] = pr;
-        }
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-#pragma unroll
-            for (int n = 0; n < NCHV; ++n)
-#pragma unroll
-                for (int e = 0; e < 8; ++e) oacc[g][n][e] *= alpha[g];
         }
         __syncwarp();
 
