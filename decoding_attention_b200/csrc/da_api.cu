@@ -62,7 +62,7 @@ int device_state(DeviceState **out) {
     return DA_OK;
 }
 
-enum class Shape { kD64, kD96, kD128, kD256, kMla, kMlaTc, kNone };
+enum class Shape { kD64, kD96, kD128, kD256, kMla, kMlaTc, kD128Tc, kNone };
 
 Shape shape_of(int64_t dim, int64_t dim_v, bool has_v) {
     if (has_v) {
@@ -83,8 +83,19 @@ bool mla_on_tensor_cores(const da_decode_args_t &a) {
            !getenv("DA_MLA_SIMT");
 }
 
+// Head dim 128 with 8..128 query heads per KV head runs on the tensor cores: at that many flops per
+// KV byte the CUDA-core kernel is bound by instruction issue, not by HBM.  DA_GQA_SIMT=1 keeps it on
+// the CUDA-core kernel (for comparisons).
+bool gqa_on_tensor_cores(const da_decode_args_t &a) {
+    if (!a.v || a.dim != 128 || a.dim_v != 128) return false;
+    const int64_t group = a.head_q / a.head_k;
+    const char *e = getenv("DA_GQA_SIMT");
+    return group >= 8 && group <= 128 && !(e && e[0] == '1');
+}
+
 int heads_per_cta(Shape s, int group) {
     if (s == Shape::kMla) return 1;
+    if (s == Shape::kD128Tc) return group;
     if (s == Shape::kMlaTc) return 128;
     const char *env = getenv("DA_HEADS_PER_CTA");
     if (env) {
@@ -110,6 +121,7 @@ SplitVariantInfo variant_info(Shape s, int heads) {
         case Shape::kD128: return split_info_d128(heads);
         case Shape::kD256: return split_info_d256(heads);
         case Shape::kMla: return split_info_mla_simt(heads);
+        case Shape::kD128Tc: return split_info_gqa_tc();
         case Shape::kMlaTc: return mla_pair_enabled() ? split_info_mla_pair() : split_info_mla_tc();
         default: return {0, 0, 0};
     }
@@ -231,6 +243,7 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
                     (long long)a.dim, (long long)a.dim_v, has_v ? "given" : "NULL");
     }
     if (shape == Shape::kMla && mla_on_tensor_cores(a)) shape = Shape::kMlaTc;
+    if (shape == Shape::kD128 && gqa_on_tensor_cores(a)) shape = Shape::kD128Tc;
     const int group = (int)(a.head_q / a.head_k);
     const int heads = heads_per_cta(shape, group);
     const SplitVariantInfo info = variant_info(shape, heads);
@@ -241,7 +254,7 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
     const int64_t tiles_per_unit = (max_len + tile - 1) / tile;
 
     // A tensor-core MLA CTA first stages 144 KB of Q: give it at least 256 keys to amortise that.
-    const int kMinTiles = 4, kWaves = shape == Shape::kMlaTc ? 2 : 4;
+    const int kMinTiles = 4, kWaves = 4;
     const int kMaxTiles = getenv("DA_MAX_TILES") ? atoi(getenv("DA_MAX_TILES")) : 32;
     int64_t splits;
     const char *env = getenv("DA_NUM_SPLITS");
@@ -249,9 +262,9 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
         splits = a.num_splits;
     } else if (env && atoi(env) > 0) {
         splits = atoi(env);
-    } else if (shape == Shape::kMlaTc) {
+    } else if (shape == Shape::kMlaTc || shape == Shape::kD128Tc) {
         // One CTA per SM and long-running CTAs: pick the split count whose CTA total fills whole
-        // waves best (a slight penalty on more splits: more partials to merge).
+        // waves best, weighed against the fixed cost of every extra CTA.
         const int64_t slots = sm_count;
         double best = -1.0;
         splits = 1;
@@ -262,7 +275,9 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
             if (s_eff != s) continue;
             const int64_t total = units * s_eff;
             const int64_t waves = (total + slots - 1) / slots;
-            const double score = (double)total / (double)(waves * slots) - 0.004 * (double)s;
+            // wave efficiency x the share of a CTA's life spent on tiles (a CTA costs about six tiles'
+            // worth of set-up: barrier/TMEM set-up, Q staging, pipeline fill, epilogue)
+            const double score = (double)total / (double)(waves * slots) * (double)tpc / (double)(tpc + 6);
             if (score > best) {
                 best = score;
                 splits = s;
@@ -437,7 +452,27 @@ int da_decode_fwd(const da_decode_args_t *a) {
     memset(&maps, 0, sizeof(maps));
     // Tiled TMA needs a global stride that is a multiple of 16 bytes (checked above: 8 elements) and
     // a box of at most 256 elements per dimension; the latent-KV rows (576) keep the row-wise path.
-    p.use_tmap = (plan.shape != Shape::kMla) && (plan.shape != Shape::kMlaTc) && !getenv("DA_NO_TMAP");
+    p.use_tmap = (plan.shape != Shape::kMla) && (plan.shape != Shape::kMlaTc) && (plan.shape != Shape::kD128Tc) &&
+                 !getenv("DA_NO_TMAP");
+    CUtensorMap tm_q;
+    memset(&tm_q, 0, sizeof(tm_q));
+    if (plan.shape == Shape::kD128Tc) {
+        // q as [batch][head_q][128] in boxes {64, min(128, head_q), 1}; K and V as [rows][head_k][128] in
+        // boxes {64, 1, tile}: all 128-byte-swizzled, the layout the UMMA descriptors name.
+        const uint64_t qd[3] = {128, (uint64_t)a->head_q, (uint64_t)a->batch};
+        const uint64_t qs[2] = {128 * 2, (uint64_t)p.q_row_stride * 2};
+        const uint32_t qb[3] = {64, (uint32_t)(a->head_q < 128 ? a->head_q : 128), 1};
+        rc = make_tensor_map(p.q, 3, qd, qs, qb, true, bf16, &tm_q);
+        if (rc != DA_OK) return rc;
+        const uint64_t kd[3] = {128, (uint64_t)a->head_k, kMapRows};
+        const uint64_t ks[2] = {128 * 2, (uint64_t)p.k_row_stride * 2};
+        const uint64_t vs[2] = {128 * 2, (uint64_t)p.v_row_stride * 2};
+        const uint32_t kb[3] = {64, 1, (uint32_t)plan.tile_keys};
+        rc = make_tensor_map(p.k, 3, kd, ks, kb, true, bf16, &maps.k);
+        if (rc != DA_OK) return rc;
+        rc = make_tensor_map(p.v, 3, kd, vs, kb, true, bf16, &maps.v);
+        if (rc != DA_OK) return rc;
+    }
     if (plan.shape == Shape::kMlaTc) {
         // q as [batch][128][576] in boxes {64, 128, 1}; the latent cache as [rows][576] in boxes
         // {64, tile}; both land 128-byte-swizzled, the layout the UMMA descriptors name.
@@ -466,6 +501,7 @@ int da_decode_fwd(const da_decode_args_t *a) {
         case Shape::kD128: e = launch_split_d128(bf16, plan.heads, p, maps, stream); break;
         case Shape::kD256: e = launch_split_d256(bf16, plan.heads, p, maps, stream); break;
         case Shape::kMla: e = launch_split_mla_simt(bf16, plan.heads, p, maps, stream); break;
+        case Shape::kD128Tc: e = launch_gqa_tc(bf16, p, tm_q, maps.k, maps.v, stream); break;
         case Shape::kMlaTc:
             e = mla_pair_enabled() ? launch_mla_pair(bf16, p, maps.v, stream)
                                    : launch_mla_tc(bf16, p, maps.k, maps.v, stream);

@@ -1,0 +1,396 @@
+// Grouped-query / multi-query decode attention (head dim 128) on the sm_100a tensor cores, for KV
+// heads that serve 8..128 query heads.
+//
+// With G query heads per KV head the path does 2*G flops per KV byte.  On CUDA cores
+// (da_split_kernel.cuh, at most 4 heads per CTA) G = 32 is bound by instruction issue at about a
+// tenth of the HBM rate -- the reference has the same shape of problem, one CTA per query head
+// (csrc/kernel/decoding_attn/decoding_fwd_hd128_hdv128.cu:9-25).  Here the G heads of one KV head are
+// rows of an M = 128 tcgen05.mma tile (rows >= G compute garbage that nobody reads; the tensor
+// pipe is otherwise idle), so every K/V byte is read once and used for all G heads:
+//     S[128 x 64]   = Q[128 x 128] . K_tile[64 x 128]^T      (8 MMAs  M128 N64  K16, operands K-major)
+//     O[128 x 128] += P[128 x 64]  . V_tile[64 x 128]        (4 MMAs  M128 N128 K16, V MN-major)
+// One CTA = (sequence, KV head, key range).  Q, K and V tiles arrive by tiled TMA copies with the
+// 128-byte swizzle; S (two buffers) and O live in tensor memory (256 columns).
+// Warps 0-3 = softmax/epilogue (thread r <-> TMEM lane r <-> head h0 + r; warps whose rows are all
+// >= G stay out), warp 4 = TMA producer, warp 5 = TMEM allocation + MMA issue.  Lazy reference
+// max as in the MLA kernel.  Every wait is bounded.
+#include <type_traits>
+
+#include "da_internal.h"
+#include "da_tcgen05.cuh"
+
+namespace da {
+namespace {
+
+constexpr int kRows = 128;                            // M of both contractions (G valid rows)
+constexpr int kDim = 128;
+constexpr int kTile = 64;                             // keys per tile
+constexpr int kStages = 4;
+constexpr int kBlocks = kDim / 64;                    // 64-element (128-byte) column blocks of a row
+constexpr int kQBlockBytes = kRows * 128;             // [128 heads x 64 dims]
+constexpr int kKBlockBytes = kTile * 128;             // [64 keys x 64 dims]
+constexpr int kKStageBytes = kBlocks * kKBlockBytes;  // K tile; the V tile has the same size
+constexpr int kPBytes = kRows * kTile * 2;
+constexpr int kOffQ = 0;
+constexpr int kOffK = kOffQ + kBlocks * kQBlockBytes;
+constexpr int kOffV = kOffK + kStages * kKStageBytes;
+constexpr int kOffP = kOffV + kStages * kKStageBytes;
+constexpr int kOffBar = kOffP + 2 * kPBytes;
+// q_full, kv_full/kv_empty[kStages], s_full[2], s_empty[2], p_full[2], pv_done[2]
+constexpr int kNumBars = 1 + 2 * kStages + 8;
+constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16 + 1024;
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 256;
+constexpr int kColS = 0;      // 2 x 64
+constexpr int kColO = 128;    // 128
+static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+constexpr float kRescaleThreshold = 8.0f;
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                 const __grid_constant__ CUtensorMap tm_v) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+
+    const int split = blockIdx.x;
+    const int hk = blockIdx.y;
+    const int b = blockIdx.z;
+    const int G = p.group;            // query heads of this KV head: rows 0..G-1 of the tile
+    const int h0 = hk * G;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int seq_begin = p.cu_seq_k[b];
+    const int len = p.cu_seq_k[b + 1] - seq_begin;
+    const int k_begin = split * p.chunk_keys;
+    const int k_end = min(len, k_begin + p.chunk_keys);
+    T *o_out = reinterpret_cast<T *>(p.o);
+    if (*reinterpret_cast<volatile int *>(p.status) != kStatusOk) return;  // an earlier CTA timed out: do not pile up
+
+    if (k_begin >= k_end) {
+        if (p.num_splits == 1) {  // empty sequence: zero rows, LSE = -inf
+            for (int idx = tid; idx < G * kDim; idx += kThreads) {
+                const int h = h0 + idx / kDim, d = idx % kDim;
+                if (o_out) o_out[(size_t)b * p.o_row_stride + (size_t)h * kDim + d] = from_float<T>(0.0f);
+                if (p.o_f32) p.o_f32[((size_t)b * p.head_q + h) * kDim + d] = 0.0f;
+            }
+            if (p.lse && tid < G) p.lse[(size_t)b * p.head_q + h0 + tid] = -INFINITY;
+        }
+        return;
+    }
+    const int n_tiles = (k_end - k_begin + kTile - 1) / kTile;
+    const int active_warps = (G + 31) / 32;  // softmax warps that own valid rows
+
+    uint8_t *q_s = smem + kOffQ;
+    uint8_t *k_s = smem + kOffK;
+    uint8_t *v_s = smem + kOffV;
+    uint8_t *p_s = smem + kOffP;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBar);
+    uint64_t *q_full = bars;
+    uint64_t *kv_full = bars + 1;
+    uint64_t *kv_empty = kv_full + kStages;
+    uint64_t *s_full = kv_empty + kStages;
+    uint64_t *s_empty = s_full + 2;
+    uint64_t *p_full = s_empty + 2;
+    uint64_t *pv_done = p_full + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kNumBars);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    if (tid == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&kv_full[s], 1);
+            mbar_init(&kv_empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&s_full[s], 1);
+            mbar_init(&s_empty[s], active_warps * 32);
+            mbar_init(&p_full[s], active_warps * 32);
+            mbar_init(&pv_done[s], 1);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 5) tmem_alloc(tmem_slot, kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+    constexpr uint32_t kIdescQK = instr_desc(kFmt, 0, kRows, kTile);
+    constexpr uint32_t kIdescPV = instr_desc(kFmt, 1, kRows, kDim);
+    bool ok = true;
+
+    if (warp == 4) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_q);
+            tma_prefetch_desc(&tm_k);
+            tma_prefetch_desc(&tm_v);
+            // Rows h0 .. h0+127 of q: rows past this KV head's group (or past head_q: zero-filled) only
+            // feed tile rows that are never read back.
+            // (the map's box holds min(128, head_q) rows; the transaction count is the box size).
+            mbar_arrive_expect_tx(q_full, kBlocks * min(kRows, p.head_q) * 128);
+            for (int kb = 0; kb < kBlocks; ++kb) tma_load_tile_3d(q_s + kb * kQBlockBytes, &tm_q, kb * 64, h0, b, q_full);
+        }
+        const T *k_g = reinterpret_cast<const T *>(p.k) + (size_t)hk * kDim;
+        const T *v_g = reinterpret_cast<const T *>(p.v) + (size_t)hk * kDim;
+        for (int t = 0; t < n_tiles && ok; ++t) {
+            const int st = t % kStages;
+            const uint32_t ph = (uint32_t)(t / kStages) & 1u;
+            const int key0 = k_begin + t * kTile;
+            const int rows = min(kTile, k_end - key0);
+            const size_t tok0 = (size_t)seq_begin + key0;
+            if (t >= kStages) ok = mbar_wait(&kv_empty[st], ph ^ 1u, abort_flag);
+            if (!ok) break;
+            uint8_t *kd = k_s + st * kKStageBytes, *vd = v_s + st * kKStageBytes;
+            if (rows == kTile) {
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(&kv_full[st], 2 * kKStageBytes);
+                    for (int kb = 0; kb < kBlocks; ++kb) {
+                        tma_load_tile_3d(kd + kb * kKBlockBytes, &tm_k, kb * 64, hk, (int)tok0, &kv_full[st]);
+                        tma_load_tile_3d(vd + kb * kKBlockBytes, &tm_v, kb * 64, hk, (int)tok0, &kv_full[st]);
+                    }
+                }
+            } else {
+                // Ragged tail: plain loads into the 128-byte-swizzled layout, rows past the end zeroed
+                // (the tensor maps must not be asked for rows beyond the sequence).
+                constexpr int kChunks = kDim / 8;  // 16-byte chunks per row
+                for (int i = lane; i < kTile * kChunks; i += 32) {
+                    const int r = i / kChunks, c = i % kChunks;
+                    uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
+                    if (r < rows) {
+                        kv = *reinterpret_cast<const uint4 *>(k_g + (tok0 + r) * p.k_row_stride + c * 8);
+                        vv = *reinterpret_cast<const uint4 *>(v_g + (tok0 + r) * p.v_row_stride + c * 8);
+                    }
+                    const int off = (c >> 3) * kKBlockBytes + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+                    *reinterpret_cast<uint4 *>(kd + off) = kv;
+                    *reinterpret_cast<uint4 *>(vd + off) = vv;
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&kv_full[st]);
+            }
+            __syncwarp();
+        }
+    } else if (warp == 5) {
+        // ---------------- MMA issuer ----------------
+        const uint32_t leader = elect_one();
+        const uint32_t q_addr = smem_u32(q_s), k_addr = smem_u32(k_s), v_addr = smem_u32(v_s), p_addr = smem_u32(p_s);
+        const uint64_t q_desc0 = smem_desc(q_addr, 16, 1024, 2);            // K-major, 8-row groups 1 KB apart
+        const uint64_t k_desc0 = smem_desc(k_addr, 16, 1024, 2);
+        const uint64_t v_desc0 = smem_desc(v_addr, kKBlockBytes, 1024, 2);  // MN-major: 64-col blocks LBO apart
+        const uint64_t p_desc0 = smem_desc(p_addr, kRows * 16, 128, 0);     // core matrices, 8-key chunks 2 KB apart
+        auto issue_qk = [&](int t) {
+            const uint64_t kd = k_desc0 + (uint64_t)(((t % kStages) * kKStageBytes) >> 4);
+            const uint32_t d = tmem_base + kColS + (t & 1) * kTile;
+#pragma unroll
+            for (int kb = 0; kb < kBlocks; ++kb) {
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    umma_ss(d, q_desc0 + (uint64_t)((kb * kQBlockBytes + ks * 32) >> 4),
+                            kd + (uint64_t)((kb * kKBlockBytes + ks * 32) >> 4), kIdescQK, (kb | ks) ? 1u : 0u, leader);
+                }
+            }
+            umma_commit(&s_full[t & 1], leader);
+        };
+        ok = mbar_wait(q_full, 0, abort_flag);
+        if (ok) ok = mbar_wait(&kv_full[0], 0, abort_flag);
+        if (ok) {
+            tc_fence_after();
+            issue_qk(0);
+        }
+        for (int t = 0; t < n_tiles && ok; ++t) {
+            if (t + 1 < n_tiles) {
+                const int t1 = t + 1;
+                ok = mbar_wait(&kv_full[t1 % kStages], (uint32_t)(t1 / kStages) & 1u, abort_flag);
+                if (ok && t1 >= 2) ok = mbar_wait(&s_empty[t1 & 1], ((uint32_t)(t1 / 2) & 1u) ^ 1u, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                issue_qk(t1);
+            }
+            ok = mbar_wait(&p_full[t & 1], (uint32_t)(t / 2) & 1u, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const int st = t % kStages;
+            const uint64_t pd = p_desc0 + (uint64_t)(((t & 1) * kPBytes) >> 4);
+            const uint64_t vd = v_desc0 + (uint64_t)((st * kKStageBytes) >> 4);
+#pragma unroll
+            for (int ks = 0; ks < kTile / 16; ++ks) {
+                umma_ss(tmem_base + kColO, pd + (uint64_t)((ks * 2 * (kRows * 16)) >> 4),
+                        vd + (uint64_t)((ks * 16 * 128) >> 4), kIdescPV, (t | ks) ? 1u : 0u, leader);
+            }
+            umma_commit(&kv_empty[st], leader);
+            umma_commit(&pv_done[t & 1], leader);
+        }
+        __syncwarp();
+    } else if (warp < active_warps) {
+        // ------- softmax / epilogue: thread r <-> TMEM lane r <-> head h0 + r (rows >= G are padding) -------
+        const int r = tid;
+        const bool valid = r < G;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+        const float slope2 = p.is_alibi ? exp2f(-8.0f * (float)(h0 + r + 1) / (float)p.head_q) * kLog2e : 0.0f;
+        const int pos_shift = (p.kv_pos_offset ? p.kv_pos_offset[b] : 0) - ((p.kv_total_len ? p.kv_total_len[b] : len) - 1);
+        float m_ref = -INFINITY, l = 0.0f;
+        uint32_t buf[32];
+        for (int t = 0; t < n_tiles; ++t) {
+            const int key0 = k_begin + t * kTile;
+            const int rows = min(kTile, k_end - key0);
+            ok = mbar_wait(&s_full[t & 1], (uint32_t)(t / 2) & 1u, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            float s[kTile];
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c0 = 0; c0 < kTile; c0 += 32) {
+                tmem_ld32(lane_base + kColS + (t & 1) * kTile + c0, buf);
+                tmem_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const float x = __uint_as_float(buf[j]) * p.scale_log2 + slope2 * (float)(key0 + c0 + j + pos_shift);
+                    s[c0 + j] = (c0 + j < rows) ? x : -INFINITY;
+                    mx = fmaxf(mx, s[c0 + j]);
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&s_empty[t & 1]);
+            const bool raise = mx > m_ref + kRescaleThreshold;
+            float alpha = 1.0f;
+            if (raise) {
+                alpha = exp2f(m_ref - mx);  // 0 on the first tile
+                m_ref = mx;
+                l *= alpha;
+            }
+            if (t >= 2) {
+                // The P buffer of this tile was last read by the P.V of tile t-2.
+                ok = mbar_wait(&pv_done[t & 1], ((uint32_t)(t / 2) & 1u) ^ 1u, abort_flag);
+                if (!ok) break;
+            }
+            if (t >= 1 && __any_sync(0xffffffffu, raise)) {
+                // Rare: the reference max of some row in this warp moved.  O must be idle (P.V of tile
+                // t-1 complete) while its rows are rescaled in place.
+                ok = mbar_wait(&pv_done[(t - 1) & 1], (uint32_t)((t - 1) / 2) & 1u, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll 1
+                for (int c = 0; c < kDim / 32; ++c) {
+                    tmem_ld32(lane_base + kColO + c * 32, buf);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) buf[j] = __float_as_uint(__uint_as_float(buf[j]) * alpha);
+                    tmem_st32(lane_base + kColO + c * 32, buf);
+                }
+                tmem_wait_st();
+            }
+            // P = exp2(S - m_ref), rounded to the input type, into the A-operand layout.
+            float sum = 0.0f;
+#pragma unroll
+            for (int c = 0; c < kTile / 8; ++c) {
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float p0 = exp2f(s[c * 8 + 2 * j] - m_ref), p1 = exp2f(s[c * 8 + 2 * j + 1] - m_ref);
+                    sum += p0 + p1;
+                    if (std::is_same<T, __nv_bfloat16>::value) {
+                        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                        w[j] = *reinterpret_cast<uint32_t *>(&h);
+                    } else {
+                        __half2 h = __floats2half2_rn(p0, p1);
+                        w[j] = *reinterpret_cast<uint32_t *>(&h);
+                    }
+                }
+                *reinterpret_cast<uint4 *>(p_s + (t & 1) * kPBytes + c * (kRows * 16) + r * 16) =
+                    make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            l += sum;
+            fence_proxy_async();
+            tc_fence_before();
+            mbar_arrive(&p_full[t & 1]);
+        }
+        if (ok) ok = mbar_wait(&pv_done[(n_tiles - 1) & 1], (uint32_t)((n_tiles - 1) / 2) & 1u, abort_flag);
+        if (ok) {
+            tc_fence_after();
+            const float inv = 1.0f / l;
+            const float lse = (m_ref + log2f(l)) * kLn2;
+            const int h = h0 + r;
+            const size_t row = ((size_t)b * p.head_q + h) * p.num_splits + split;
+#pragma unroll 1
+            for (int c = 0; c < kDim / 32; ++c) {
+                tmem_ld32(lane_base + kColO + c * 32, buf);
+                tmem_wait_ld();
+                const int d0 = c * 32;
+                if (!valid) continue;
+                if (p.num_splits > 1) {
+                    float4 *dst = reinterpret_cast<float4 *>(p.part_o + row * kDim + d0);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        dst[j] = make_float4(__uint_as_float(buf[4 * j]) * inv, __uint_as_float(buf[4 * j + 1]) * inv,
+                                             __uint_as_float(buf[4 * j + 2]) * inv, __uint_as_float(buf[4 * j + 3]) * inv);
+                    }
+                } else {
+                    if (o_out) {
+                        uint4 *dst = reinterpret_cast<uint4 *>(o_out + (size_t)b * p.o_row_stride + (size_t)h * kDim + d0);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            alignas(16) T tmp[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) tmp[e] = from_float<T>(__uint_as_float(buf[8 * j + e]) * inv);
+                            dst[j] = *reinterpret_cast<uint4 *>(tmp);
+                        }
+                    }
+                    if (p.o_f32) {
+                        float *dst = p.o_f32 + ((size_t)b * p.head_q + h) * kDim + d0;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) dst[j] = __uint_as_float(buf[j]) * inv;
+                    }
+                }
+            }
+            if (valid) {
+                if (p.num_splits > 1) {
+                    p.part_lse[row] = lse;
+                } else if (p.lse) {
+                    p.lse[(size_t)b * p.head_q + h] = lse;
+                }
+            }
+            tc_fence_before();
+        }
+    }
+
+    if (!ok && lane == 0) atomicExch(p.status, kStatusWaitTimeout);
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+}  // namespace
+
+SplitVariantInfo split_info_gqa_tc() { return {kTile, kRows, 1}; }
+
+// tm_q: rank-3 map of q [batch][head_q][128], box {64, min(128, head_q), 1}; tm_k / tm_v: rank-3 maps
+// [rows][head_k][128], box {64, 1, 64 keys}; all with the 128-byte swizzle.
+cudaError_t launch_gqa_tc(bool bf16, const SplitParams &p, const CUtensorMap &tm_q, const CUtensorMap &tm_k,
+                          const CUtensorMap &tm_v, cudaStream_t stream) {
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    if (dev < 64 && !attr_set[dev]) {
+        err = cudaFuncSetAttribute(da_gqa_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (err != cudaSuccess) return err;
+        err = cudaFuncSetAttribute(da_gqa_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   kSmemBytes);
+        if (err != cudaSuccess) return err;
+        attr_set[dev] = true;
+    }
+    dim3 grid(p.num_splits, p.head_k, p.batch);
+    if (bf16) {
+        da_gqa_tc_kernel<__nv_bfloat16><<<grid, kThreads, kSmemBytes, stream>>>(p, tm_q, tm_k, tm_v);
+    } else {
+        da_gqa_tc_kernel<__half><<<grid, kThreads, kSmemBytes, stream>>>(p, tm_q, tm_k, tm_v);
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace da
