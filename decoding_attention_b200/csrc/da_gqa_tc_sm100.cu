@@ -11,9 +11,13 @@
 //     O[128 x 128] += P[128 x 64]  . V_tile[64 x 128]        (4 MMAs  M128 N128 K16, V MN-major)
 // One CTA = (sequence, KV head, key range).  Q, K and V tiles arrive by tiled TMA copies with the
 // 128-byte swizzle; S (two buffers) and O live in tensor memory (256 columns).
-// Warps 0-3 = softmax/epilogue (thread r <-> TMEM lane r <-> head h0 + r; warps whose rows are all
-// >= G stay out), warp 4 = TMA producer, warp 5 = TMEM allocation + MMA issue.  Lazy reference
-// max as in the MLA kernel.  Every wait is bounded.
+// Warps 0-15 = softmax/epilogue.  A warp can only reach the TMEM lanes of its quadrant (warp % 4),
+// so four warps share each block of 32 rows and split the 64 score columns (and the 128 output
+// columns) four ways: with few valid rows per tile the softmax, not the tensor pipe, sets the
+// pace, and its latency is per-thread serial work.  The four threads of a row agree on the row
+// maximum through shared memory once per tile.  Quadrants whose rows are all >= G stay out.
+// Warp 16 = TMA producer, warp 17 = TMEM allocation + MMA issue.  Lazy reference max as in the MLA
+// kernel.  Every wait is bounded (the per-tile rendezvous of the softmax threads is an mbarrier).
 #include <type_traits>
 
 #include "da_internal.h"
@@ -35,16 +39,35 @@ constexpr int kOffQ = 0;
 constexpr int kOffK = kOffQ + kBlocks * kQBlockBytes;
 constexpr int kOffV = kOffK + kStages * kKStageBytes;
 constexpr int kOffP = kOffV + kStages * kKStageBytes;
-constexpr int kOffBar = kOffP + 2 * kPBytes;
-// q_full, kv_full/kv_empty[kStages], s_full[2], s_empty[2], p_full[2], pv_done[2]
-constexpr int kNumBars = 1 + 2 * kStages + 8;
+constexpr int kColSplit = 4;                          // softmax threads per row: 2 streams x 2 column halves
+constexpr int kColsPer = 32;                          // score columns per thread
+constexpr int kOffRowMax = kOffP + 2 * kPBytes;       // [2][kColSplit][128] floats: per-thread partial row maxima / sums
+constexpr int kOffBar = kOffRowMax + 2 * kColSplit * kRows * 4 + 1024;  // + [2][128] stream maxima for the final merge
+// q_full, kv_full/kv_empty[kStages], s_full[2], s_empty[2], p_full[2], pv_done[2], row_sync[2], fin_sync
+constexpr int kNumBars = 1 + 2 * kStages + 11;
 constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16 + 1024;
-constexpr int kThreads = 192;
-constexpr int kTmemCols = 256;
-constexpr int kColS = 0;      // 2 x 64
-constexpr int kColO = 128;    // 128
+constexpr int kSoftmaxWarps = 4 * kColSplit;
+constexpr int kProducerWarp = kSoftmaxWarps, kMmaWarp = kSoftmaxWarps + 1;
+constexpr int kThreads = (kSoftmaxWarps + 2) * 32;
+constexpr int kTmemCols = 512;
+constexpr int kColS = 0;      // 2 x 64: one S buffer per stream
+constexpr int kColO = 128;    // 2 x 128: one accumulator per stream
 static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 constexpr float kRescaleThreshold = 8.0f;
+
+#ifdef DA_GQA_PROFILE
+// Development aid (not compiled into the shipped library): cycles CTA (0,0,0) spends in each step.
+__device__ long long g_gqa_prof[64];
+#define PROF_DECL long long prof_t0 = 0, prof_acc[16] = {}; (void)prof_t0
+#define PROF_BEGIN() prof_t0 = clock64()
+#define PROF_END(slot) do { long long now_ = clock64(); prof_acc[(slot) & 15] += now_ - prof_t0; prof_t0 = now_; } while (0)
+#define PROF_FLUSH(base) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0) { for (int i_ = 0; i_ < 16; ++i_) g_gqa_prof[(base) + i_] += prof_acc[i_]; } } while (0)
+#else
+#define PROF_DECL
+#define PROF_BEGIN()
+#define PROF_END(slot)
+#define PROF_FLUSH(base)
+#endif
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -78,7 +101,8 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
         return;
     }
     const int n_tiles = (k_end - k_begin + kTile - 1) / kTile;
-    const int active_warps = (G + 31) / 32;  // softmax warps that own valid rows
+    const int active_quads = (G + 31) / 32;                   // 32-row blocks that hold valid rows
+    const int participants = active_quads * 2 * 32;           // softmax threads at work on one stream
 
     uint8_t *q_s = smem + kOffQ;
     uint8_t *k_s = smem + kOffK;
@@ -92,6 +116,9 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
     uint64_t *s_empty = s_full + 2;
     uint64_t *p_full = s_empty + 2;
     uint64_t *pv_done = p_full + 2;
+    uint64_t *row_sync = pv_done + 2;
+    uint64_t *fin_sync = row_sync + 2;
+    float *rowmax_s = reinterpret_cast<float *>(smem + kOffRowMax);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kNumBars);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
@@ -103,14 +130,16 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&s_full[s], 1);
-            mbar_init(&s_empty[s], active_warps * 32);
-            mbar_init(&p_full[s], active_warps * 32);
+            mbar_init(&s_empty[s], participants);
+            mbar_init(&p_full[s], participants);
             mbar_init(&pv_done[s], 1);
+            mbar_init(&row_sync[s], participants);
         }
+        mbar_init(fin_sync, 2 * participants);
         *abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == 5) tmem_alloc(tmem_slot, kTmemCols);
+    if (warp == kMmaWarp) tmem_alloc(tmem_slot, kTmemCols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -121,7 +150,7 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
     constexpr uint32_t kIdescPV = instr_desc(kFmt, 1, kRows, kDim);
     bool ok = true;
 
-    if (warp == 4) {
+    if (warp == kProducerWarp) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             tma_prefetch_desc(&tm_q);
@@ -173,7 +202,7 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             }
             __syncwarp();
         }
-    } else if (warp == 5) {
+    } else if (warp == kMmaWarp) {
         // ---------------- MMA issuer ----------------
         const uint32_t leader = elect_one();
         const uint32_t q_addr = smem_u32(q_s), k_addr = smem_u32(k_s), v_addr = smem_u32(v_s), p_addr = smem_u32(p_s);
@@ -200,16 +229,22 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             tc_fence_after();
             issue_qk(0);
         }
+        PROF_DECL;
         for (int t = 0; t < n_tiles && ok; ++t) {
+            PROF_BEGIN();
             if (t + 1 < n_tiles) {
                 const int t1 = t + 1;
                 ok = mbar_wait(&kv_full[t1 % kStages], (uint32_t)(t1 / kStages) & 1u, abort_flag);
+                PROF_END(0);
                 if (ok && t1 >= 2) ok = mbar_wait(&s_empty[t1 & 1], ((uint32_t)(t1 / 2) & 1u) ^ 1u, abort_flag);
+                PROF_END(1);
                 if (!ok) break;
                 tc_fence_after();
                 issue_qk(t1);
+                PROF_END(2);
             }
             ok = mbar_wait(&p_full[t & 1], (uint32_t)(t / 2) & 1u, abort_flag);
+            PROF_END(3);
             if (!ok) break;
             tc_fence_after();
             const int st = t % kStages;
@@ -217,75 +252,95 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             const uint64_t vd = v_desc0 + (uint64_t)((st * kKStageBytes) >> 4);
 #pragma unroll
             for (int ks = 0; ks < kTile / 16; ++ks) {
-                umma_ss(tmem_base + kColO, pd + (uint64_t)((ks * 2 * (kRows * 16)) >> 4),
-                        vd + (uint64_t)((ks * 16 * 128) >> 4), kIdescPV, (t | ks) ? 1u : 0u, leader);
+                umma_ss(tmem_base + kColO + (t & 1) * kDim, pd + (uint64_t)((ks * 2 * (kRows * 16)) >> 4),
+                        vd + (uint64_t)((ks * 16 * 128) >> 4), kIdescPV, (t >= 2 || ks > 0) ? 1u : 0u, leader);
             }
             umma_commit(&kv_empty[st], leader);
             umma_commit(&pv_done[t & 1], leader);
+            PROF_END(4);
         }
+        PROF_FLUSH(0);
         __syncwarp();
-    } else if (warp < active_warps) {
-        // ------- softmax / epilogue: thread r <-> TMEM lane r <-> head h0 + r (rows >= G are padding) -------
-        const int r = tid;
+    } else if ((warp & 3) < active_quads) {
+        // ------- softmax / epilogue -------
+        // Two independent online-softmax streams run interleaved: even tiles (S buffer 0, P buffer 0,
+        // accumulator O0) and odd tiles (buffer 1, O1), each with its own reference max and sum; they
+        // are merged at the end like two key-range splits.  That keeps two tiles' worth of the
+        // (latency-bound) softmax chain in flight.  Thread (quad, strm, hf, lane) owns row 32 quad + lane
+        // of stream strm and its score columns [32 hf, +32).
+        const int quad = warp & 3, cp = warp >> 2, strm = cp >> 1, hf = cp & 1;
+        const int r = quad * 32 + lane;
         const bool valid = r < G;
-        const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+        const uint32_t o_col = kColO + strm * kDim;
         const float slope2 = p.is_alibi ? exp2f(-8.0f * (float)(h0 + r + 1) / (float)p.head_q) * kLog2e : 0.0f;
         const int pos_shift = (p.kv_pos_offset ? p.kv_pos_offset[b] : 0) - ((p.kv_total_len ? p.kv_total_len[b] : len) - 1);
         float m_ref = -INFINITY, l = 0.0f;
         uint32_t buf[32];
-        for (int t = 0; t < n_tiles; ++t) {
-            const int key0 = k_begin + t * kTile;
-            const int rows = min(kTile, k_end - key0);
-            ok = mbar_wait(&s_full[t & 1], (uint32_t)(t / 2) & 1u, abort_flag);
+        float *rm = rowmax_s + strm * (2 * kRows);  // [2 halves][128] partial row maxima of this stream
+        PROF_DECL;
+        int last_t = -1;
+        for (int t = strm; t < n_tiles; t += 2) {
+            PROF_BEGIN();
+            const int it = t >> 1;  // use count of this stream's barriers
+            const int key0 = k_begin + t * kTile + hf * kColsPer;
+            const int rows = min(kTile, k_end - (k_begin + t * kTile)) - hf * kColsPer;  // valid columns of this thread
+            ok = __all_sync(0xffffffffu, mbar_wait(&s_full[strm], (uint32_t)it & 1u, abort_flag));
+            PROF_END(0);
             if (!ok) break;
             tc_fence_after();
-            float s[kTile];
+            tmem_ld32(lane_base + kColS + strm * kTile + hf * kColsPer, buf);
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(&s_empty[strm]);
+            float s[kColsPer];
             float mx = -INFINITY;
 #pragma unroll
-            for (int c0 = 0; c0 < kTile; c0 += 32) {
-                tmem_ld32(lane_base + kColS + (t & 1) * kTile + c0, buf);
-                tmem_wait_ld();
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const float x = __uint_as_float(buf[j]) * p.scale_log2 + slope2 * (float)(key0 + c0 + j + pos_shift);
-                    s[c0 + j] = (c0 + j < rows) ? x : -INFINITY;
-                    mx = fmaxf(mx, s[c0 + j]);
-                }
+            for (int j = 0; j < kColsPer; ++j) {
+                const float x = __uint_as_float(buf[j]) * p.scale_log2 + slope2 * (float)(key0 + j + pos_shift);
+                s[j] = (j < rows) ? x : -INFINITY;
+                mx = fmaxf(mx, s[j]);
             }
-            tc_fence_before();
-            mbar_arrive(&s_empty[t & 1]);
+            // The two threads of a row agree on the tile's row maximum.
+            rm[hf * kRows + r] = mx;
+            PROF_END(1);
+            mbar_arrive(&row_sync[strm]);
+            ok = __all_sync(0xffffffffu, mbar_wait(&row_sync[strm], (uint32_t)it & 1u, abort_flag));
+            PROF_END(2);
+            if (!ok) break;
+            mx = fmaxf(mx, rm[(hf ^ 1) * kRows + r]);
             const bool raise = mx > m_ref + kRescaleThreshold;
             float alpha = 1.0f;
             if (raise) {
-                alpha = exp2f(m_ref - mx);  // 0 on the first tile
+                alpha = exp2f(m_ref - mx);  // 0 on the stream's first tile
                 m_ref = mx;
                 l *= alpha;
             }
-            if (t >= 2) {
-                // The P buffer of this tile was last read by the P.V of tile t-2.
-                ok = mbar_wait(&pv_done[t & 1], ((uint32_t)(t / 2) & 1u) ^ 1u, abort_flag);
+            if (it >= 1) {
+                // This stream's previous P.V has finished: its P buffer and its accumulator are idle.
+                ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[strm], (uint32_t)(it - 1) & 1u, abort_flag));
                 if (!ok) break;
-            }
-            if (t >= 1 && __any_sync(0xffffffffu, raise)) {
-                // Rare: the reference max of some row in this warp moved.  O must be idle (P.V of tile
-                // t-1 complete) while its rows are rescaled in place.
-                ok = mbar_wait(&pv_done[(t - 1) & 1], (uint32_t)((t - 1) / 2) & 1u, abort_flag);
-                if (!ok) break;
-                tc_fence_after();
+                if (__any_sync(0xffffffffu, raise)) {
+                    // Rare: the reference max of some row of this quadrant moved; rescale this thread's 64
+                    // columns of the row in place.
+                    tc_fence_after();
 #pragma unroll 1
-                for (int c = 0; c < kDim / 32; ++c) {
-                    tmem_ld32(lane_base + kColO + c * 32, buf);
-                    tmem_wait_ld();
+                    for (int c = 0; c < 2; ++c) {
+                        uint32_t ob[32];
+                        tmem_ld32(lane_base + o_col + hf * 64 + c * 32, ob);
+                        tmem_wait_ld();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) buf[j] = __float_as_uint(__uint_as_float(buf[j]) * alpha);
-                    tmem_st32(lane_base + kColO + c * 32, buf);
+                        for (int j = 0; j < 32; ++j) ob[j] = __float_as_uint(__uint_as_float(ob[j]) * alpha);
+                        tmem_st32(lane_base + o_col + hf * 64 + c * 32, ob);
+                    }
+                    tmem_wait_st();
                 }
-                tmem_wait_st();
             }
-            // P = exp2(S - m_ref), rounded to the input type, into the A-operand layout.
+            PROF_END(3);
+            // P = exp2(S - m_ref), rounded to the input type, into the A-operand layout (8-key chunks).
             float sum = 0.0f;
 #pragma unroll
-            for (int c = 0; c < kTile / 8; ++c) {
+            for (int c = 0; c < kColsPer / 8; ++c) {
                 uint32_t w[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -299,34 +354,62 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                         w[j] = *reinterpret_cast<uint32_t *>(&h);
                     }
                 }
-                *reinterpret_cast<uint4 *>(p_s + (t & 1) * kPBytes + c * (kRows * 16) + r * 16) =
+                *reinterpret_cast<uint4 *>(p_s + strm * kPBytes + (hf * (kColsPer / 8) + c) * (kRows * 16) + r * 16) =
                     make_uint4(w[0], w[1], w[2], w[3]);
             }
             l += sum;
             fence_proxy_async();
             tc_fence_before();
-            mbar_arrive(&p_full[t & 1]);
+            mbar_arrive(&p_full[strm]);
+            last_t = t;
+            PROF_END(4);
         }
-        if (ok) ok = mbar_wait(&pv_done[(n_tiles - 1) & 1], (uint32_t)((n_tiles - 1) / 2) & 1u, abort_flag);
+        if (warp == 0) PROF_FLUSH(16);
+        // ---- merge the two streams and write the row out ----
+        float *l_part = rowmax_s + 2 * 2 * kRows;       // [4 threads of a row][128]
+        float *m_strm = l_part + kColSplit * kRows;     // [2 streams][128]
+        if (ok) {
+            l_part[cp * kRows + r] = l;
+            if (hf == 0) m_strm[strm * kRows + r] = m_ref;
+            mbar_arrive(fin_sync);
+            ok = __all_sync(0xffffffffu, mbar_wait(fin_sync, 0, abort_flag));
+        }
+        // both accumulators must be final: the last P.V of either stream
+        if (ok && last_t >= 0) ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[strm], (uint32_t)(last_t >> 1) & 1u, abort_flag));
+        const int other_last = ((n_tiles - 1) & 1) == (strm ^ 1) ? n_tiles - 1 : n_tiles - 2;
+        if (ok && other_last >= 0) {
+            ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[strm ^ 1], (uint32_t)(other_last >> 1) & 1u, abort_flag));
+        }
         if (ok) {
             tc_fence_after();
-            const float inv = 1.0f / l;
-            const float lse = (m_ref + log2f(l)) * kLn2;
+            const float m0 = m_strm[r], m1 = m_strm[kRows + r];
+            const float l0 = l_part[0 * kRows + r] + l_part[1 * kRows + r];
+            const float l1 = l_part[2 * kRows + r] + l_part[3 * kRows + r];
+            const float mm = fmaxf(m0, m1);                      // stream 0 always has a tile: finite
+            const float w0 = exp2f(m0 - mm), w1 = (m1 == -INFINITY) ? 0.0f : exp2f(m1 - mm);
+            const float lsum = l0 * w0 + l1 * w1;
+            const float inv = 1.0f / lsum;
+            const float lse = (mm + log2f(lsum)) * kLn2;
             const int h = h0 + r;
             const size_t row = ((size_t)b * p.head_q + h) * p.num_splits + split;
-#pragma unroll 1
-            for (int c = 0; c < kDim / 32; ++c) {
-                tmem_ld32(lane_base + kColO + c * 32, buf);
-                tmem_wait_ld();
-                const int d0 = c * 32;
-                if (!valid) continue;
+            uint32_t ob[32];
+            tmem_ld32(lane_base + kColO + cp * 32, buf);          // stream 0, this thread's 32 output columns
+            tmem_ld32(lane_base + kColO + kDim + cp * 32, ob);    // stream 1 (never written if it had no tile)
+            tmem_wait_ld();
+            float out[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float a0 = __uint_as_float(buf[j]) * w0;
+                const float a1 = (w1 > 0.0f) ? __uint_as_float(ob[j]) * w1 : 0.0f;
+                out[j] = (a0 + a1) * inv;
+            }
+            const int d0 = cp * 32;
+            if (valid) {
                 if (p.num_splits > 1) {
                     float4 *dst = reinterpret_cast<float4 *>(p.part_o + row * kDim + d0);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        dst[j] = make_float4(__uint_as_float(buf[4 * j]) * inv, __uint_as_float(buf[4 * j + 1]) * inv,
-                                             __uint_as_float(buf[4 * j + 2]) * inv, __uint_as_float(buf[4 * j + 3]) * inv);
-                    }
+                    for (int j = 0; j < 8; ++j) dst[j] = make_float4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+                    if (cp == 0) p.part_lse[row] = lse;
                 } else {
                     if (o_out) {
                         uint4 *dst = reinterpret_cast<uint4 *>(o_out + (size_t)b * p.o_row_stride + (size_t)h * kDim + d0);
@@ -334,22 +417,16 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                         for (int j = 0; j < 4; ++j) {
                             alignas(16) T tmp[8];
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) tmp[e] = from_float<T>(__uint_as_float(buf[8 * j + e]) * inv);
+                            for (int e = 0; e < 8; ++e) tmp[e] = from_float<T>(out[8 * j + e]);
                             dst[j] = *reinterpret_cast<uint4 *>(tmp);
                         }
                     }
                     if (p.o_f32) {
                         float *dst = p.o_f32 + ((size_t)b * p.head_q + h) * kDim + d0;
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) dst[j] = __uint_as_float(buf[j]) * inv;
+                        for (int j = 0; j < 32; ++j) dst[j] = out[j];
                     }
-                }
-            }
-            if (valid) {
-                if (p.num_splits > 1) {
-                    p.part_lse[row] = lse;
-                } else if (p.lse) {
-                    p.lse[(size_t)b * p.head_q + h] = lse;
+                    if (p.lse && cp == 0) p.lse[(size_t)b * p.head_q + h] = lse;
                 }
             }
             tc_fence_before();
@@ -358,13 +435,24 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
 
     if (!ok && lane == 0) atomicExch(p.status, kStatusWaitTimeout);
     __syncthreads();
-    if (warp == 5) {
+    if (warp == kMmaWarp) {
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
     }
 }
 
 }  // namespace
+
+#ifdef DA_GQA_PROFILE
+extern "C" void da_debug_gqa_prof(long long *out, int reset) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, g_gqa_prof, sizeof(long long) * 64);
+    if (reset) {
+        long long z[64] = {};
+        cudaMemcpyToSymbol(g_gqa_prof, z, sizeof(z));
+    }
+}
+#endif
 
 SplitVariantInfo split_info_gqa_tc() { return {kTile, kRows, 1}; }
 
