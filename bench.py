@@ -358,7 +358,8 @@ def other_configs(cabi, dev, world, rank, barrier, max_over_ranks, hbm_peak):
     w = synth.config_long_mha()
     lo, hi = sharded.key_range(w.seq_lens[0], rank, world)
     q, k, v, cu = w.make(dev, key_range=(lo, hi))
-    dec = sharded.KeyRangeShardedDecoder(1, w.head_q, w.dim_v, w.dtype, dev)
+    fused = os.environ.get("DA_SHARD_EXCHANGE", "fused") != "nccl"
+    dec = sharded.KeyRangeShardedDecoder(1, w.head_q, w.dim_v, w.dtype, dev, fused=fused)
     off = torch.tensor([lo], dtype=torch.int32, device=dev)
     tot = torch.tensor([w.seq_lens[0]], dtype=torch.int32, device=dev)
     for _ in range(5):
@@ -377,7 +378,9 @@ def other_configs(cabi, dev, world, rank, barrier, max_over_ranks, hbm_peak):
     res["mha_bf16_b1_sk131072_key_range_sharded"] = {
         "n_gpus": world, "us_per_call": round(sec * 1e6, 2), "kv_GBps": round(w.kv_bytes() / sec / 1e9, 1),
         "frac_of_hbm_peak_per_gpu": round(w.kv_bytes() / world / sec / 1e9 / hbm_peak, 4), "scaling": "strong",
-        "steps": "local partial (o fp32, lse) -> all-gather of %d-byte records -> on-device LSE merge" % (
+        "steps": ("local partial (o fp32, lse) -> one kernel: peer stores of the %d-byte record + flags, bounded wait, "
+                  "LSE merge" if fused else
+                  "local partial (o fp32, lse) -> NCCL all-gather of %d-byte records -> on-device LSE merge") % (
             dec.rec.numel() * 4)}
     return res
 

@@ -347,6 +347,13 @@ void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_r
 
 int report_error(int code, const char *msg) { return fail(code, "%s", msg); }
 
+int xmerge_status_ptr(int **out) {
+    DeviceState *st = nullptr;
+    int rc = device_state(&st);
+    if (rc == DA_OK) *out = st->status_ptr;
+    return rc;
+}
+
 }  // namespace da
 
 using namespace da;

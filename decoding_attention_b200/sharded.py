@@ -8,8 +8,11 @@ benchmarks/cpp/benchmark_decoding_attn.cpp:27, :43), so both modes below are add
 * key-range sharding -- one long sequence's KV cache lives in contiguous key ranges, one per rank.
   Every rank computes a partial (o fp32, lse) over its range, the fixed-size records are
   all-gathered (NCCL over NVLink; tiny, latency-bound) and every rank merges them on its device
-  with da_merge_partials.
+  with da_merge_partials -- or, with ``fused=True``, one kernel per rank pushes its record to the
+  peers' symmetric buffers with peer stores, waits (bounded) for theirs and merges
+  (da_exchange_merge): no collective call, one launch instead of three.
 """
+import ctypes
 from typing import List, Sequence, Tuple
 
 import torch
@@ -65,11 +68,14 @@ class KeyRangeShardedDecoder:
     """Decode attention for sequences whose KV cache is sharded by key range over the ranks of a
     process group.  Construct once per (batch, head_q, dim_v); ``step`` is then allocation-free."""
 
-    def __init__(self, batch, head_q, dim_v, out_dtype, device, group=None):
+    def __init__(self, batch, head_q, dim_v, out_dtype, device, group=None, fused=False):
         from . import cabi
         self.cabi = cabi
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.fused = fused
+        self.epoch = 0
         self.rows, self.dim_v, self.head_q, self.batch = batch * head_q, dim_v, head_q, batch
         n = record_floats(self.rows, dim_v)
         self.rec = torch.zeros(n, dtype=torch.float32, device=device)
@@ -77,6 +83,29 @@ class KeyRangeShardedDecoder:
         self.out = torch.empty(batch, head_q, dim_v, dtype=out_dtype, device=device)
         self.lse = torch.empty(batch, head_q, dtype=torch.float32, device=device)
         self.rec_o, self.rec_lse = record_views(self.rec, self.rows, dim_v)
+        if fused:
+            self._setup_exchange(device)
+
+    def _setup_exchange(self, device):
+        """Symmetric gather buffer (one per rank, each mapped into every peer) for da_exchange_merge."""
+        nbytes = self.cabi.lib().da_exchange_buffer_bytes(self.world, self.rows, self.dim_v)
+        if self.world == 1:
+            self.xbuf = torch.zeros(nbytes // 4, dtype=torch.float32, device=device)
+            ptrs = [self.xbuf.data_ptr()]
+        else:
+            import torch.distributed._symmetric_memory as symm_mem
+            pg = self.group if self.group is not None else dist.group.WORLD
+            try:
+                symm_mem.enable_symm_mem_for_group(pg.group_name)
+            except Exception:
+                pass  # newer torch enables groups on demand
+            self.xbuf = symm_mem.empty(nbytes // 4, dtype=torch.float32, device=device)
+            self.xbuf.zero_()
+            self._hdl = symm_mem.rendezvous(self.xbuf, pg.group_name)
+            ptrs = [int(x) for x in self._hdl.buffer_ptrs]
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)  # every rank's flags are zero before anybody pushes
+        self.peer_ptrs = (ctypes.c_void_p * self.world)(*ptrs)
 
     def local_partial(self, q, k, v, cu_seq_k, max_seq_k, is_alibi, kv_pos_offset, kv_total_len, softmax_scale=None):
         a = self.cabi.make_args(q, k, v, None, cu_seq_k, max_seq_k, self.dim_v, is_alibi=is_alibi,
@@ -104,5 +133,15 @@ class KeyRangeShardedDecoder:
              softmax_scale=None):
         """q replicated; k, v this rank's key range; returns the full result on every rank."""
         self.local_partial(q, k, v, cu_seq_k, max_seq_k, is_alibi, kv_pos_offset, kv_total_len, softmax_scale)
+        if self.fused:
+            return self.exchange_merge()
         self.exchange()
         return self.merge()
+
+    def exchange_merge(self):
+        self.epoch += 1
+        self.cabi.check(self.cabi.lib().da_exchange_merge(
+            self.rec.data_ptr(), self.peer_ptrs, self.world, self.rank, self.rows, self.dim_v, self.epoch,
+            self.out.data_ptr(), self.lse.data_ptr(), int(self.out.dtype == torch.bfloat16),
+            torch.cuda.current_stream().cuda_stream))
+        return self.out

@@ -125,6 +125,20 @@ int da_merge_partials(const float *part_o, const float *part_lse, int32_t num_pa
                       int64_t part_stride_o, int64_t row_stride_o, int64_t part_stride_lse, int64_t row_stride_lse,
                       void *o, float *o_f32, float *lse, int32_t is_bf16, void *stream);
 
+/* Key-range sharding without a collective library: one kernel per rank that (1) stores this rank's
+ * record `rec` (o fp32 [rows, dim_v] followed by lse fp32 [rows]) into every peer's gather buffer
+ * with peer stores and raises a flag there, (2) waits -- bounded -- for all peers' flags of this
+ * step in its own buffer, (3) merges the `world` records into o [rows, dim_v] (+ optional lse).
+ * peer_bufs[r] is the device address, valid on THIS device, of rank r's gather buffer (a symmetric
+ * allocation of da_exchange_buffer_bytes(world, rows, dim_v) bytes, zero-filled once before the
+ * first step; peer_bufs[rank] is the local one).  `epoch` numbers the steps: 1, 2, 3, ... the same
+ * on every rank.  All ranks must call it once per step, each on its own GPU, and be running
+ * concurrently.  A peer that never shows up makes the wait run out: the rows are left unwritten
+ * and da_device_status() reports DA_ERR_TIMEOUT.  No reference counterpart (single-GPU library). */
+int da_exchange_merge(const float *rec, void *const *peer_bufs, int32_t world, int32_t rank, int64_t rows,
+                      int32_t dim_v, uint32_t epoch, void *o, float *lse, int32_t is_bf16, void *stream);
+size_t da_exchange_buffer_bytes(int32_t world, int64_t rows, int32_t dim_v);
+
 /* Profiling hook for the calling thread: while both are non-NULL, da_decode_fwd records the CUDA
  * event `start_event` on the stream just before its main (key-streaming) kernel and `stop_event`
  * just after it, so a benchmark can time that kernel apart from the merge kernel.  Pass NULLs to

@@ -15,14 +15,17 @@ from helpers import assert_close
 pytestmark = pytest.mark.gpu
 
 
-def test_key_range_decoder_single_rank(native_lib, oracle):
+@pytest.mark.parametrize("fused", [False, True])
+def test_key_range_decoder_single_rank(native_lib, oracle, fused):
     dev = "cuda:0"
     w = synth.Workload("long1", torch.bfloat16, 32, 32, 128, 128, [9000], is_alibi=True, dist="normal", scale=0.5)
     q, k, v, cu = w.make("cpu")
     expect = oracle.attn_cpu(q, k, v, cu, is_alibi=True)
-    dec = sharded.KeyRangeShardedDecoder(1, 32, 128, w.dtype, dev)
-    out = dec.step(q.to(dev), k.to(dev), v.to(dev), cu.to(dev), 9000, is_alibi=True)
+    dec = sharded.KeyRangeShardedDecoder(1, 32, 128, w.dtype, dev, fused=fused)
+    for _ in range(3):  # several steps: the exchange buffers are double-buffered by step parity
+        out = dec.step(q.to(dev), k.to(dev), v.to(dev), cu.to(dev), 9000, is_alibi=True)
     torch.cuda.synchronize()
+    assert native_lib.device_status() == native_lib.DA_OK
     assert_close(out, expect, "world-1 key-range decoder")
 
 
@@ -34,7 +37,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, ret):
+def _worker(rank, world, port, ret, fused=False):
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     sys.path.insert(0, root)
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
@@ -45,21 +48,25 @@ def _worker(rank, world, port, ret):
         w = synth.Workload("long2", torch.bfloat16, 32, 32, 128, 128, [20000], is_alibi=True, dist="normal", scale=0.5)
         lo, hi = sharded.key_range(20000, rank, world)
         q, k, v, cu = w.make(dev, key_range=(lo, hi))
-        dec = sharded.KeyRangeShardedDecoder(1, 32, 128, w.dtype, dev)
+        dec = sharded.KeyRangeShardedDecoder(1, 32, 128, w.dtype, dev, fused=fused)
         off = torch.tensor([lo], dtype=torch.int32, device=dev)
         tot = torch.tensor([20000], dtype=torch.int32, device=dev)
-        out = dec.step(q, k, v, cu, hi - lo, is_alibi=True, kv_pos_offset=off, kv_total_len=tot)
+        for _ in range(4):
+            out = dec.step(q, k, v, cu, hi - lo, is_alibi=True, kv_pos_offset=off, kv_total_len=tot)
         torch.cuda.synchronize()
+        from decoding_attention_b200 import cabi
+        assert cabi.device_status() == cabi.DA_OK
         ret[rank] = out.cpu()
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_key_range_decoder_two_ranks(oracle):
+@pytest.mark.parametrize("fused", [False, True])
+def test_key_range_decoder_two_ranks(oracle, fused):
     world = 2
     ret = mp.get_context("spawn").Manager().dict()
-    mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), ret, fused), nprocs=world, join=True)
     w = synth.Workload("long2", torch.bfloat16, 32, 32, 128, 128, [20000], is_alibi=True, dist="normal", scale=0.5)
     q, k, v, cu = w.make("cpu")
     expect = oracle.attn_cpu(q, k, v, cu, is_alibi=True)
