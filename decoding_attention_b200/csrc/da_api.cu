@@ -647,6 +647,35 @@ void da_set_profile_events(void *start_event, void *stop_event) {
     g_prof_stop = reinterpret_cast<cudaEvent_t>(stop_event);
 }
 
+namespace da {
+namespace {
+// A wait that nothing ever satisfies, with a short bound: exercises the give-up path of the kernels'
+// bounded waits (flag -> status word -> da_device_status) without harming the context.
+__global__ void da_selftest_wait_kernel(int *status, long long max_cycles) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+        const long long t0 = clock64();
+        bool done = false;
+        while (!done && clock64() - t0 < max_cycles) done = mbar_try_wait(&bar, 0);
+        if (!done) atomicExch(status, kStatusWaitTimeout);
+    }
+}
+}  // namespace
+}  // namespace da
+
+int da_selftest_wait_timeout(void *stream) {
+    DeviceState *st = nullptr;
+    int rc = device_state(&st);
+    if (rc != DA_OK) return rc;
+    da_selftest_wait_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(st->status_ptr, 2000000ll);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(DA_ERR_CUDA, "selftest launch: %s", cudaGetErrorString(e));
+    return DA_OK;
+}
+
 int da_device_status(void) {
     DeviceState *st = nullptr;
     int rc = device_state(&st);

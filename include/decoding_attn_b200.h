@@ -150,6 +150,12 @@ void da_set_profile_events(void *start_event, void *stop_event);
  * has no counterpart: its kernel has no waits and its host checks exit() (common.h:17-49). */
 int da_device_status(void);
 
+/* Launches a one-warp kernel that waits, with a bound of about a millisecond, on a barrier nobody
+ * will ever arrive on, and gives up the way the attention kernels' bounded waits do.  Afterwards
+ * da_device_status() returns DA_ERR_TIMEOUT once (and clears the word); the context stays usable.
+ * For testing the failure path without faulting or hanging a GPU.  No reference counterpart. */
+int da_selftest_wait_timeout(void *stream);
+
 const char *da_status_string(int status);
 const char *da_last_error(void);
 

@@ -203,3 +203,44 @@ def test_argument_errors(native_lib):
     bad.q = None
     with pytest.raises(native_lib.DecodingAttnError):
         native_lib.decode_fwd(bad)
+
+
+def test_bounded_wait_gives_up_and_reports(native_lib, oracle):
+    """Failure path without a fault: a wait that nothing satisfies runs out after ~1 ms, the status word
+    reports it once, and the context keeps working."""
+    assert native_lib.device_status() == native_lib.DA_OK
+    native_lib.check(native_lib.lib().da_selftest_wait_timeout(None))
+    assert native_lib.device_status() == native_lib.DA_ERR_TIMEOUT
+    assert b"bounded wait" in native_lib.lib().da_last_error()
+    assert native_lib.device_status() == native_lib.DA_OK  # cleared by the read
+    w = synth.Workload("after_timeout", torch.float16, 8, 2, 128, 128, [300], dist="normal", seed=41)
+    check(native_lib, oracle, w)
+
+
+def test_cuda_graph_replay(native_lib, oracle):
+    """The call is stream-ordered with no host synchronisation: after a warm-up call (attribute set-up,
+    tensor maps) it can be captured in a CUDA graph with a caller workspace and replayed."""
+    w = synth.Workload("graph", torch.bfloat16, 32, 8, 128, 128, [1500, 64, 700], dist="normal", scale=0.5, seed=42)
+    q, k, v, cu = [t.to(DEV) for t in w.make("cpu")]
+    expect = oracle.attn_cpu(*w.make("cpu"))
+    o = torch.zeros(3, 32, 128, dtype=w.dtype, device=DEV)
+    probe = native_lib.make_args(q, k, v, o, cu, w.max_seq_k, 128, num_splits=3)
+    ws = torch.empty(native_lib.workspace_bytes(probe), dtype=torch.uint8, device=DEV)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        args = native_lib.make_args(q, k, v, o, cu, w.max_seq_k, 128, num_splits=3, workspace=ws,
+                                    stream=side.cuda_stream)
+        native_lib.decode_fwd(args)  # warm-up outside the capture
+        side.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            native_lib.decode_fwd(args)
+    o.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    assert_close(o, expect, "graph replay")
+    q.copy_(torch.roll(q, 1, dims=1))  # new query, same graph
+    g.replay()
+    torch.cuda.synchronize()
+    expect2 = oracle.attn_cpu(q.cpu(), *w.make("cpu")[1:])
+    assert_close(o, expect2, "graph replay with new q")
