@@ -4,16 +4,29 @@
 // Shape: 128 query heads share one KV head whose rows hold 576 values; V is the first 512 of them
 // (the reference runs this shape through its generic kernel, one CTA per query head:
 // csrc/kernel/decoding_attn/decoding_fwd_hd576_hdv512.cu:9-17, so every K row is fetched 128
-// times).  Here the 128 heads are the M dimension of two dense contractions per key tile:
-//     S[128 x N]   = Q[128 x 576] . K_tile[N x 576]^T          (both operands K-major)
-//     O[128 x 256] += P[128 x N]  . V_tile[N x 256]             (V = the same smem tile, MN-major)
+// times).  Here the 128 heads are the M dimension of two dense contractions per 64-key tile:
+//     S[128 x 64]   = Q[128 x 576] . K_tile[64 x 576]^T         (both operands K-major)
+//     O[128 x 256] += P[128 x 64]  . V_tile[64 x 256]            (V = the same smem bytes, MN-major)
 // TMEM holds 128 lanes x 512 fp32 columns, which the 128 x 512 output alone would fill, so one CTA
-// owns one half of the output columns (256 TMEM columns) plus two S buffers; the two CTAs of a
-// (sequence, key range) each compute S themselves and never talk to each other.
+// owns one half of the output columns (256 TMEM columns); the two CTAs of a (sequence, key range)
+// each compute S themselves and never talk to each other.
+//
+// An M=128 tcgen05.mma step costs the same for N = 64 keys as for N = 32, so tiles are 64 keys.  A
+// 64-key tile is 72 KB and Q is 144 KB, more than shared memory holds twice over, hence:
+//   * Q: four 64-column blocks live in TMEM (A operand read from TMEM), five in shared memory;
+//   * P never touches shared memory: it is written over its own S columns in TMEM (16-bit pairs)
+//     and read from there as the A operand of P.V;
+//   * K tiles are not staged whole.  Of the nine 64-column blocks of a tile only the four that make
+//     up this CTA's half of V are needed again for P.V; they go to a ring of three 32 KB slots.  The
+//     other five are dead once S has consumed them and stream through a ring of six 8 KB slots,
+//     each released by a tcgen05.commit right after its four MMAs.
+// TMEM columns: S0 | S1 (64 each, P aliased) | O (256) | Q (4 x 32).
 //
 // Warp roles (192 threads): warps 0-3 = softmax/epilogue, thread r owns TMEM lane r = head r, so
 // row maxima, sums and the rare rescale of O need no cross-thread traffic; warp 4 = TMA producer;
-// warp 5 = TMEM allocation and MMA issue (one elected lane).
+// warp 5 = TMEM allocation and MMA issue (one elected lane).  The MMA pipe executes in issue
+// order S(0) S(1) PV(0) S(2) PV(1) ..., which is what makes the S/P aliasing safe: S(t+2) is issued
+// after PV(t), and PV(t) after the softmax threads have replaced S(t) by P(t).
 // Online softmax with a lazy reference: the running reference max m_ref of a row is only raised
 // when a score exceeds it by more than 8 (log2 domain), so O is rescaled a handful of times.
 // Every wait is bounded; on expiry the CTA records kStatusWaitTimeout and still frees its TMEM.
@@ -29,34 +42,36 @@ constexpr int kHeads = 128;       // M of both contractions
 constexpr int kDim = 576;         // K of S = Q K^T
 constexpr int kDimV = 512;
 constexpr int kHalfV = 256;       // output columns per CTA
-#ifndef DA_MLA_TILE
-#define DA_MLA_TILE 32
-#endif
-constexpr int kTile = DA_MLA_TILE;                // keys per tile (N of S, K of O): 32 or 64
-constexpr int kStages = kTile == 32 ? 4 : 2;      // K tiles in flight
-constexpr int kSBufs = kTile == 32 ? 2 : 1;       // S accumulators in TMEM (64 columns in total)
-constexpr int kQTmemBlocks = 6;   // column blocks of Q kept in TMEM (A operand read from TMEM)
-constexpr int kQSmemBlocks = 3;   // the remaining ones stay in shared memory
+constexpr int kTile = 64;         // keys per tile (N of S, K of O)
 constexpr int kBlocks = kDim / 64;                    // 64-element (128-byte) column blocks of a row
+constexpr int kVBlocks = 4;                           // blocks of a tile that are this CTA's V columns
+constexpr int kABlocks = kBlocks - kVBlocks;          // blocks only S needs
+constexpr int kQTmemBlocks = 4;   // Q blocks kept in TMEM: those that meet the first four streamed blocks
+constexpr int kQSmemBlocks = kBlocks - kQTmemBlocks;
 constexpr int kQBlockBytes = kHeads * 128;            // 16 KB: [128 heads x 64 dims], 128B-swizzled
-constexpr int kKBlockBytes = kTile * 128;             // [kTile keys x 64 dims], 128B-swizzled
-constexpr int kKStageBytes = kBlocks * kKBlockBytes;
-constexpr int kPBytes = kHeads * kTile * 2;           // core-matrix (no swizzle) K-major
+constexpr int kKBlockBytes = kTile * 128;             // 8 KB: [64 keys x 64 dims], 128B-swizzled
+constexpr int kASlots = 6;                            // ring of streamed blocks
+constexpr int kVSlots = 3;                            // ring of V quarter-tiles
+constexpr int kVSlotBytes = kVBlocks * kKBlockBytes;
 constexpr int kOffQ = 0;
-constexpr int kOffK = kOffQ + kQSmemBlocks * kQBlockBytes;
-constexpr int kOffP = kOffK + kStages * kKStageBytes;
-constexpr int kOffBar = kOffP + 2 * kPBytes;
-// q_full, q_tmem, k_full/k_empty[kStages], s_full[2], s_empty[2], p_full[2], pv_done[2]
-constexpr int kNumBars = 2 + 2 * kStages + 2 + 2 + 2 + 2;
+constexpr int kOffA = kOffQ + kQSmemBlocks * kQBlockBytes;
+constexpr int kOffV = kOffA + kASlots * kKBlockBytes;
+constexpr int kOffBar = kOffV + kVSlots * kVSlotBytes;
+// q_full, q_tmem, a_full/a_empty[kASlots], v_full/v_empty[kVSlots], s_full[2], p_full[2], pv_done[2]
+constexpr int kNumBars = 2 + 2 * kASlots + 2 * kVSlots + 2 + 2 + 2;
 constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16 + 1024;  // + tmem slot/abort flag + alignment slack
 constexpr int kThreads = 192;
 constexpr int kTmemCols = 512;
-constexpr int kColS = 0;      // kSBufs S buffers of kTile columns
-constexpr int kColO = 64;     // 256 output columns
-constexpr int kColQ = 320;    // kQTmemBlocks * 32 columns: Q as packed 16-bit pairs, row r in lane r
-static_assert(kColQ + kQTmemBlocks * 32 <= kTmemCols && kQTmemBlocks + kQSmemBlocks == kBlocks, "TMEM / Q split");
+constexpr int kColS = 0;      // two S buffers of kTile columns; P(t) overwrites the first half of S(t)
+constexpr int kColO = 128;    // 256 output columns
+constexpr int kColQ = 384;    // kQTmemBlocks * 32 columns: Q as packed 16-bit pairs, row r in lane r
+static_assert(kColQ + kQTmemBlocks * 32 <= kTmemCols, "TMEM budget");
 static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 constexpr float kRescaleThreshold = 8.0f;
+
+// Column block of the j-th streamed block (j < kABlocks) and of the j-th V block for output half h.
+__device__ __forceinline__ int a_block(int h, int j) { return j < 4 ? (h ? j : 4 + j) : 8; }
+__device__ __forceinline__ int v_block(int h, int j) { return 4 * h + j; }
 
 #ifdef DA_MLA_PROFILE
 // Development aid (not compiled into the shipped library): cycles CTA (0,0,0) spends in each wait.
@@ -70,9 +85,24 @@ __device__ long long g_mla_prof[64];
 #define PROF_END(slot)
 #endif
 
-struct MlaParams {
-    SplitParams sp;  // q/k/o pointers, strides, split geometry, scale, status
-};
+// One [64 keys x 64 dims] block of the latent cache into a 128-byte-swizzled 8 KB slot.  Whole
+// tiles go by TMA (lane 0 issues; the bytes are counted on `bar`, whose expect_tx the caller has
+// posted); a ragged last tile is read with plain loads, rows past the end zeroed, because the
+// tensor map must not be asked for rows beyond the sequence.
+template <typename T>
+__device__ __forceinline__ void load_block(uint8_t *dst, const CUtensorMap *tm, const T *k_g, size_t k_row_stride, int block,
+                                           size_t tok0, int rows, uint64_t *bar, int lane) {
+    if (rows == kTile) {
+        if (lane == 0) tma_load_2d(dst, tm, block * 64, (int)tok0, bar);
+    } else {
+        for (int i = lane; i < kTile * 8; i += 32) {
+            const int r = i >> 3, cc = i & 7;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (r < rows) v = *reinterpret_cast<const uint4 *>(k_g + (tok0 + r) * k_row_stride + block * 64 + cc * 8);
+            *reinterpret_cast<uint4 *>(dst + r * 128 + ((cc ^ (r & 7)) << 4)) = v;
+        }
+    }
+}
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -105,16 +135,17 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
     const int n_tiles = (k_end - k_begin + kTile - 1) / kTile;
 
     uint8_t *q_s = smem + kOffQ;
-    uint8_t *k_s = smem + kOffK;
-    uint8_t *p_s = smem + kOffP;
+    uint8_t *a_s = smem + kOffA;
+    uint8_t *v_s = smem + kOffV;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBar);
     uint64_t *q_full = bars;
     uint64_t *q_tmem = bars + 1;
-    uint64_t *k_full = bars + 2;
-    uint64_t *k_empty = k_full + kStages;
-    uint64_t *s_full = k_empty + kStages;
-    uint64_t *s_empty = s_full + 2;
-    uint64_t *p_full = s_empty + 2;
+    uint64_t *a_full = bars + 2;
+    uint64_t *a_empty = a_full + kASlots;
+    uint64_t *v_full = a_empty + kASlots;
+    uint64_t *v_empty = v_full + kVSlots;
+    uint64_t *s_full = v_empty + kVSlots;
+    uint64_t *p_full = s_full + 2;
     uint64_t *pv_done = p_full + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kNumBars);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -122,13 +153,16 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
     if (tid == 0) {
         mbar_init(q_full, 1);
         mbar_init(q_tmem, kHeads);
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(&k_full[s], 1);
-            mbar_init(&k_empty[s], 1);
+        for (int s = 0; s < kASlots; ++s) {
+            mbar_init(&a_full[s], 1);
+            mbar_init(&a_empty[s], 1);
+        }
+        for (int s = 0; s < kVSlots; ++s) {
+            mbar_init(&v_full[s], 1);
+            mbar_init(&v_empty[s], 1);
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&s_full[s], 1);
-            mbar_init(&s_empty[s], kHeads);
             mbar_init(&p_full[s], kHeads);
             mbar_init(&pv_done[s], 1);
         }
@@ -151,42 +185,56 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
         if (lane == 0) {
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_k);
+            // Q blocks for shared memory: slot 0 meets the last streamed block, slots 1-4 the V blocks.
             mbar_arrive_expect_tx(q_full, kQSmemBlocks * kQBlockBytes);
-            for (int kb = 0; kb < kQSmemBlocks; ++kb) {
-                tma_load_tile_3d(q_s + kb * kQBlockBytes, &tm_q, (kQTmemBlocks + kb) * 64, 0, b, q_full);
+            tma_load_tile_3d(q_s, &tm_q, a_block(half, kABlocks - 1) * 64, 0, b, q_full);
+            for (int j = 0; j < kVBlocks; ++j) {
+                tma_load_tile_3d(q_s + (1 + j) * kQBlockBytes, &tm_q, v_block(half, j) * 64, 0, b, q_full);
             }
         }
         const T *k_g = reinterpret_cast<const T *>(p.k);
+        int a_slot = 0;
+        uint32_t a_round = 0;  // how many times the streamed ring has wrapped
         PROF_DECL;
         for (int t = 0; t < n_tiles && ok; ++t) {
-            const int st = t % kStages;
-            const uint32_t ph = (uint32_t)(t / kStages) & 1u;
             const int key0 = k_begin + t * kTile;
             const int rows = min(kTile, k_end - key0);
             const size_t tok0 = (size_t)seq_begin + key0;
+            const bool whole = rows == kTile;
+            // V quarter-tile first: its slot was released three tiles ago.
+            const int vs = t % kVSlots;
             PROF_BEGIN();
-            if (t >= kStages) ok = mbar_wait(&k_empty[st], ph ^ 1u, abort_flag);
+            if (t >= kVSlots) ok = mbar_wait(&v_empty[vs], ((uint32_t)(t / kVSlots) & 1u) ^ 1u, abort_flag);
             PROF_END(0);
             if (!ok) break;
-            uint8_t *dst = k_s + st * kKStageBytes;
-            if (rows == kTile) {
-                if (lane == 0) {
-                    mbar_arrive_expect_tx(&k_full[st], kKStageBytes);
-                    for (int kb = 0; kb < kBlocks; ++kb) tma_load_2d(dst + kb * kKBlockBytes, &tm_k, kb * 64, (int)tok0, &k_full[st]);
-                }
-            } else {
-                // Ragged tail: plain loads into the 128-byte-swizzled layout, rows past the end zeroed
-                // (the tensor map must not be asked for rows beyond the sequence).
-                for (int i = lane; i < kTile * (kDim / 8); i += 32) {
-                    const int r = i / (kDim / 8), c = i % (kDim / 8);
-                    uint4 v = make_uint4(0, 0, 0, 0);
-                    if (r < rows) v = *reinterpret_cast<const uint4 *>(k_g + (tok0 + r) * p.k_row_stride + c * 8);
-                    const int kb = c >> 3, cc = c & 7;
-                    *reinterpret_cast<uint4 *>(dst + kb * kKBlockBytes + r * 128 + ((cc ^ (r & 7)) << 4)) = v;
-                }
+            if (whole && lane == 0) mbar_arrive_expect_tx(&v_full[vs], kVSlotBytes);
+            for (int j = 0; j < kVBlocks; ++j) {
+                load_block<T>(v_s + vs * kVSlotBytes + j * kKBlockBytes, &tm_k, k_g, p.k_row_stride, v_block(half, j), tok0,
+                              rows, &v_full[vs], lane);
+            }
+            if (!whole) {
                 fence_proxy_async();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&k_full[st]);
+                if (lane == 0) mbar_arrive(&v_full[vs]);
+            }
+            // then the five streamed blocks, each into the next slot of the ring
+            for (int j = 0; j < kABlocks && ok; ++j) {
+                PROF_BEGIN();
+                if (a_round > 0) ok = mbar_wait(&a_empty[a_slot], (a_round & 1u) ^ 1u, abort_flag);
+                PROF_END(1);
+                if (!ok) break;
+                if (whole && lane == 0) mbar_arrive_expect_tx(&a_full[a_slot], kKBlockBytes);
+                load_block<T>(a_s + a_slot * kKBlockBytes, &tm_k, k_g, p.k_row_stride, a_block(half, j), tok0, rows,
+                              &a_full[a_slot], lane);
+                if (!whole) {
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&a_full[a_slot]);
+                }
+                if (++a_slot == kASlots) {
+                    a_slot = 0;
+                    ++a_round;
+                }
             }
             __syncwarp();
         }
@@ -194,78 +242,86 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
         // ---------------- MMA issuer ----------------
         {
             const uint32_t leader = elect_one();
-            const uint32_t q_addr = smem_u32(q_s), k_addr = smem_u32(k_s), p_addr = smem_u32(p_s);
-            // Descriptors differ from tile to tile only in their start-address field (low 14 bits, in
-            // 16-byte units): build them once and add constant offsets, so that the unrolled issue
-            // sequence is one add per operand and the MMA itself.  (A single thread issues these;
-            // every extra dependent instruction here is tensor-pipe idle time.)
-            const uint64_t q_desc0 = smem_desc(q_addr, 16, 1024, 2);
-            const uint64_t k_desc0 = smem_desc(k_addr, 16, 1024, 2);
-            const uint64_t v_desc0 = smem_desc(k_addr + (half * 4) * kKBlockBytes, kKBlockBytes, 1024, 2);
-            const uint64_t p_desc0 = smem_desc(p_addr, kHeads * 16, 128, 0);
+            // Descriptors differ from slot to slot only in their start-address field (low 14 bits, in
+            // 16-byte units): build them once and add offsets, so that the unrolled issue sequence is
+            // one add per operand and the MMA itself.  (A single thread issues these; every extra
+            // dependent instruction here is tensor-pipe idle time.)
+            const uint64_t q_desc0 = smem_desc(smem_u32(q_s), 16, 1024, 2);
+            const uint64_t a_desc0 = smem_desc(smem_u32(a_s), 16, 1024, 2);
+            const uint64_t vk_desc0 = smem_desc(smem_u32(v_s), 16, 1024, 2);            // V slot as K-major rows (for S)
+            const uint64_t vn_desc0 = smem_desc(smem_u32(v_s), kKBlockBytes, 1024, 2);  // V slot MN-major (for P.V)
             const uint32_t q_tmem_addr = tmem_base + kColQ;
-            auto issue_qk = [&](int t) {
-                const uint64_t kd = k_desc0 + (uint64_t)(((t % kStages) * kKStageBytes) >> 4);
-                const uint32_t d = tmem_base + kColS + (t % kSBufs) * kTile;
+            int a_slot = 0;
+            uint32_t a_round = 0;
+            PROF_DECL;
+            auto issue_qk = [&](int t) -> bool {
+                const uint32_t d = tmem_base + kColS + (t & 1) * kTile;
 #pragma unroll
-                for (int kb = 0; kb < kBlocks; ++kb) {
+                for (int j = 0; j < kABlocks; ++j) {
+                    PROF_BEGIN();
+                    if (!mbar_wait(&a_full[a_slot], a_round & 1u, abort_flag)) return false;
+                    PROF_END(10);
+                    tc_fence_after();
+                    const uint64_t bd = a_desc0 + (uint64_t)((a_slot * kKBlockBytes) >> 4);
 #pragma unroll
                     for (int ks = 0; ks < 4; ++ks) {
-                        const uint64_t bd = kd + (uint64_t)((kb * kKBlockBytes + ks * 32) >> 4);
-                        if (kb < kQTmemBlocks) {
-                            umma_ts(d, q_tmem_addr + kb * 32 + ks * 8, bd, kIdescQK, (kb | ks) ? 1u : 0u, leader);
+                        if (j < kQTmemBlocks) {
+                            umma_ts(d, q_tmem_addr + j * 32 + ks * 8, bd + (uint64_t)(ks * 2), kIdescQK, (j | ks) ? 1u : 0u, leader);
                         } else {
-                            umma_ss(d, q_desc0 + (uint64_t)(((kb - kQTmemBlocks) * kQBlockBytes + ks * 32) >> 4), bd,
-                                    kIdescQK, 1u, leader);
+                            umma_ss(d, q_desc0 + (uint64_t)(ks * 2), bd + (uint64_t)(ks * 2), kIdescQK, 1u, leader);
                         }
                     }
+                    umma_commit(&a_empty[a_slot], leader);
+                    if (++a_slot == kASlots) {
+                        a_slot = 0;
+                        ++a_round;
+                    }
                 }
-                umma_commit(&s_full[t % kSBufs], leader);
+                PROF_BEGIN();
+                if (!mbar_wait(&v_full[t % kVSlots], (uint32_t)(t / kVSlots) & 1u, abort_flag)) return false;
+                PROF_END(11);
+                tc_fence_after();
+                const uint64_t vd = vk_desc0 + (uint64_t)(((t % kVSlots) * kVSlotBytes) >> 4);
+#pragma unroll
+                for (int j = 0; j < kVBlocks; ++j) {
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        umma_ss(d, q_desc0 + (uint64_t)(((1 + j) * kQBlockBytes + ks * 32) >> 4),
+                                vd + (uint64_t)((j * kKBlockBytes + ks * 32) >> 4), kIdescQK, 1u, leader);
+                    }
+                }
+                umma_commit(&s_full[t & 1], leader);
+                return true;
             };
-            PROF_DECL;
             PROF_BEGIN();
             ok = mbar_wait(q_full, 0, abort_flag);
             if (ok) ok = mbar_wait(q_tmem, 0, abort_flag);
             PROF_END(8);
-            PROF_BEGIN();
-            if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag);
-            PROF_END(9);
             if (ok) {
                 tc_fence_after();
-                issue_qk(0);
+                ok = issue_qk(0);
             }
             for (int t = 0; t < n_tiles && ok; ++t) {
                 if (t + 1 < n_tiles) {
-                    const int t1 = t + 1;
-                    PROF_BEGIN();
-                    ok = mbar_wait(&k_full[t1 % kStages], (uint32_t)(t1 / kStages) & 1u, abort_flag);
-                    PROF_END(10);
-                    PROF_BEGIN();
-                    if (ok && t1 >= kSBufs) ok = mbar_wait(&s_empty[t1 % kSBufs], ((uint32_t)(t1 / kSBufs) & 1u) ^ 1u, abort_flag);
-                    PROF_END(11);
+                    ok = issue_qk(t + 1);
                     if (!ok) break;
-                    tc_fence_after();
-                    PROF_BEGIN();
-                    issue_qk(t1);
-                    PROF_END(12);
                 }
                 PROF_BEGIN();
                 ok = mbar_wait(&p_full[t & 1], (uint32_t)(t / 2) & 1u, abort_flag);
                 PROF_END(13);
                 if (!ok) break;
                 tc_fence_after();
-                const int st = t % kStages;
+                const int vs = t % kVSlots;
                 const uint32_t d = tmem_base + kColO;
-                // A = P: core matrices of 8 rows x 16 bytes, 8-row groups 128 B apart, 8-key chunks 2 KB apart.
+                // A = P from TMEM: 16 keys = 8 columns of 16-bit pairs per step.
                 // B = V, MN-major: 64-column blocks kKBlockBytes apart (LBO), 8-key groups 1 KB apart (SBO).
-                const uint64_t pd = p_desc0 + (uint64_t)(((t & 1) * kPBytes) >> 4);
-                const uint64_t vd = v_desc0 + (uint64_t)((st * kKStageBytes) >> 4);
+                const uint32_t pa = tmem_base + kColS + (t & 1) * kTile;
+                const uint64_t vd = vn_desc0 + (uint64_t)((vs * kVSlotBytes) >> 4);
 #pragma unroll
                 for (int ks = 0; ks < kTile / 16; ++ks) {
-                    umma_ss(d, pd + (uint64_t)((ks * 2 * (kHeads * 16)) >> 4), vd + (uint64_t)((ks * 16 * 128) >> 4), kIdescPV,
-                            (t | ks) ? 1u : 0u, leader);
+                    umma_ts(d, pa + ks * 8, vd + (uint64_t)((ks * 16 * 128) >> 4), kIdescPV, (t | ks) ? 1u : 0u, leader);
                 }
-                umma_commit(&k_empty[st], leader);
+                umma_commit(&v_empty[vs], leader);
                 umma_commit(&pv_done[t & 1], leader);
             }
         }
@@ -282,16 +338,17 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
         const long long prof_start = clock64();
         (void)prof_start;
         {
-            // Q columns [0, 64 * kQTmemBlocks) of this thread's head go to TMEM as packed 16-bit pairs.
+            // The Q columns that meet the first four streamed blocks go to TMEM as packed 16-bit pairs.
             const T *q_row = reinterpret_cast<const T *>(p.q) + (size_t)b * p.q_row_stride + (size_t)r * kDim;
 #pragma unroll 1
-            for (int kb = 0; kb < kQTmemBlocks; ++kb) {
+            for (int j = 0; j < kQTmemBlocks; ++j) {
+                const T *src = q_row + a_block(half, j) * 64;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const uint4 v = *reinterpret_cast<const uint4 *>(q_row + kb * 64 + j * 8);
-                    buf[4 * j] = v.x, buf[4 * j + 1] = v.y, buf[4 * j + 2] = v.z, buf[4 * j + 3] = v.w;
+                for (int i = 0; i < 8; ++i) {
+                    const uint4 v = *reinterpret_cast<const uint4 *>(src + i * 8);
+                    buf[4 * i] = v.x, buf[4 * i + 1] = v.y, buf[4 * i + 2] = v.z, buf[4 * i + 3] = v.w;
                 }
-                tmem_st32(lane_base + kColQ + kb * 32, buf);
+                tmem_st32(lane_base + kColQ + j * 32, buf);
             }
             tmem_wait_st();
             tc_fence_before();
@@ -300,8 +357,9 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
         for (int t = 0; t < n_tiles; ++t) {
             const int key0 = k_begin + t * kTile;
             const int rows = min(kTile, k_end - key0);
+            const uint32_t s_addr = lane_base + kColS + (t & 1) * kTile;
             PROF_BEGIN();
-            ok = mbar_wait(&s_full[t % kSBufs], (uint32_t)(t / kSBufs) & 1u, abort_flag);
+            ok = mbar_wait(&s_full[t & 1], (uint32_t)(t / 2) & 1u, abort_flag);
             PROF_END(16 + warp);
             if (!ok) break;
             tc_fence_after();
@@ -310,7 +368,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             float mx = -INFINITY;
 #pragma unroll
             for (int c0 = 0; c0 < kTile; c0 += 32) {
-                tmem_ld32(lane_base + kColS + (t % kSBufs) * kTile + c0, buf);
+                tmem_ld32(s_addr + c0, buf);
                 tmem_wait_ld();
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
@@ -319,8 +377,6 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                     mx = fmaxf(mx, s[c0 + j]);
                 }
             }
-            tc_fence_before();
-            mbar_arrive(&s_empty[t % kSBufs]);
             const bool raise = mx > m_ref + kRescaleThreshold;
             float alpha = 1.0f;
             if (raise) {
@@ -329,13 +385,6 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                 l *= alpha;
             }
             PROF_END(20 + warp);
-            PROF_BEGIN();
-            if (t >= 2) {
-                // The P buffer of this tile was last read by the P.V of tile t-2.
-                ok = mbar_wait(&pv_done[t & 1], ((uint32_t)(t / 2) & 1u) ^ 1u, abort_flag);
-                if (!ok) break;
-            }
-            PROF_END(24 + warp);
             PROF_BEGIN();
             if (t >= 1 && __any_sync(0xffffffffu, raise)) {
                 // Rare: the reference max of some row in this warp moved.  O must be idle (P.V of tile
@@ -353,28 +402,26 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                 }
                 tmem_wait_st();
             }
-            // P = exp2(S - m_ref), rounded to the input type, into the A-operand layout.
+            PROF_END(24 + warp);
+            PROF_BEGIN();
+            // P = exp2(S - m_ref), rounded to the input type, packed in pairs over the first half of S(t).
+            // (The tile that used these columns before, t-2, is past its P.V: S(t) was issued after it.)
             float sum = 0.0f;
 #pragma unroll
-            for (int c = 0; c < kTile / 8; ++c) {
-                uint32_t w[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float p0 = exp2f(s[c * 8 + 2 * j] - m_ref), p1 = exp2f(s[c * 8 + 2 * j + 1] - m_ref);
-                    sum += p0 + p1;
-                    if (std::is_same<T, __nv_bfloat16>::value) {
-                        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                        w[j] = *reinterpret_cast<uint32_t *>(&h);
-                    } else {
-                        __half2 h = __floats2half2_rn(p0, p1);
-                        w[j] = *reinterpret_cast<uint32_t *>(&h);
-                    }
+            for (int j = 0; j < kTile / 2; ++j) {
+                const float p0 = exp2f(s[2 * j] - m_ref), p1 = exp2f(s[2 * j + 1] - m_ref);
+                sum += p0 + p1;
+                if (std::is_same<T, __nv_bfloat16>::value) {
+                    __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                    buf[j] = *reinterpret_cast<uint32_t *>(&h);
+                } else {
+                    __half2 h = __floats2half2_rn(p0, p1);
+                    buf[j] = *reinterpret_cast<uint32_t *>(&h);
                 }
-                *reinterpret_cast<uint4 *>(p_s + (t & 1) * kPBytes + c * (kHeads * 16) + r * 16) =
-                    make_uint4(w[0], w[1], w[2], w[3]);
             }
+            tmem_st32(s_addr, buf);
             l += sum;
-            fence_proxy_async();
+            tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&p_full[t & 1]);
             PROF_END(28 + warp);
