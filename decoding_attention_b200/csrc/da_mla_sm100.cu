@@ -74,15 +74,19 @@ __device__ __forceinline__ int a_block(int h, int j) { return j < 4 ? (h ? j : 4
 __device__ __forceinline__ int v_block(int h, int j) { return 4 * h + j; }
 
 #ifdef DA_MLA_PROFILE
-// Development aid (not compiled into the shipped library): cycles CTA (0,0,0) spends in each wait.
+// Development aid (not compiled into the shipped library): cycles the warps of CTA (0,0,0) spend in
+// each wait, accumulated in registers and written out once per role.
 __device__ long long g_mla_prof[64];
-#define PROF_DECL long long prof_t0 = 0; (void)prof_t0
+#define PROF_DECL long long prof_t0 = 0, prof_a0 = 0, prof_a1 = 0, prof_a2 = 0, prof_a3 = 0; (void)prof_t0, (void)prof_a0, (void)prof_a1, (void)prof_a2, (void)prof_a3
 #define PROF_BEGIN() prof_t0 = clock64()
-#define PROF_END(slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0) g_mla_prof[slot] += clock64() - prof_t0; } while (0)
+#define PROF_END(i) prof_a##i += clock64() - prof_t0
+#define PROF_FLUSH(base) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0) { \
+    g_mla_prof[(base)] += prof_a0; g_mla_prof[(base) + 1] += prof_a1; g_mla_prof[(base) + 2] += prof_a2; g_mla_prof[(base) + 3] += prof_a3; } } while (0)
 #else
 #define PROF_DECL
 #define PROF_BEGIN()
-#define PROF_END(slot)
+#define PROF_END(i)
+#define PROF_FLUSH(base)
 #endif
 
 // One [64 keys x 64 dims] block of the latent cache into a 128-byte-swizzled 8 KB slot.  Whole
@@ -238,6 +242,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             }
             __syncwarp();
         }
+        PROF_FLUSH(0);
     } else if (warp == 5) {
         // ---------------- MMA issuer ----------------
         {
@@ -260,7 +265,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                 for (int j = 0; j < kABlocks; ++j) {
                     PROF_BEGIN();
                     if (!mbar_wait(&a_full[a_slot], a_round & 1u, abort_flag)) return false;
-                    PROF_END(10);
+                    PROF_END(1);
                     tc_fence_after();
                     const uint64_t bd = a_desc0 + (uint64_t)((a_slot * kKBlockBytes) >> 4);
 #pragma unroll
@@ -279,7 +284,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                 }
                 PROF_BEGIN();
                 if (!mbar_wait(&v_full[t % kVSlots], (uint32_t)(t / kVSlots) & 1u, abort_flag)) return false;
-                PROF_END(11);
+                PROF_END(2);
                 tc_fence_after();
                 const uint64_t vd = vk_desc0 + (uint64_t)(((t % kVSlots) * kVSlotBytes) >> 4);
 #pragma unroll
@@ -296,7 +301,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             PROF_BEGIN();
             ok = mbar_wait(q_full, 0, abort_flag);
             if (ok) ok = mbar_wait(q_tmem, 0, abort_flag);
-            PROF_END(8);
+            PROF_END(0);
             if (ok) {
                 tc_fence_after();
                 ok = issue_qk(0);
@@ -308,7 +313,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                 }
                 PROF_BEGIN();
                 ok = mbar_wait(&p_full[t & 1], (uint32_t)(t / 2) & 1u, abort_flag);
-                PROF_END(13);
+                PROF_END(3);
                 if (!ok) break;
                 tc_fence_after();
                 const int vs = t % kVSlots;
@@ -324,6 +329,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                 umma_commit(&v_empty[vs], leader);
                 umma_commit(&pv_done[t & 1], leader);
             }
+            PROF_FLUSH(8);
         }
         __syncwarp();
     } else {
@@ -360,7 +366,10 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             const uint32_t s_addr = lane_base + kColS + (t & 1) * kTile;
             PROF_BEGIN();
             ok = mbar_wait(&s_full[t & 1], (uint32_t)(t / 2) & 1u, abort_flag);
-            PROF_END(16 + warp);
+            PROF_END(0);
+#ifdef DA_MLA_PROFILE
+            if (t == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0) g_mla_prof[34] += clock64() - prof_start;
+#endif
             if (!ok) break;
             tc_fence_after();
             PROF_BEGIN();
@@ -384,7 +393,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                 m_ref = mx;
                 l *= alpha;
             }
-            PROF_END(20 + warp);
+            PROF_END(1);
             PROF_BEGIN();
             if (t >= 1 && __any_sync(0xffffffffu, raise)) {
                 // Rare: the reference max of some row in this warp moved.  O must be idle (P.V of tile
@@ -402,7 +411,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                 }
                 tmem_wait_st();
             }
-            PROF_END(24 + warp);
+            PROF_END(2);
             PROF_BEGIN();
             // P = exp2(S - m_ref), rounded to the input type, packed in pairs over the first half of S(t).
             // (The tile that used these columns before, t-2, is past its P.V: S(t) was issued after it.)
@@ -424,14 +433,14 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&p_full[t & 1]);
-            PROF_END(28 + warp);
+            PROF_END(3);
         }
 #ifdef DA_MLA_PROFILE
         if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0) {
             g_mla_prof[32] += clock64() - prof_start;
             g_mla_prof[33] += n_tiles;
         }
-        PROF_BEGIN();
+        PROF_FLUSH(16 + 4 * warp);
 #endif
         if (ok) ok = mbar_wait(&pv_done[(n_tiles - 1) & 1], (uint32_t)((n_tiles - 1) / 2) & 1u, abort_flag);
         if (ok) {
@@ -478,9 +487,6 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             }
             tc_fence_before();
         }
-#ifdef DA_MLA_PROFILE
-        PROF_END(36 + warp);
-#endif
     }
 
     if (!ok && lane == 0) atomicExch(p.status, kStatusWaitTimeout);
