@@ -32,6 +32,8 @@ class DecodeArgs(ctypes.Structure):
         ("kv_pos_offset", ctypes.c_void_p), ("kv_total_len", ctypes.c_void_p),
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
         ("stream", ctypes.c_void_p),
+        ("block_table", ctypes.c_void_p), ("block_table_stride", ctypes.c_int64),
+        ("page_size", ctypes.c_int32), ("reserved1", ctypes.c_int32),
     ]
 
 
@@ -96,8 +98,12 @@ def _ptr(t):
 
 
 def make_args(q, k, v, o, cu_seq_k, max_seq_k, dim_v, is_alibi=False, softmax_scale=None, lse=None, o_f32=None,
-              kv_pos_offset=None, kv_total_len=None, workspace=None, num_splits=0, stream=0, packed=False):
-    """Fill a DecodeArgs from torch tensors (device tensors, or host tensors for the *_host call)."""
+              kv_pos_offset=None, kv_total_len=None, workspace=None, num_splits=0, stream=0, packed=False,
+              block_table=None, page_size=0):
+    """Fill a DecodeArgs from torch tensors (device tensors, or host tensors for the *_host call).
+
+    Paged cache: pass ``block_table`` (int32 [batch, blocks]) and ``page_size``; ``k`` / ``v`` are then the
+    page pools, either [num_pages * page_size, head_k, dim] or [num_pages, page_size, head_k, dim]."""
     import torch
     a = DecodeArgs()
     a.struct_size = ctypes.sizeof(DecodeArgs)
@@ -107,6 +113,9 @@ def make_args(q, k, v, o, cu_seq_k, max_seq_k, dim_v, is_alibi=False, softmax_sc
     a.q, a.k, a.v, a.o, a.cu_seq_k = _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(cu_seq_k)
     a.max_seq_k = int(max_seq_k)
     a.batch = cu_seq_k.numel() - 1
+    if block_table is not None and k.dim() == 4:  # [num_pages, page_size, head_k, dim] -> rows
+        k = k.view(-1, k.shape[2], k.shape[3])
+        v = v.view(-1, v.shape[2], v.shape[3]) if v is not None else None
     a.head_q, a.dim = q.shape[1], q.shape[2]
     a.head_k = k.shape[1]
     a.dim_v = int(dim_v)
@@ -121,6 +130,10 @@ def make_args(q, k, v, o, cu_seq_k, max_seq_k, dim_v, is_alibi=False, softmax_sc
         a.workspace = workspace.data_ptr()
         a.workspace_bytes = workspace.numel() * workspace.element_size()
     a.stream = int(stream) if stream else None
+    if block_table is not None:
+        a.block_table = block_table.data_ptr()
+        a.block_table_stride = block_table.stride(0)
+        a.page_size = int(page_size)
     return a
 
 

@@ -338,6 +338,19 @@ int check_args(const da_decode_args_t *a) {
             return fail(DA_ERR_INVALID_ARG, "row stride %d must be a multiple of 8 elements and cover a row", i);
         }
     }
+    if (a->block_table) {
+        // Every kernel's key tile is 32 or 64 keys; a page must hold whole tiles.
+        if (a->page_size < 64 || (a->page_size & (a->page_size - 1)) != 0) {
+            return fail(DA_ERR_UNSUPPORTED, "page_size %d: paged caches need a power-of-two page size >= 64", a->page_size);
+        }
+        if (a->block_table_stride <= 0) return fail(DA_ERR_INVALID_ARG, "block_table_stride must be positive");
+        if (a->max_seq_k > a->block_table_stride * (int64_t)a->page_size) {
+            return fail(DA_ERR_INVALID_ARG, "block table rows (%lld pages of %d keys) cannot hold max_seq_k = %lld",
+                        (long long)a->block_table_stride, a->page_size, (long long)a->max_seq_k);
+        }
+    } else if (a->page_size != 0 || a->block_table_stride != 0) {
+        return fail(DA_ERR_INVALID_ARG, "page_size / block_table_stride given without a block_table");
+    }
     return DA_OK;
 }
 
@@ -432,6 +445,10 @@ int da_decode_fwd(const da_decode_args_t *a) {
     p.kv_pos_offset = a->kv_pos_offset;
     p.kv_total_len = a->kv_total_len;
     p.status = st->status_ptr;
+    p.block_table = a->block_table;
+    p.block_table_stride = a->block_table_stride;
+    p.page_shift = 0;
+    for (int ps = a->page_size; ps > 1; ps >>= 1) ++p.page_shift;
     p.q_row_stride = a->q_row_stride ? a->q_row_stride : a->head_q * a->dim;
     p.k_row_stride = a->k_row_stride ? a->k_row_stride : a->head_k * a->dim;
     p.v_row_stride = a->v ? (a->v_row_stride ? a->v_row_stride : a->head_k * a->dim_v) : p.k_row_stride;
@@ -452,6 +469,9 @@ int da_decode_fwd(const da_decode_args_t *a) {
     }
     if ((int64_t)p.head_k * p.head_chunks > 65535) {
         return fail(DA_ERR_INVALID_ARG, "head_k * head chunks exceeds the grid limit");
+    }
+    if (a->block_table && a->page_size % plan.tile_keys != 0) {
+        return fail(DA_ERR_UNSUPPORTED, "page_size %d is not a multiple of the %d-key tile", a->page_size, plan.tile_keys);
     }
 
     const bool bf16 = a->is_bf16 != 0;
@@ -549,8 +569,8 @@ int da_decode_fwd_host(const da_decode_args_t *h) {
     int rc = check_args(h);
     if (rc != DA_OK) return rc;
     if (!h->o) return fail(DA_ERR_INVALID_ARG, "o must be given");
-    if (h->o_f32 || h->kv_pos_offset || h->kv_total_len || h->workspace) {
-        return fail(DA_ERR_INVALID_ARG, "o_f32, kv_pos_offset, kv_total_len and workspace are device-only fields");
+    if (h->o_f32 || h->kv_pos_offset || h->kv_total_len || h->workspace || h->block_table) {
+        return fail(DA_ERR_INVALID_ARG, "o_f32, kv_pos_offset, kv_total_len, workspace and block_table are device-only fields");
     }
     if (h->q_row_stride || h->k_row_stride || h->v_row_stride || h->o_row_stride) {
         return fail(DA_ERR_INVALID_ARG, "host tensors must be packed (row strides 0)");

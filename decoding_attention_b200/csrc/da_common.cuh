@@ -30,6 +30,9 @@ struct SplitParams {
     const int *kv_pos_offset;  // optional [batch]: position of key 0 inside a longer sequence (ALiBi)
     const int *kv_total_len;   // optional [batch]: length of that longer sequence (ALiBi)
     int *status;               // device status word
+    const int *block_table;    // optional [batch, block_table_stride]: page of each page_size-key block (paged cache)
+    long long block_table_stride;
+    int page_shift;            // log2(page_size); pages hold a whole number of key tiles
     long long q_row_stride, k_row_stride, v_row_stride, o_row_stride;  // in elements
     int head_q, head_k;
     int group;         // query heads per KV head
@@ -41,6 +44,15 @@ struct SplitParams {
     int use_tmap;      // full tiles are fetched with one tiled TMA copy through the tensor maps
     float scale_log2;  // softmax scale * log2(e)
 };
+
+// Row of the cache that holds key `key0` of sequence `b` (key0 is a multiple of the key tile).  Packed
+// cache: the sequence's rows are consecutive from cu_seq_k[b].  Paged cache: the block table names
+// the page; a tile never straddles two pages because the page size is a multiple of the tile.
+__device__ __forceinline__ size_t kv_tile_row(const SplitParams &p, int b, int seq_begin, int key0) {
+    if (!p.block_table) return (size_t)seq_begin + key0;
+    const int page = p.block_table[(size_t)b * p.block_table_stride + (key0 >> p.page_shift)];
+    return ((size_t)page << p.page_shift) + (key0 & ((1 << p.page_shift) - 1));
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

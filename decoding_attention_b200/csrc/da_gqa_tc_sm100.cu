@@ -169,7 +169,7 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             const uint32_t ph = (uint32_t)(t / kStages) & 1u;
             const int key0 = k_begin + t * kTile;
             const int rows = min(kTile, k_end - key0);
-            const size_t tok0 = (size_t)seq_begin + key0;
+            const size_t tok0 = kv_tile_row(p, b, seq_begin, key0);
             if (t >= kStages) ok = mbar_wait(&kv_empty[st], ph ^ 1u, abort_flag);
             if (!ok) break;
             uint8_t *kd = k_s + st * kKStageBytes, *vd = v_s + st * kKStageBytes;

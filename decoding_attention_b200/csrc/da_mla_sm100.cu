@@ -203,7 +203,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
         for (int t = 0; t < n_tiles && ok; ++t) {
             const int key0 = k_begin + t * kTile;
             const int rows = min(kTile, k_end - key0);
-            const size_t tok0 = (size_t)seq_begin + key0;
+            const size_t tok0 = kv_tile_row(p, b, seq_begin, key0);
             const bool whole = rows == kTile;
             // V quarter-tile first: its slot was released three tiles ago.
             const int vs = t % kVSlots;

@@ -197,7 +197,7 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
             const uint32_t ph = (uint32_t)(t / STAGES) & 1u;
             const int key0 = k_begin + t * TILE;
             const int rows = min(TILE, k_end - key0);
-            const size_t tok0 = (size_t)seq_begin + key0;
+            const size_t tok0 = kv_tile_row(p, b, seq_begin, key0);
             if (t >= STAGES) ok = mbar_wait(&empty_k[st], ph ^ 1u, abort_flag);
             if (!ok) break;
             const bool whole = p.use_tmap && rows == TILE;  // a partial tile must not read past the sequence

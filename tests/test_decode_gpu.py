@@ -244,3 +244,77 @@ def test_cuda_graph_replay(native_lib, oracle):
     torch.cuda.synchronize()
     expect2 = oracle.attn_cpu(q.cpu(), *w.make("cpu")[1:])
     assert_close(o, expect2, "graph replay with new q")
+
+
+def to_pages(k, v, cu, page_size, seed):
+    """Scatter a packed cache into a shuffled page pool whose unused rows are NaN (a kernel that reads
+    a row it should not turns the output NaN).  Returns (k_pool, v_pool, block_table)."""
+    g = torch.Generator().manual_seed(seed)
+    lens = (cu[1:] - cu[:-1]).tolist()
+    blocks = [(n + page_size - 1) // page_size for n in lens]
+    n_pages = sum(blocks) + 2
+    order = torch.randperm(n_pages, generator=g).tolist()
+    k_pool = torch.full((n_pages, page_size) + tuple(k.shape[1:]), float("nan"), dtype=k.dtype)
+    v_pool = torch.full((n_pages, page_size) + tuple(v.shape[1:]), float("nan"), dtype=v.dtype) if v is not None else None
+    table = torch.zeros(len(lens), max(max(blocks), 1) + 1, dtype=torch.int32)
+    nxt = 0
+    for b, n in enumerate(lens):
+        for i in range(blocks[b]):
+            page = order[nxt]
+            nxt += 1
+            table[b, i] = page
+            lo = int(cu[b]) + i * page_size
+            hi = min(lo + page_size, int(cu[b]) + n)
+            k_pool[page, :hi - lo] = k[lo:hi]
+            if v is not None:
+                v_pool[page, :hi - lo] = v[lo:hi]
+    return k_pool, v_pool, table
+
+
+PAGED = [
+    # dtype, head_q, head_k, dim, dim_v, lens, page_size, alibi, splits
+    (torch.bfloat16, 32, 8, 128, 128, [700, 64, 1, 129, 0], 64, False, 0),     # CUDA-core kernel, 4 heads per CTA
+    (torch.float16, 32, 8, 128, 128, [700, 64, 1, 129], 128, True, 3),
+    (torch.float16, 16, 16, 64, 64, [333, 1000], 128, False, 0),
+    (torch.bfloat16, 8, 4, 96, 96, [257, 31], 256, False, 2),
+    (torch.float16, 8, 2, 256, 256, [100, 400], 64, False, 0),                # 32-key tiles
+    (torch.float16, 32, 1, 128, 128, [300, 2048, 65], 64, True, 0),            # tensor-core GQA kernel
+    (torch.bfloat16, 128, 1, 576, 512, [500, 64, 1000, 1], 64, False, 0),      # tensor-core MLA kernel
+    (torch.bfloat16, 128, 1, 576, 512, [900, 130], 128, False, 2),
+    (torch.float16, 16, 1, 576, 512, [200, 70], 64, False, 0),                 # CUDA-core MLA kernel
+]
+
+
+@pytest.mark.parametrize("dt,hq,hk,d,dv,lens,page,alibi,splits", PAGED)
+def test_paged_cache(native_lib, oracle, dt, hq, hk, d, dv, lens, page, alibi, splits):
+    """Paged input (block table + page pool) gives what the packed cache gives: the oracle runs on the
+    packed tensors, the library on a shuffled pool with NaN in every row no sequence owns."""
+    mla = d == 576
+    w = synth.Workload(f"paged_{d}_{page}", dt, hq, hk, d, dv, lens, is_alibi=alibi, dist="normal", scale=0.4, mla=mla, seed=77)
+    q, k, v, cu = w.make("cpu")
+    expect, lse_e = oracle.attn_cpu(q, k, v, cu, dim_v=dv, is_alibi=alibi, return_lse=True)
+    k_pool, v_pool, table = to_pages(k, v, cu, page, seed=page + d)
+    o = torch.full((len(lens), hq, dv), float("nan"), dtype=dt, device=DEV)
+    lse = torch.empty(len(lens), hq, dtype=torch.float32, device=DEV)
+    args = native_lib.make_args(q.to(DEV), k_pool.to(DEV), v_pool.to(DEV) if v_pool is not None else None, o, cu.to(DEV),
+                                max(w.max_seq_k, 1), dv, is_alibi=alibi, lse=lse, num_splits=splits,
+                                block_table=table.to(DEV), page_size=page)
+    native_lib.decode_fwd(args)
+    torch.cuda.synchronize()
+    assert native_lib.device_status() == native_lib.DA_OK
+    assert_close(o, expect, w.name)
+    fin = torch.isfinite(lse_e)
+    assert (lse.cpu()[fin] - lse_e[fin]).abs().max().item() <= 2e-3
+    assert torch.equal(torch.isinf(lse.cpu()), ~fin)
+
+
+def test_paged_cache_argument_errors(native_lib):
+    w = synth.Workload("paged_err", torch.float16, 8, 8, 128, 128, [100], seed=3)
+    q, k, v, cu = [t.to(DEV) for t in w.make("cpu")]
+    o = torch.empty(1, 8, 128, dtype=torch.float16, device=DEV)
+    table = torch.zeros(1, 4, dtype=torch.int32, device=DEV)
+    for page in (16, 96):  # too small; not a power of two
+        with pytest.raises(native_lib.DecodingAttnError):
+            native_lib.decode_fwd(native_lib.make_args(q, k, v, o, cu, 100, 128, block_table=table, page_size=page))
+    with pytest.raises(native_lib.DecodingAttnError):  # table rows too short for max_seq_k
+        native_lib.decode_fwd(native_lib.make_args(q, k, v, o, cu, 1000, 128, block_table=table, page_size=64))
