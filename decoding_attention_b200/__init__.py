@@ -9,7 +9,7 @@ __version__ = "0.1.0"
 
 
 def __getattr__(name):
-    if name in ("decoding_attn_fwd", "dmha_fwd", "dmla_fwd", "merge_partials"):
+    if name in ("decoding_attn_fwd", "dmha_fwd", "dmla_fwd", "paged_fwd", "merge_partials"):
         from . import interface
         return getattr(interface, name)
     raise AttributeError(name)

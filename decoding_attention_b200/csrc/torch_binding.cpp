@@ -36,7 +36,8 @@ struct Outputs {
 
 Outputs run(const at::Tensor &q, const at::Tensor &k, const std::optional<at::Tensor> &v_,
             const std::optional<at::Tensor> &o_, const at::Tensor &cu_seq_k, int64_t max_seq_k, int64_t dim_v,
-            bool is_alibi, std::optional<double> softmax_scale, bool want_lse) {
+            bool is_alibi, std::optional<double> softmax_scale, bool want_lse, const at::Tensor *block_table = nullptr,
+            int64_t page_size = 0) {
     auto q_dtype = q.dtype();
     TORCH_CHECK(q_dtype == torch::kFloat16 || q_dtype == torch::kBFloat16,
                 "Decoding-Attention only support FP16 and BF16 data type");
@@ -124,6 +125,15 @@ Outputs run(const at::Tensor &q, const at::Tensor &k, const std::optional<at::Te
     a.dim_v = dim_v;
     a.softmax_scale = softmax_scale.has_value() ? (float)softmax_scale.value() : 0.0f;
     a.stream = stream;
+    if (block_table) {
+        TORCH_CHECK(block_table->dtype() == torch::kInt32, "block_table must have dtype int32");
+        TORCH_CHECK(block_table->is_cuda() && block_table->device() == q.device(), "all tensors must be on one device");
+        TORCH_CHECK(block_table->dim() == 2 && block_table->size(0) == batch && block_table->stride(1) == 1,
+                    "block_table must be [batch, blocks] with a contiguous last dimension");
+        a.block_table = block_table->data_ptr<int32_t>();
+        a.block_table_stride = block_table->stride(0);
+        a.page_size = (int32_t)page_size;
+    }
 
     const int rc = da_decode_fwd(&a);
     TORCH_CHECK(rc == DA_OK, "decoding_attn: ", da_status_string(rc), ": ", da_last_error());
@@ -149,6 +159,29 @@ pybind11::object dmla_fwd(const at::Tensor &q, const at::Tensor &kv, const at::T
                           int64_t dim_v, std::optional<double> softmax_scale, std::optional<at::Tensor> out,
                           bool return_lse) {
     Outputs r = run(q, kv, std::nullopt, out, cu_seq_k, max_seq_k, dim_v, false, softmax_scale, return_lse);
+    if (return_lse) return pybind11::cast(std::make_tuple(r.o, r.lse));
+    return pybind11::cast(r.o);
+}
+
+// Paged cache: k_cache [num_pages, page_size, head_k, dim], v_cache the same with dim_v (or None for the
+// latent-KV shape), block_table int32 [batch, blocks].  No counterpart in the reference's binding; its
+// Python benchmark builds these layouts for the libraries it compares against
+// (benchmarks/python/benchmark_decoding_attn.py:129-151, :182-190).
+pybind11::object paged_fwd(const at::Tensor &q, const at::Tensor &k_cache, std::optional<at::Tensor> v_cache,
+                           const at::Tensor &cu_seq_k, const at::Tensor &block_table, int64_t max_seq_k, int64_t dim_v,
+                           bool is_alibi, std::optional<double> softmax_scale, std::optional<at::Tensor> out,
+                           bool return_lse) {
+    TORCH_CHECK(k_cache.dim() == 4 && k_cache.is_contiguous(), "k_cache must be a contiguous [pages, page_size, head_k, dim]");
+    const int64_t page_size = k_cache.size(1);
+    const at::Tensor k = k_cache.view({-1, k_cache.size(2), k_cache.size(3)});
+    std::optional<at::Tensor> v;
+    if (v_cache.has_value()) {
+        TORCH_CHECK(v_cache->dim() == 4 && v_cache->is_contiguous() && v_cache->size(0) == k_cache.size(0) &&
+                        v_cache->size(1) == page_size,
+                    "v_cache must be a contiguous [pages, page_size, head_k, dim_v] like k_cache");
+        v = v_cache->view({-1, v_cache->size(2), v_cache->size(3)});
+    }
+    Outputs r = run(q, k, v, out, cu_seq_k, max_seq_k, dim_v, is_alibi, softmax_scale, return_lse, &block_table, page_size);
     if (return_lse) return pybind11::cast(std::make_tuple(r.o, r.lse));
     return pybind11::cast(r.o);
 }
@@ -194,6 +227,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("dmla_fwd", &dmla_fwd, "MLA decode (latent KV)", py::arg("q"), py::arg("kv"), py::arg("cu_seq_k"),
           py::arg("max_seq_k"), py::arg("dim_v") = 512, py::arg("softmax_scale") = py::none(),
           py::arg("out") = py::none(), py::arg("return_lse") = false);
+    m.def("paged_fwd", &paged_fwd, "Decode over a paged KV cache", py::arg("q"), py::arg("k_cache"), py::arg("v_cache"),
+          py::arg("cu_seq_k"), py::arg("block_table"), py::arg("max_seq_k"), py::arg("dim_v"), py::arg("is_alibi") = false,
+          py::arg("softmax_scale") = py::none(), py::arg("out") = py::none(), py::arg("return_lse") = false);
     m.def("merge_partials", &merge_partials, "LSE merge of key-range partials", py::arg("part_o"),
           py::arg("part_lse"), py::arg("out_dtype"));
     m.def("launch_count", []() { return da_launch_count(); });

@@ -49,6 +49,26 @@ def dmla_fwd(q, kv, cu_seq_k, max_seq_k, dim_v=512, softmax_scale=None, out=None
     return decoding_attn_cuda.dmla_fwd(q, kv, cu_seq_k, max_seq_k, dim_v, softmax_scale, out, return_lse)
 
 
+def paged_fwd(q, k_cache, v_cache, seq_lens, block_table, max_seq_k=None, dim_v=None, is_alibi=False, softmax_scale=None,
+              out=None, return_lse=False):
+    """Decode attention over a paged KV cache (the layout serving engines keep).
+
+    q [batch, head_q, dim]; k_cache [num_pages, page_size, head_k, dim]; v_cache the same with dim_v, or
+    None for the latent-KV (MLA) shape; seq_lens int32 [batch]; block_table int32 [batch, blocks]: key j
+    of sequence b is row ``j % page_size`` of page ``block_table[b, j // page_size]``.  page_size must be a
+    power of two >= 64.  The reference has no paged entry point; its Python benchmark builds such
+    layouts for the libraries it compares against (benchmarks/python/benchmark_decoding_attn.py:182-190).
+    """
+    cu_seq_k = torch.zeros(seq_lens.numel() + 1, dtype=torch.int32, device=seq_lens.device)
+    cu_seq_k[1:] = torch.cumsum(seq_lens, 0)
+    if max_seq_k is None:
+        max_seq_k = block_table.shape[1] * k_cache.shape[1]
+    if dim_v is None:
+        dim_v = v_cache.shape[-1] if v_cache is not None else 512
+    return decoding_attn_cuda.paged_fwd(q, k_cache, v_cache, cu_seq_k, block_table, max_seq_k, dim_v, is_alibi,
+                                        softmax_scale, out, return_lse)
+
+
 def merge_partials(part_o, part_lse, out_dtype):
     """LSE merge of partial results over disjoint key ranges: part_o fp32 [parts, ..., dim_v]."""
     return decoding_attn_cuda.merge_partials(part_o.contiguous(), part_lse.contiguous(), out_dtype)
