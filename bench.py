@@ -348,7 +348,41 @@ def other_configs(cabi, dev, world, rank, barrier, max_over_ranks, hbm_peak):
                                "20 back-to-back calls, inputs larger than L2"}
         del q, k, v, o
 
+    def paged(name, w, page):
+        """The same workload read through a block table over a shuffled pool of `page`-key pages
+        (device-side scatter of the packed cache; the call is what is timed)."""
+        q, k, v, cu = w.make(dev)
+        blocks = [(n + page - 1) // page for n in w.seq_lens]
+        n_pages = sum(blocks)
+        order = torch.randperm(n_pages, generator=torch.Generator().manual_seed(1234)).to(torch.int32)
+        table = torch.zeros(w.batch, max(blocks), dtype=torch.int32)
+        rows = torch.empty(w.total_k, dtype=torch.int64)  # pool row of every packed row
+        nxt = 0
+        for b, n in enumerate(w.seq_lens):
+            pages = order[nxt:nxt + blocks[b]]
+            nxt += blocks[b]
+            table[b, :blocks[b]] = pages
+            j = torch.arange(n)
+            rows[w.cu[b]:w.cu[b] + n] = pages[j // page].to(torch.int64) * page + j % page
+        rows = rows.to(dev)
+        k_pool = torch.zeros(n_pages * page, w.head_k, w.dim, dtype=w.dtype, device=dev)
+        k_pool[rows] = k
+        v_pool = None
+        if v is not None:
+            v_pool = torch.zeros(n_pages * page, w.head_k, w.dim_v, dtype=w.dtype, device=dev)
+            v_pool[rows] = v
+        del k, v, rows
+        o = torch.empty(w.batch, w.head_q, w.dim_v, dtype=w.dtype, device=dev)
+        args = cabi.make_args(q, k_pool, v_pool, o, cu, w.max_seq_k, w.dim_v, is_alibi=w.is_alibi,
+                              stream=torch.cuda.current_stream().cuda_stream, block_table=table.to(dev), page_size=page)
+        sec, _, _ = time_resident(cabi, args, 20, 3, lambda: None)
+        res[name] = {"us_per_call": round(sec * 1e6, 2), "kv_GBps": round(w.kv_bytes() / sec / 1e9, 1),
+                     "frac_of_hbm_peak": round(w.kv_bytes() / sec / 1e9 / hbm_peak, 4), "page_size": page,
+                     "num_splits": cabi.num_splits(args), "timing": "20 back-to-back calls, inputs larger than L2"}
+
     if world == 1:
+        paged("gqa_bf16_b256_varlen_paged64", synth.config_gqa_varlen(), 64)
+        paged("mla_bf16_b128_sk4096_paged64", synth.config_mla(batch=128), 64)
         one("mha_fp16_b4_sk1024", synth.config_mha_small(), True)
         one("mqa_alibi_fp16_b128_sk2048", synth.config_mqa_alibi(), True)
         for b in (1, 8, 32, 128):
