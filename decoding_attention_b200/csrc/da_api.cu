@@ -289,6 +289,8 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
         if (tiles_per_cta < kMinTiles) tiles_per_cta = kMinTiles;
         if (tiles_per_cta > kMaxTiles) tiles_per_cta = kMaxTiles;
         splits = (tiles_per_unit + tiles_per_cta - 1) / tiles_per_cta;
+        // Between one and two waves the second wave runs nearly empty: rather fill one wave.
+        if (units * splits > slots && units * splits < 2 * slots && slots / units >= 1) splits = slots / units;
     }
     if (splits < 1) splits = 1;
     if (splits > tiles_per_unit) splits = tiles_per_unit;
