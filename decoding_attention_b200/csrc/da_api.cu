@@ -561,7 +561,7 @@ int da_decode_fwd(const da_decode_args_t *a) {
         m.head_q = (int)a->head_q;
         m.chunk_keys = plan.chunk_keys;
         m.is_bf16 = bf16;
-        e = launch_merge(m, stream);
+        e = launch_merge(m, stream, /*overlap=*/true);
         if (e != cudaSuccess) return fail(DA_ERR_CUDA, "merge kernel launch: %s", cudaGetErrorString(e));
     }
     return DA_OK;

@@ -54,6 +54,14 @@ __device__ __forceinline__ size_t kv_tile_row(const SplitParams &p, int b, int s
     return ((size_t)page << p.page_shift) + (key0 & ((1 << p.page_shift) - 1));
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may
+// start while its predecessor in the stream is still running; it must not touch the predecessor's
+// output before pdl_wait() (which returns once the predecessor has finished and flushed).  The
+// predecessor lets the successor's CTAs be scheduled early with pdl_launch_dependents().  Both are
+// no-ops for kernels launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {

@@ -76,6 +76,7 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
+    pdl_launch_dependents();  // the merge kernel may be scheduled behind this grid's last CTAs
     const int split = blockIdx.x;
     const int hk = blockIdx.y;
     const int b = blockIdx.z;

@@ -61,7 +61,7 @@ struct MergeParams {
     long long rows;
     int num_parts, dim_v, head_q, chunk_keys, is_bf16;
 };
-cudaError_t launch_merge(const MergeParams &p, cudaStream_t s);
+cudaError_t launch_merge(const MergeParams &p, cudaStream_t s, bool overlap = false);
 
 void count_launch(int n = 1);
 

@@ -11,6 +11,7 @@ namespace da {
 
 template <typename T>
 __global__ void __launch_bounds__(128) da_merge_kernel(const MergeParams p) {
+    pdl_launch_dependents();  // a successor launched for overlap (the exchange kernel) may be scheduled early
     const int tpr = p.dim_v / 4;  // threads per row, one float4 each
     const int rpb = 128 / tpr;    // rows per block
     const int r_in_blk = threadIdx.x / tpr;
@@ -25,6 +26,7 @@ __global__ void __launch_bounds__(128) da_merge_kernel(const MergeParams p) {
         const int len = p.cu_seq_k[b + 1] - p.cu_seq_k[b];
         n = min(n, (len + p.chunk_keys - 1) / p.chunk_keys);
     }
+    pdl_wait();  // the partials come from the kernel launched just before this one
     const float *lse_row = p.part_lse + row * p.row_stride_lse;
     const float *o_row = p.part_o + row * p.row_stride_o + t * 4;
 
@@ -56,18 +58,26 @@ __global__ void __launch_bounds__(128) da_merge_kernel(const MergeParams p) {
     if (p.lse && t == 0) p.lse[row] = (mx > -INFINITY) ? mx + log2f(wsum) * kLn2 : -INFINITY;
 }
 
-cudaError_t launch_merge(const MergeParams &p, cudaStream_t s) {
+// `overlap`: the launch may begin while the preceding kernel of the stream is still running (programmatic
+// dependent launch); the kernel waits for that kernel's results itself.
+cudaError_t launch_merge(const MergeParams &p, cudaStream_t s, bool overlap) {
     if (p.dim_v % 4 != 0 || p.dim_v > 512 || p.dim_v <= 0) return cudaErrorInvalidValue;
     if (p.rows <= 0) return cudaSuccess;
     const int rpb = 128 / (p.dim_v / 4);
     const long long blocks = (p.rows + rpb - 1) / rpb;
-    if (p.is_bf16) {
-        da_merge_kernel<__nv_bfloat16><<<(unsigned)blocks, 128, 0, s>>>(p);
-    } else {
-        da_merge_kernel<__half><<<(unsigned)blocks, 128, 0, s>>>(p);
-    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)blocks);
+    cfg.blockDim = dim3(128);
+    cfg.stream = s;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = overlap ? 1 : 0;
+    cudaError_t e = p.is_bf16 ? cudaLaunchKernelEx(&cfg, da_merge_kernel<__nv_bfloat16>, p)
+                              : cudaLaunchKernelEx(&cfg, da_merge_kernel<__half>, p);
     count_launch();
-    return cudaGetLastError();
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 }  // namespace da

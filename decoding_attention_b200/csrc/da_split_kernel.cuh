@@ -129,6 +129,7 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
     constexpr int NCH = C::NCH, NCHV = C::NCHV, NV = C::NV, RV = C::RV, REP = C::REP, STAGES = C::STAGES;
     extern __shared__ __align__(128) uint8_t smem[];
 
+    pdl_launch_dependents();  // the merge kernel may be scheduled behind this grid's last CTAs
     const int split = blockIdx.x;
     const int hk = blockIdx.y / p.head_chunks;
     const int hc = blockIdx.y % p.head_chunks;

@@ -48,6 +48,7 @@ __device__ __forceinline__ unsigned *flag_ptr(float *base, const XMergeParams &p
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads) da_xmerge_kernel(const XMergeParams p) {
+    pdl_wait();  // the record comes from the kernel launched just before this one
     const int cta = blockIdx.x, tid = threadIdx.x;
     const long long r0 = (long long)cta * kRowsPerCta;
     const int nrows = (int)min((long long)kRowsPerCta, p.rows - r0);
@@ -178,13 +179,20 @@ extern "C" int da_exchange_merge(const float *rec, void *const *peer_bufs, int32
     p.epoch = epoch;
     const unsigned ctas = (unsigned)((rows + kRowsPerCta - 1) / kRowsPerCta);
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    if (is_bf16) {
-        da_xmerge_kernel<__nv_bfloat16><<<ctas, kThreads, 0, s>>>(p);
-    } else {
-        da_xmerge_kernel<__half><<<ctas, kThreads, 0, s>>>(p);
-    }
+    // Launched for overlap with the preceding kernel of the stream (it waits for that kernel's results itself).
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ctas);
+    cfg.blockDim = dim3(kThreads);
+    cfg.stream = s;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = is_bf16 ? cudaLaunchKernelEx(&cfg, da_xmerge_kernel<__nv_bfloat16>, p)
+                            : cudaLaunchKernelEx(&cfg, da_xmerge_kernel<__half>, p);
     count_launch();
-    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return report_error(DA_ERR_CUDA, cudaGetErrorString(e));
     return DA_OK;
 }
