@@ -111,30 +111,37 @@ def make_call(cabi, w, q, k, v, cu, o, **kw):
 
 
 def time_resident(cabi, args, steps, warmup, barrier, flush=None):
-    """K back-to-back steps between two events (after W warm-ups); also the split kernel alone via the
-    profiling hook.  Returns (seconds per step, seconds per main-kernel launch, launches)."""
+    """K back-to-back steps between two events (after W warm-ups), exactly as a caller would issue them;
+    then, outside the timed region, the same K steps again with the profiling hook, which brackets the
+    main (key-streaming) kernel of every call with its own events.  (The hook's event records sit between
+    the kernels of a call and keep them from overlapping, so it must not run inside the timed region.)
+    Returns (seconds per step, seconds per main-kernel launch, launches in the timed region)."""
     for _ in range(warmup):
         cabi.decode_fwd(args)
-    torch.cuda.synchronize()
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
-    for a, b in ev:  # create the underlying events
-        a.record()
-        b.record()
     torch.cuda.synchronize()
     barrier()
     torch.cuda.synchronize()
     l0 = cabi.launch_count()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0.record()
-    for a, b in ev:
-        cabi.set_profile_events(a, b)
+    for _ in range(steps):
         cabi.decode_fwd(args)
     t1.record()
-    cabi.set_profile_events(None, None)
     torch.cuda.synchronize()
     barrier()
     launches = cabi.launch_count() - l0
     total = t0.elapsed_time(t1) * 1e-3
+
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for a, b in ev:  # create the underlying events
+        a.record()
+        b.record()
+    torch.cuda.synchronize()
+    for a, b in ev:
+        cabi.set_profile_events(a, b)
+        cabi.decode_fwd(args)
+    cabi.set_profile_events(None, None)
+    torch.cuda.synchronize()
     kern = statistics.mean(a.elapsed_time(b) for a, b in ev) * 1e-3
     return total / steps, kern, launches
 
@@ -480,7 +487,7 @@ def run_profile_config(opt):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seqs", type=int, default=SEQS_PER_GPU,

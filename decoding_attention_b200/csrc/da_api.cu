@@ -226,6 +226,7 @@ struct Plan {
     int chunk_keys;
     int tile_keys;
     size_t scratch_bytes;
+    size_t order_offset;  // byte offset of the launch-order array inside the scratch, or 0 if none
 };
 
 // Pick the number of key-range splits.  The host does not know the sequence lengths (cu_seq_k is a
@@ -312,6 +313,15 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
     plan->tile_keys = tile;
     plan->scratch_bytes =
         splits > 1 ? (size_t)a.batch * a.head_q * splits * ((size_t)a.dim_v + 1) * sizeof(float) : 0;
+    // More CTAs than fit at once and enough sequences for their order to matter: launch longest first.
+    const int64_t all_slots = (int64_t)sm_count * (info.ctas_per_sm > 0 ? info.ctas_per_sm : 1);
+    plan->order_offset = 0;
+    // (the order kernel costs 3-4 us: worth it only when a CTA runs long enough for a ragged tail to cost more)
+    if (a.batch >= 16 && units * splits > all_slots && chunk_tiles >= 16 && !getenv("DA_NO_ORDER")) {
+        plan->scratch_bytes = (plan->scratch_bytes + 15) / 16 * 16;
+        plan->order_offset = plan->scratch_bytes + 16;  // never 0
+        plan->scratch_bytes = plan->order_offset + (size_t)a.batch * sizeof(int);
+    }
     return DA_OK;
 }
 
@@ -471,6 +481,12 @@ int da_decode_fwd(const da_decode_args_t *a) {
     p.is_alibi = a->is_alibi ? 1 : 0;
     const float scale = a->softmax_scale > 0.0f ? a->softmax_scale : (float)(1.0 / std::sqrt((double)a->dim));
     p.scale_log2 = scale * kLog2e;
+    if (plan.order_offset) {
+        int *order = reinterpret_cast<int *>(reinterpret_cast<char *>(scratch) + plan.order_offset);
+        cudaError_t oe = launch_order(a->cu_seq_k, (int)a->batch, a->max_seq_k, order, stream);
+        if (oe != cudaSuccess) return fail(DA_ERR_CUDA, "order kernel launch: %s", cudaGetErrorString(oe));
+        p.batch_order = order;
+    }
     if (plan.num_splits > 1) {
         p.part_o = scratch;
         p.part_lse = scratch + (size_t)a->batch * a->head_q * plan.num_splits * a->dim_v;

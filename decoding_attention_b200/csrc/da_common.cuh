@@ -30,6 +30,7 @@ struct SplitParams {
     const int *kv_pos_offset;  // optional [batch]: position of key 0 inside a longer sequence (ALiBi)
     const int *kv_total_len;   // optional [batch]: length of that longer sequence (ALiBi)
     int *status;               // device status word
+    const int *batch_order;    // optional [batch]: sequence handled by grid slice z (longest first), else z itself
     const int *block_table;    // optional [batch, block_table_stride]: page of each page_size-key block (paged cache)
     long long block_table_stride;
     int page_shift;            // log2(page_size); pages hold a whole number of key tiles

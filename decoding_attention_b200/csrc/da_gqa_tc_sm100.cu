@@ -79,7 +79,8 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
     pdl_launch_dependents();  // the merge kernel may be scheduled behind this grid's last CTAs
     const int split = blockIdx.x;
     const int hk = blockIdx.y;
-    const int b = blockIdx.z;
+    if (p.batch_order) pdl_wait();  // written by the order kernel launched just before this one
+    const int b = p.batch_order ? p.batch_order[blockIdx.z] : (int)blockIdx.z;
     const int G = p.group;            // query heads of this KV head: rows 0..G-1 of the tile
     const int h0 = hk * G;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -475,9 +476,9 @@ cudaError_t launch_gqa_tc(bool bf16, const SplitParams &p, const CUtensorMap &tm
     }
     dim3 grid(p.num_splits, p.head_k, p.batch);
     if (bf16) {
-        da_gqa_tc_kernel<__nv_bfloat16><<<grid, kThreads, kSmemBytes, stream>>>(p, tm_q, tm_k, tm_v);
+        return launch_kernel(da_gqa_tc_kernel<__nv_bfloat16>, grid, kThreads, kSmemBytes, stream, p.batch_order != nullptr, p, tm_q, tm_k, tm_v);
     } else {
-        da_gqa_tc_kernel<__half><<<grid, kThreads, kSmemBytes, stream>>>(p, tm_q, tm_k, tm_v);
+        return launch_kernel(da_gqa_tc_kernel<__half>, grid, kThreads, kSmemBytes, stream, p.batch_order != nullptr, p, tm_q, tm_k, tm_v);
     }
     return cudaGetLastError();
 }

@@ -1,5 +1,6 @@
 // Host-side declarations shared by the translation units of libdecoding_attn_b200.so.
 #pragma once
+#include <utility>
 
 #include <cuda_runtime.h>
 
@@ -63,7 +64,30 @@ struct MergeParams {
 };
 cudaError_t launch_merge(const MergeParams &p, cudaStream_t s, bool overlap = false);
 
+// Batch indices sorted by descending sequence length into order[batch] (da_order.cu).
+cudaError_t launch_order(const int *cu_seq_k, int batch, long long max_len, int *order, cudaStream_t s);
+
 void count_launch(int n = 1);
+
+// Launches `kernel`.  With `overlap` the launch may begin while the preceding kernel of the stream is
+// still running (programmatic dependent launch); the kernel then calls pdl_wait() before it reads
+// anything that kernel wrote.
+template <typename... P, typename... A>
+inline cudaError_t launch_kernel(void (*kernel)(P...), dim3 grid, unsigned threads, size_t smem_bytes, cudaStream_t s,
+                                 bool overlap, A &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = s;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = overlap ? 1 : 0;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
+    return e != cudaSuccess ? e : cudaGetLastError();
+}
 
 // Records `msg` as the calling thread's last error (da_last_error) and returns `code`.
 int report_error(int code, const char *msg);

@@ -86,7 +86,7 @@ da_mla_pair_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_k
 
     const uint32_t rank = cluster_ctarank();  // 0 or 1: which half of the output columns / of the contraction
     const int split = blockIdx.y;
-    const int b = blockIdx.z;
+    const int b = p.batch_order ? p.batch_order[blockIdx.z] : (int)blockIdx.z;
     pdl_launch_dependents();  // the merge kernel may be scheduled behind this grid's last CTAs
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int seq_begin = p.cu_seq_k[b];

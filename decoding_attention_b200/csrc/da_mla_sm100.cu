@@ -117,7 +117,8 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
     pdl_launch_dependents();  // the merge kernel may be scheduled behind this grid's last CTAs
     const int split = blockIdx.x;
     const int half = blockIdx.y;  // which 256 output columns
-    const int b = blockIdx.z;
+    if (p.batch_order) pdl_wait();  // written by the order kernel launched just before this one
+    const int b = p.batch_order ? p.batch_order[blockIdx.z] : (int)blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int seq_begin = p.cu_seq_k[b];
     const int len = p.cu_seq_k[b + 1] - seq_begin;
@@ -531,9 +532,9 @@ cudaError_t launch_mla_tc(bool bf16, const SplitParams &p, const CUtensorMap &tm
     }
     dim3 grid(p.num_splits, 2, p.batch);
     if (bf16) {
-        da_mla_tc_kernel<__nv_bfloat16><<<grid, kThreads, kSmemBytes, stream>>>(p, tm_q, tm_k);
+        return launch_kernel(da_mla_tc_kernel<__nv_bfloat16>, grid, kThreads, kSmemBytes, stream, p.batch_order != nullptr, p, tm_q, tm_k);
     } else {
-        da_mla_tc_kernel<__half><<<grid, kThreads, kSmemBytes, stream>>>(p, tm_q, tm_k);
+        return launch_kernel(da_mla_tc_kernel<__half>, grid, kThreads, kSmemBytes, stream, p.batch_order != nullptr, p, tm_q, tm_k);
     }
     return cudaGetLastError();
 }

@@ -133,7 +133,8 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
     const int split = blockIdx.x;
     const int hk = blockIdx.y / p.head_chunks;
     const int hc = blockIdx.y % p.head_chunks;
-    const int b = blockIdx.z;
+    if (p.batch_order) pdl_wait();  // written by the order kernel launched just before this one
+    const int b = p.batch_order ? p.batch_order[blockIdx.z] : (int)blockIdx.z;
     const int h0 = hk * p.group + hc * G;  // first query head of this CTA
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
@@ -483,8 +484,7 @@ cudaError_t launch_split(const SplitParams &p, const CUtensorMap &tm_k, const CU
         attr_set[dev] = true;
     }
     dim3 grid(p.num_splits, p.head_k * p.head_chunks, p.batch);
-    da_split_kernel<C><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(p, tm_k, tm_v);
-    return cudaGetLastError();
+    return launch_kernel(da_split_kernel<C>, grid, C::THREADS, C::SMEM_BYTES, stream, p.batch_order != nullptr, p, tm_k, tm_v);
 }
 
 }  // namespace da
