@@ -108,7 +108,7 @@ int da_decode_fwd_host(const da_decode_args_t *host_args);
  * someone else -- an engine that gave all of HBM to its KV-cache pool, code running where calls
  * into the CUDA allocator are forbidden.  Leave args->workspace NULL.  Returns DA_ERR_WORKSPACE,
  * without launching anything, when the call would need more than the array holds (num_splits = 1
- * never needs scratch).  It calls no cudaMalloc / cudaFree.  The first call on a device looks up
+ * needs at most 4 bytes per sequence and always fits).  It calls no cudaMalloc / cudaFree.  The first call on a device looks up
  * the array's device address (cudaGetSymbolAddress); make that first call outside any stream
  * capture.  All calls on a device share the array, which keeps the previous call's bytes (nothing
  * in it needs clearing): calls that overlap on the GPU race, so keep them on one stream.
@@ -117,7 +117,8 @@ int da_decode_fwd_host(const da_decode_args_t *host_args);
 int da_decode_fwd_static(const da_decode_args_t *args);
 size_t da_static_scratch_bytes(void);
 
-/* Scratch bytes da_decode_fwd needs for these arguments (0 when it will not split).  No reference
+/* Scratch bytes da_decode_fwd needs for these arguments: the split partials (none when it will not
+ * split) plus, for grids of more than one wave, 4 bytes per sequence for the launch order.  No reference
  * counterpart: the reference kernel keeps its only scratch, the score row, in shared memory
  * (decoding_fwd_launch_template.h:14-18). */
 size_t da_decode_workspace_bytes(const da_decode_args_t *args);
