@@ -318,3 +318,23 @@ def test_paged_cache_argument_errors(native_lib):
             native_lib.decode_fwd(native_lib.make_args(q, k, v, o, cu, 100, 128, block_table=table, page_size=page))
     with pytest.raises(native_lib.DecodingAttnError):  # table rows too short for max_seq_k
         native_lib.decode_fwd(native_lib.make_args(q, k, v, o, cu, 1000, 128, block_table=table, page_size=64))
+
+
+@pytest.mark.parametrize("splits", [1, 0])
+def test_longest_first_launch_order(native_lib, oracle, splits):
+    """A grid of more than one wave of long CTAs takes its sequences longest first (a device-side sort of
+    the batch by length): every sequence must still land in its own output row."""
+    g = torch.Generator().manual_seed(99)
+    lens = torch.randint(16, 3000, (64,), generator=g).tolist()
+    lens[5], lens[40] = 0, 2999
+    w = synth.Workload("order", torch.bfloat16, 32, 8, 128, 128, lens, dist="normal", scale=0.5, seed=98)
+    q, k, v, cu = w.make("cpu")
+    dq, dk, dv, dcu = q.to(DEV), k.to(DEV), v.to(DEV), cu.to(DEV)
+    o = torch.full((64, 32, 128), float("nan"), dtype=w.dtype, device=DEV)
+    args = native_lib.make_args(dq, dk, dv, o, dcu, w.max_seq_k, 128, num_splits=splits)
+    if splits == 1:  # partials are not needed, so any scratch is the launch-order array
+        assert native_lib.workspace_bytes(args) >= 64 * 4
+    native_lib.decode_fwd(args)
+    torch.cuda.synchronize()
+    assert native_lib.device_status() == native_lib.DA_OK
+    assert_close(o, oracle.attn_cpu(q, k, v, cu), "longest-first order")
