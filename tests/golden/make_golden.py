@@ -1,6 +1,6 @@
 """Generates tests/golden/*.npz from the reference's own Python attention.
 
-Run in a container that has a checkout of Bruce-Lee-LY/decoding_attention (default /root/reference):
+Run where a checkout of Bruce-Lee-LY/decoding_attention is available (path as the first argument):
 
     python tests/golden/make_golden.py [/path/to/reference]
 
