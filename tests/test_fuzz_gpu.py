@@ -38,7 +38,7 @@ def make_case(seed):
                 splits=r.choice([0, 0, 1, 2, 5]), page=r.choice([0, 0, 64, 128]), pad=r.choice([0, 0, 8, 64]))
 
 
-@pytest.mark.parametrize("seed", range(60))
+@pytest.mark.parametrize("seed", range(150))
 def test_random_case(native_lib, oracle, seed):
     c = make_case(seed)
     w = synth.Workload(f"fuzz{seed}", c["dt"], c["head_q"], c["head_k"], c["dim"], c["dim_v"], c["lens"], is_alibi=c["alibi"],
