@@ -149,7 +149,8 @@ class KeyRangeShardedDecoder:
         return self.merge()
 
     def exchange_merge(self):
-        self.epoch += 1
+        # 1, 2, ..., 2^32 - 2, 1, ...: never 0 (the flags' initial value) and alternating parity across the wrap
+        self.epoch = self.epoch % 0xFFFFFFFE + 1
         self.cabi.check(self.cabi.lib().da_exchange_merge(
             self.rec.data_ptr(), self.peer_ptrs, self.world, self.rank, self.rows, self.dim_v, self.epoch,
             self.out.data_ptr(), self.lse.data_ptr(), int(self.out.dtype == torch.bfloat16),
