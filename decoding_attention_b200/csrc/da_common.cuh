@@ -125,6 +125,18 @@ __device__ __forceinline__ void bulk_copy_g2s_hint(void *dst_smem, const void *s
         "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
         : "memory");
 }
+// 16-byte asynchronous copy global -> shared through the load/store unit (not the TMA engine).  With
+// src_bytes = 0 nothing is read and the 16 bytes are zero-filled.
+__device__ __forceinline__ void cp_async16(void *dst_smem, const void *src_gmem, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst_smem)), "l"(src_gmem), "r"(src_bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 // A whole K/V tile: tiled TMA copy of the box {dim, 1 head, tile rows} at (0, head, row) of the
 // rank-3 tensor map [rows][heads][dim].  One instruction per tile; the engine walks the rows.
 __device__ __forceinline__ void tma_load_tile_3d(void *dst_smem, const CUtensorMap *tmap, int c0, int c1, int c2,

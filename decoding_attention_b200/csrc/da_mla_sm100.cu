@@ -22,9 +22,11 @@
 //     each released by a tcgen05.commit right after its four MMAs.
 // TMEM columns: S0 | S1 (64 each, P aliased) | O (256) | Q (4 x 32).
 //
-// Warp roles (192 threads): warps 0-3 = softmax/epilogue, thread r owns TMEM lane r = head r, so
-// row maxima, sums and the rare rescale of O need no cross-thread traffic; warp 4 = TMA producer;
-// warp 5 = TMEM allocation and MMA issue (one elected lane).  The MMA pipe executes in issue
+// Warp roles (320 threads): warps 0-3 = softmax/epilogue, thread r owns TMEM lane r = head r, so
+// row maxima, sums and the rare rescale of O need no cross-thread traffic; warp 4 = TMA producer
+// (Q and the streamed blocks); warp 5 = TMEM allocation and MMA issue (one elected lane); warps
+// 6-9 = loaders of the V quarter-tiles with 16-byte cp.async, because one SM's TMA engine alone
+// moves only about 21 B/clk.  The MMA pipe executes in issue
 // order S(0) S(1) PV(0) S(2) PV(1) ..., which is what makes the S/P aliasing safe: S(t+2) is issued
 // after PV(t), and PV(t) after the softmax threads have replaced S(t) by P(t).
 // Online softmax with a lazy reference: the running reference max m_ref of a row is only raised
@@ -60,7 +62,9 @@ constexpr int kOffBar = kOffV + kVSlots * kVSlotBytes;
 // q_full, q_tmem, a_full/a_empty[kASlots], v_full/v_empty[kVSlots], s_full[2], p_full[2], pv_done[2]
 constexpr int kNumBars = 2 + 2 * kASlots + 2 * kVSlots + 2 + 2 + 2;
 constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16 + 1024;  // + tmem slot/abort flag + alignment slack
-constexpr int kThreads = 192;
+constexpr int kLoaderWarps = 4;                       // warps that fetch the V quarter-tiles through the load/store unit
+constexpr int kLoaderThreads = kLoaderWarps * 32;
+constexpr int kThreads = 192 + kLoaderThreads;
 constexpr int kTmemCols = 512;
 constexpr int kColS = 0;      // two S buffers of kTile columns; P(t) overwrites the first half of S(t)
 constexpr int kColO = 128;    // 256 output columns
@@ -164,7 +168,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             mbar_init(&a_empty[s], 1);
         }
         for (int s = 0; s < kVSlots; ++s) {
-            mbar_init(&v_full[s], 1);
+            mbar_init(&v_full[s], kLoaderThreads);
             mbar_init(&v_empty[s], 1);
         }
         for (int s = 0; s < 2; ++s) {
@@ -207,23 +211,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             const int rows = min(kTile, k_end - key0);
             const size_t tok0 = kv_tile_row(p, b, seq_begin, key0);
             const bool whole = rows == kTile;
-            // V quarter-tile first: its slot was released three tiles ago.
-            const int vs = t % kVSlots;
-            PROF_BEGIN();
-            if (t >= kVSlots) ok = mbar_wait(&v_empty[vs], ((uint32_t)(t / kVSlots) & 1u) ^ 1u, abort_flag);
-            PROF_END(0);
-            if (!ok) break;
-            if (whole && lane == 0) mbar_arrive_expect_tx(&v_full[vs], kVSlotBytes);
-            for (int j = 0; j < kVBlocks; ++j) {
-                load_block<T>(v_s + vs * kVSlotBytes + j * kKBlockBytes, &tm_k, k_g, p.k_row_stride, v_block(half, j), tok0,
-                              rows, &v_full[vs], lane);
-            }
-            if (!whole) {
-                fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&v_full[vs]);
-            }
-            // then the five streamed blocks, each into the next slot of the ring
+            // the five streamed blocks, each into the next slot of the ring (the V blocks come from the loader warps)
             for (int j = 0; j < kABlocks && ok; ++j) {
                 PROF_BEGIN();
                 if (a_round > 0) ok = mbar_wait(&a_empty[a_slot], (a_round & 1u) ^ 1u, abort_flag);
@@ -334,6 +322,46 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             PROF_FLUSH(8);
         }
         __syncwarp();
+    } else if (warp >= 6) {
+        // ---------------- V loaders: 16-byte cp.async through the load/store unit ----------------
+        // The TMA engine of an SM moves about 21 B/clk (measured with bulk copies, L2-resident source, any
+        // depth); 16-byte loads from many threads reach 85-97 B/clk on the same data.  The four V blocks of
+        // a tile (32 KB of its 72 KB) therefore bypass the TMA engine: 128 threads x 16 cp.async, written
+        // straight into the 128-byte-swizzled layout; a tile is published (wait_group, proxy fence, arrive)
+        // once the next one has been issued, so two are in flight.
+        const int lt = tid - 6 * 32;  // 0..127
+        const T *k_g = reinterpret_cast<const T *>(p.k);
+        PROF_DECL;
+        for (int t = 0; t < n_tiles && ok; ++t) {
+            const int key0 = k_begin + t * kTile;
+            const int rows = min(kTile, k_end - key0);
+            const size_t tok0 = kv_tile_row(p, b, seq_begin, key0);
+            const int vs = t % kVSlots;
+            PROF_BEGIN();
+            if (t >= kVSlots) ok = mbar_wait(&v_empty[vs], ((uint32_t)(t / kVSlots) & 1u) ^ 1u, abort_flag);
+            PROF_END(0);
+            if (!ok) break;
+            uint8_t *slot = v_s + vs * kVSlotBytes;
+#pragma unroll
+            for (int n = 0; n < kVBlocks * kTile * 8 / kLoaderThreads; ++n) {
+                const int i = lt + n * kLoaderThreads;
+                const int j = i >> 9, r = (i >> 3) & 63, cc = i & 7;
+                const T *src = k_g + (tok0 + min(r, rows - 1)) * p.k_row_stride + v_block(half, j) * 64 + cc * 8;
+                cp_async16(slot + j * kKBlockBytes + r * 128 + ((cc ^ (r & 7)) << 4), src, r < rows ? 16u : 0u);  // 0: zero fill
+            }
+            cp_async_commit();
+            PROF_BEGIN();
+            if (t >= 1) {  // the tile issued one iteration ago has landed: publish it to the tensor pipe
+                cp_async_wait<1>();
+                fence_proxy_async();
+                mbar_arrive(&v_full[(t - 1) % kVSlots]);
+            }
+            PROF_END(1);
+        }
+        cp_async_wait<0>();
+        fence_proxy_async();
+        if (ok) mbar_arrive(&v_full[(n_tiles - 1) % kVSlots]);
+        if (warp == 6) PROF_FLUSH(4);
     } else {
         // ---------------- softmax / epilogue: thread r <-> TMEM lane r <-> head r ----------------
         const int r = tid;
