@@ -146,8 +146,9 @@ def time_resident(cabi, args, steps, warmup, barrier, flush=None):
     return total / steps, kern, launches
 
 
-def time_flushed(cabi, args, iters, flush_buf):
-    """Per-call events with an L2-sized write between calls (for working sets that fit in L2)."""
+def time_flushed(cabi, args, iters, flush_buf, spread=None):
+    """Per-call events with an L2-sized write between calls (for working sets that fit in L2).
+    Returns the median; `spread`, if given, receives the 10th and 90th percentiles (seconds)."""
     times = []
     for i in range(iters + 3):
         flush_buf.add_(1)
@@ -158,6 +159,9 @@ def time_flushed(cabi, args, iters, flush_buf):
         torch.cuda.synchronize()
         if i >= 3:
             times.append(a.elapsed_time(b) * 1e-3)
+    times.sort()
+    if spread is not None:
+        spread[:] = [times[len(times) // 10], times[(len(times) * 9) // 10]]
     return statistics.median(times)
 
 
@@ -344,15 +348,18 @@ def other_configs(cabi, dev, world, rank, barrier, max_over_ranks, hbm_peak):
         for _ in range(3):
             cabi.decode_fwd(args)
         torch.cuda.synchronize()
+        spread = []
         if flushed:
-            sec = time_flushed(cabi, args, 20, flush)
+            sec = time_flushed(cabi, args, 50, flush, spread)
         else:
             sec, _, _ = time_resident(cabi, args, 20, 3, lambda: None)
         res[name] = {"us_per_call": round(sec * 1e6, 2), "kv_GBps": round(w.kv_bytes() / sec / 1e9, 1),
                      "frac_of_hbm_peak": round(w.kv_bytes() / sec / 1e9 / hbm_peak, 4),
                      "ref_tflops": round(w.ref_flops() / sec / 1e12, 3), "num_splits": cabi.num_splits(args),
-                     "timing": "median of 20 calls, 256 MB L2 flush between calls" if flushed else
+                     "timing": "median of 50 calls, 256 MB L2 flush between calls" if flushed else
                                "20 back-to-back calls, inputs larger than L2"}
+        if spread:
+            res[name]["us_p10_p90"] = [round(x * 1e6, 2) for x in spread]
         del q, k, v, o
 
     def paged(name, w, page):
