@@ -401,6 +401,9 @@ def other_configs(cabi, dev, world, rank, barrier, max_over_ranks, hbm_peak):
         one("mqa_alibi_fp16_b128_sk2048", synth.config_mqa_alibi(), True)
         for b in (1, 8, 32, 128):
             one(f"mla_bf16_b{b}_sk4096", synth.config_mla(batch=b), b <= 8)
+        # the same latent cache with 16 query heads: one GPU's share of the 128 heads under 8-way tensor parallelism
+        one("mla_bf16_h16_b128_sk4096", synth.Workload("mla_h16", torch.bfloat16, 16, 1, 576, 512, [4096] * 128,
+                                                       dist="normal", scale=0.3, mla=True), False)
 
     # key-range sharded long sequence (strong scaling: 131072 keys in total at every N)
     w = synth.config_long_mha()

@@ -76,11 +76,14 @@ Shape shape_of(int64_t dim, int64_t dim_v, bool has_v) {
     return Shape::kNone;
 }
 
-// The tensor-core kernel covers the shape the latent-KV layout exists for: 128 query heads over one
-// KV head.  Other head counts of (576, 512) run on the CUDA-core kernel.
+// The tensor-core kernel covers the shape the latent-KV layout exists for: up to 128 query heads over
+// one KV head (128 in the full model, 16..64 per GPU under tensor parallelism; the reference's suite
+// runs 16, 32, 64 and 128, tests/test_decoding_attn.py:97).  Fewer than 8 heads, or several KV heads,
+// run on the CUDA-core kernel.  The cluster-pair variant is built for exactly 128 heads.
+bool mla_pair_enabled();
 bool mla_on_tensor_cores(const da_decode_args_t &a) {
-    return a.v == nullptr && a.dim == 576 && a.dim_v == 512 && a.head_q == 128 && a.head_k == 1 &&
-           !getenv("DA_MLA_SIMT");
+    if (a.v != nullptr || a.dim != 576 || a.dim_v != 512 || a.head_k != 1 || getenv("DA_MLA_SIMT")) return false;
+    return a.head_q == 128 || (a.head_q >= 8 && a.head_q < 128 && !mla_pair_enabled());
 }
 
 // Head dim 128 with 8..128 query heads per KV head runs on the tensor cores: at that many flops per
@@ -96,7 +99,7 @@ bool gqa_on_tensor_cores(const da_decode_args_t &a) {
 int heads_per_cta(Shape s, int group) {
     if (s == Shape::kMla) return 1;
     if (s == Shape::kD128Tc) return group;
-    if (s == Shape::kMlaTc) return 128;
+    if (s == Shape::kMlaTc) return group;  // all heads of the KV head in one CTA (rows past them are padding)
     const char *env = getenv("DA_HEADS_PER_CTA");
     if (env) {
         int g = atoi(env);
@@ -527,9 +530,9 @@ int da_decode_fwd(const da_decode_args_t *a) {
     if (plan.shape == Shape::kMlaTc) {
         // q as [batch][128][576] in boxes {64, 128, 1}; the latent cache as [rows][576] in boxes
         // {64, tile}; both land 128-byte-swizzled, the layout the UMMA descriptors name.
-        const uint64_t qd[3] = {576, 128, (uint64_t)a->batch};
+        const uint64_t qd[3] = {576, (uint64_t)a->head_q, (uint64_t)a->batch};
         const uint64_t qs[2] = {576 * 2, (uint64_t)p.q_row_stride * 2};
-        const uint32_t qb[3] = {64, 128, 1};
+        const uint32_t qb[3] = {64, (uint32_t)a->head_q, 1};  // head_q <= 128 rows
         rc = make_tensor_map(p.q, 3, qd, qs, qb, true, bf16, &maps.k);
         if (rc != DA_OK) return rc;
         const uint64_t kd[2] = {576, kMapRows};

@@ -1,7 +1,8 @@
 // Latent-KV (MLA) decode attention on the sm_100a tensor cores: tcgen05.mma with accumulators in
 // tensor memory (TMEM), operands staged by TMA.
 //
-// Shape: 128 query heads share one KV head whose rows hold 576 values; V is the first 512 of them
+// Shape: up to 128 query heads (rows past head_q are padding) share one KV head whose rows hold 576
+// values; V is the first 512 of them
 // (the reference runs this shape through its generic kernel, one CTA per query head:
 // csrc/kernel/decoding_attn/decoding_fwd_hd576_hdv512.cu:9-17, so every K row is fetched 128
 // times).  Here the 128 heads are the M dimension of two dense contractions per 64-key tile:
@@ -133,12 +134,12 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
 
     if (k_begin >= k_end) {
         if (p.num_splits == 1) {  // empty sequence: zero row, LSE = -inf
-            for (int idx = tid; idx < kHeads * kHalfV; idx += kThreads) {
+            for (int idx = tid; idx < p.head_q * kHalfV; idx += kThreads) {
                 const int h = idx / kHalfV, d = half * kHalfV + idx % kHalfV;
                 if (o_out) o_out[(size_t)b * p.o_row_stride + (size_t)h * kDimV + d] = from_float<T>(0.0f);
                 if (p.o_f32) p.o_f32[((size_t)b * p.head_q + h) * kDimV + d] = 0.0f;
             }
-            if (p.lse && half == 0 && tid < kHeads) p.lse[(size_t)b * p.head_q + tid] = -INFINITY;
+            if (p.lse && half == 0 && tid < p.head_q) p.lse[(size_t)b * p.head_q + tid] = -INFINITY;
         }
         return;
     }
@@ -196,7 +197,9 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_k);
             // Q blocks for shared memory: slot 0 meets the last streamed block, slots 1-4 the V blocks.
-            mbar_arrive_expect_tx(q_full, kQSmemBlocks * kQBlockBytes);
+            // (the map's box holds head_q <= 128 rows; rows past them keep whatever shared memory held and only
+            // feed tile rows that are never read back)
+            mbar_arrive_expect_tx(q_full, kQSmemBlocks * p.head_q * 128);
             tma_load_tile_3d(q_s, &tm_q, a_block(half, kABlocks - 1) * 64, 0, b, q_full);
             for (int j = 0; j < kVBlocks; ++j) {
                 tma_load_tile_3d(q_s + (1 + j) * kQBlockBytes, &tm_q, v_block(half, j) * 64, 0, b, q_full);
@@ -365,6 +368,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
     } else {
         // ---------------- softmax / epilogue: thread r <-> TMEM lane r <-> head r ----------------
         const int r = tid;
+        const bool valid = r < p.head_q;  // with fewer than 128 heads the remaining rows are padding
         const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
         const float slope2 = p.is_alibi ? exp2f(-8.0f * (float)(r + 1) / (float)p.head_q) * kLog2e : 0.0f;
         const int pos_shift = (p.kv_pos_offset ? p.kv_pos_offset[b] : 0) - ((p.kv_total_len ? p.kv_total_len[b] : len) - 1);
@@ -381,7 +385,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                 const T *src = q_row + a_block(half, j) * 64;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    const uint4 v = *reinterpret_cast<const uint4 *>(src + i * 8);
+                    const uint4 v = valid ? *reinterpret_cast<const uint4 *>(src + i * 8) : make_uint4(0, 0, 0, 0);
                     buf[4 * i] = v.x, buf[4 * i + 1] = v.y, buf[4 * i + 2] = v.z, buf[4 * i + 3] = v.w;
                 }
                 tmem_st32(lane_base + kColQ + j * 32, buf);
@@ -412,7 +416,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     const float x = __uint_as_float(buf[j]) * p.scale_log2 + slope2 * (float)(key0 + c0 + j + pos_shift);
-                    s[c0 + j] = (c0 + j < rows) ? x : -INFINITY;
+                    s[c0 + j] = (c0 + j < rows) ? (valid ? x : 0.0f) : -INFINITY;
                     mx = fmaxf(mx, s[c0 + j]);
                 }
             }
@@ -483,6 +487,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                 tmem_ld32(lane_base + kColO + c * 32, buf);
                 tmem_wait_ld();
                 const int d0 = half * kHalfV + c * 32;
+                if (!valid) continue;  // padding row: nothing to write (the loads above are warp-wide)
                 if (p.num_splits > 1) {
                     float4 *dst = reinterpret_cast<float4 *>(p.part_o + row * kDimV + d0);
 #pragma unroll
@@ -508,7 +513,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                     }
                 }
             }
-            if (half == 0) {
+            if (half == 0 && valid) {
                 if (p.num_splits > 1) {
                     p.part_lse[row] = lse;
                 } else if (p.lse) {
