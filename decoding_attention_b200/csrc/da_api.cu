@@ -86,14 +86,16 @@ bool mla_on_tensor_cores(const da_decode_args_t &a) {
     return a.head_q == 128 || (a.head_q >= 8 && a.head_q < 128 && !mla_pair_enabled());
 }
 
-// Head dim 128 with 8..128 query heads per KV head runs on the tensor cores: at that many flops per
-// KV byte the CUDA-core kernel is bound by instruction issue, not by HBM.  DA_GQA_SIMT=1 keeps it on
-// the CUDA-core kernel (for comparisons).
+// Head dim 128 runs on the tensor cores unless the group of query heads per KV head is 1, 2 or 4, the
+// sizes the CUDA-core kernel handles in one CTA per KV head at the HBM rate.  Any other group would
+// cost it one pass over K and V per 1-, 2- or 4-head chunk (7 heads: 344 us against 121 us on the tensor
+// cores for 64 x 4096 keys), and from 8 heads up it is bound by instruction issue anyway.
+// DA_GQA_SIMT=1 keeps everything on the CUDA-core kernel (for comparisons).
 bool gqa_on_tensor_cores(const da_decode_args_t &a) {
     if (!a.v || a.dim != 128 || a.dim_v != 128) return false;
     const int64_t group = a.head_q / a.head_k;
     const char *e = getenv("DA_GQA_SIMT");
-    return group >= 8 && group <= 128 && !(e && e[0] == '1');
+    return group >= 3 && group != 4 && group <= 128 && !(e && e[0] == '1');
 }
 
 int heads_per_cta(Shape s, int group) {

@@ -1,5 +1,6 @@
 // Grouped-query / multi-query decode attention (head dim 128) on the sm_100a tensor cores, for KV
-// heads that serve 8..128 query heads.
+// heads that serve 3 or 5..128 query heads (1, 2 and 4 stay on the CUDA-core kernel, which handles
+// them in one CTA per KV head).
 //
 // With G query heads per KV head the path does 2*G flops per KV byte.  On CUDA cores
 // (da_split_kernel.cuh, at most 4 heads per CTA) G = 32 is bound by instruction issue at about a
