@@ -62,7 +62,7 @@ int device_state(DeviceState **out) {
     return DA_OK;
 }
 
-enum class Shape { kD64, kD96, kD128, kD256, kMla, kMlaTc, kD128Tc, kNone };
+enum class Shape { kD64, kD96, kD128, kD256, kMla, kMlaTc, kGqaTc, kNone };
 
 Shape shape_of(int64_t dim, int64_t dim_v, bool has_v) {
     if (has_v) {
@@ -86,21 +86,26 @@ bool mla_on_tensor_cores(const da_decode_args_t &a) {
     return a.head_q == 128 || (a.head_q >= 8 && a.head_q < 128 && !mla_pair_enabled());
 }
 
-// Head dim 128 runs on the tensor cores unless the group of query heads per KV head is 1, 2 or 4, the
-// sizes the CUDA-core kernel handles in one CTA per KV head at the HBM rate.  Any other group would
-// cost it one pass over K and V per 1-, 2- or 4-head chunk (7 heads: 344 us against 121 us on the tensor
-// cores for 64 x 4096 keys), and from 8 heads up it is bound by instruction issue anyway.
-// DA_GQA_SIMT=1 keeps everything on the CUDA-core kernel (for comparisons).
+// Head dims 64, 128 and 256 run on the tensor cores unless the group of query heads per KV head is one
+// the CUDA-core kernel serves well: 1, 2 or 4 heads, which it handles in one CTA per KV head at the HBM
+// rate (and 3 heads at dims 64 and 256, where its two chunks still win).  Any other group would cost it
+// one pass over K and V per 1-, 2- or 4-head chunk (dim 128, 7 heads: 344 us against 121 us on the
+// tensor cores for 64 x 4096 keys), and from 8 heads up it is bound by instruction issue anyway (dim
+// 256, 32 heads: 979 against 141 us).  DA_GQA_SIMT=1 keeps everything on the CUDA-core kernel.
 bool gqa_on_tensor_cores(const da_decode_args_t &a) {
-    if (!a.v || a.dim != 128 || a.dim_v != 128) return false;
+    if (!a.v || a.dim != a.dim_v || (a.dim != 64 && a.dim != 128 && a.dim != 256)) return false;
     const int64_t group = a.head_q / a.head_k;
     const char *e = getenv("DA_GQA_SIMT");
-    return group >= 3 && group != 4 && group <= 128 && !(e && e[0] == '1');
+    if (e && e[0] == '1') return false;
+    const char *m = getenv("DA_GQA_TC_MIN");  // development knob: smallest group that goes to the tensor cores
+    if (m) return group >= atoi(m) && group <= 128;
+    if (group > 128) return false;
+    return a.dim == 128 ? (group >= 3 && group != 4) : group >= 5;
 }
 
 int heads_per_cta(Shape s, int group) {
     if (s == Shape::kMla) return 1;
-    if (s == Shape::kD128Tc) return group;
+    if (s == Shape::kGqaTc) return group;
     if (s == Shape::kMlaTc) return group;  // all heads of the KV head in one CTA (rows past them are padding)
     const char *env = getenv("DA_HEADS_PER_CTA");
     if (env) {
@@ -126,7 +131,7 @@ SplitVariantInfo variant_info(Shape s, int heads) {
         case Shape::kD128: return split_info_d128(heads);
         case Shape::kD256: return split_info_d256(heads);
         case Shape::kMla: return split_info_mla_simt(heads);
-        case Shape::kD128Tc: return split_info_gqa_tc();
+        case Shape::kGqaTc: return split_info_gqa_tc();
         case Shape::kMlaTc: return mla_pair_enabled() ? split_info_mla_pair() : split_info_mla_tc();
         default: return {0, 0, 0};
     }
@@ -249,7 +254,7 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
                     (long long)a.dim, (long long)a.dim_v, has_v ? "given" : "NULL");
     }
     if (shape == Shape::kMla && mla_on_tensor_cores(a)) shape = Shape::kMlaTc;
-    if (shape == Shape::kD128 && gqa_on_tensor_cores(a)) shape = Shape::kD128Tc;
+    if ((shape == Shape::kD64 || shape == Shape::kD128 || shape == Shape::kD256) && gqa_on_tensor_cores(a)) shape = Shape::kGqaTc;
     const int group = (int)(a.head_q / a.head_k);
     const int heads = heads_per_cta(shape, group);
     const SplitVariantInfo info = variant_info(shape, heads);
@@ -268,7 +273,7 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
         splits = a.num_splits;
     } else if (env && atoi(env) > 0) {
         splits = atoi(env);
-    } else if (shape == Shape::kMlaTc || shape == Shape::kD128Tc) {
+    } else if (shape == Shape::kMlaTc || shape == Shape::kGqaTc) {
         // One CTA per SM and long-running CTAs: pick the split count whose CTA total fills whole
         // waves best, weighed against the fixed cost of every extra CTA.
         const int64_t slots = sm_count;
@@ -508,21 +513,22 @@ int da_decode_fwd(const da_decode_args_t *a) {
     memset(&maps, 0, sizeof(maps));
     // Tiled TMA needs a global stride that is a multiple of 16 bytes (checked above: 8 elements) and
     // a box of at most 256 elements per dimension; the latent-KV rows (576) keep the row-wise path.
-    p.use_tmap = (plan.shape != Shape::kMla) && (plan.shape != Shape::kMlaTc) && (plan.shape != Shape::kD128Tc) &&
+    p.use_tmap = (plan.shape != Shape::kMla) && (plan.shape != Shape::kMlaTc) && (plan.shape != Shape::kGqaTc) &&
                  !getenv("DA_NO_TMAP");
     CUtensorMap tm_q;
     memset(&tm_q, 0, sizeof(tm_q));
-    if (plan.shape == Shape::kD128Tc) {
-        // q as [batch][head_q][128] in boxes {64, min(128, head_q), 1}; K and V as [rows][head_k][128] in
+    if (plan.shape == Shape::kGqaTc) {
+        // q as [batch][head_q][dim] in boxes {64, min(128, head_q), 1}; K and V as [rows][head_k][dim] in
         // boxes {64, 1, tile}: all 128-byte-swizzled, the layout the UMMA descriptors name.
-        const uint64_t qd[3] = {128, (uint64_t)a->head_q, (uint64_t)a->batch};
-        const uint64_t qs[2] = {128 * 2, (uint64_t)p.q_row_stride * 2};
+        const uint64_t dim = (uint64_t)a->dim;  // 64, 128 or 256
+        const uint64_t qd[3] = {dim, (uint64_t)a->head_q, (uint64_t)a->batch};
+        const uint64_t qs[2] = {dim * 2, (uint64_t)p.q_row_stride * 2};
         const uint32_t qb[3] = {64, (uint32_t)(a->head_q < 128 ? a->head_q : 128), 1};
         rc = make_tensor_map(p.q, 3, qd, qs, qb, true, bf16, &tm_q);
         if (rc != DA_OK) return rc;
-        const uint64_t kd[3] = {128, (uint64_t)a->head_k, kMapRows};
-        const uint64_t ks[2] = {128 * 2, (uint64_t)p.k_row_stride * 2};
-        const uint64_t vs[2] = {128 * 2, (uint64_t)p.v_row_stride * 2};
+        const uint64_t kd[3] = {dim, (uint64_t)a->head_k, kMapRows};
+        const uint64_t ks[2] = {dim * 2, (uint64_t)p.k_row_stride * 2};
+        const uint64_t vs[2] = {dim * 2, (uint64_t)p.v_row_stride * 2};
         const uint32_t kb[3] = {64, 1, (uint32_t)plan.tile_keys};
         rc = make_tensor_map(p.k, 3, kd, ks, kb, true, bf16, &maps.k);
         if (rc != DA_OK) return rc;
@@ -557,7 +563,7 @@ int da_decode_fwd(const da_decode_args_t *a) {
         case Shape::kD128: e = launch_split_d128(bf16, plan.heads, p, maps, stream); break;
         case Shape::kD256: e = launch_split_d256(bf16, plan.heads, p, maps, stream); break;
         case Shape::kMla: e = launch_split_mla_simt(bf16, plan.heads, p, maps, stream); break;
-        case Shape::kD128Tc: e = launch_gqa_tc(bf16, p, tm_q, maps.k, maps.v, stream); break;
+        case Shape::kGqaTc: e = launch_gqa_tc(bf16, (int)a->dim, p, tm_q, maps.k, maps.v, stream); break;
         case Shape::kMlaTc:
             e = mla_pair_enabled() ? launch_mla_pair(bf16, p, maps.v, stream)
                                    : launch_mla_tc(bf16, p, maps.k, maps.v, stream);

@@ -1,24 +1,28 @@
-// Grouped-query / multi-query decode attention (head dim 128) on the sm_100a tensor cores, for KV
-// heads that serve 3 or 5..128 query heads (1, 2 and 4 stay on the CUDA-core kernel, which handles
-// them in one CTA per KV head).
+// Grouped-query / multi-query decode attention (head dims 64, 128, 256) on the sm_100a tensor cores,
+// for KV heads that serve a group of query heads the CUDA-core kernel handles badly (more than 4, or
+// not 1, 2 or 4; at most 128).
 //
 // With G query heads per KV head the path does 2*G flops per KV byte.  On CUDA cores
 // (da_split_kernel.cuh, at most 4 heads per CTA) G = 32 is bound by instruction issue at about a
 // tenth of the HBM rate -- the reference has the same shape of problem, one CTA per query head
 // (csrc/kernel/decoding_attn/decoding_fwd_hd128_hdv128.cu:9-25).  Here the G heads of one KV head are
 // rows of an M = 128 tcgen05.mma tile (rows >= G compute garbage that nobody reads; the tensor
-// pipe is otherwise idle), so every K/V byte is read once and used for all G heads:
-//     S[128 x 64]   = Q[128 x 128] . K_tile[64 x 128]^T      (8 MMAs  M128 N64  K16, operands K-major)
-//     O[128 x 128] += P[128 x 64]  . V_tile[64 x 128]        (4 MMAs  M128 N128 K16, V MN-major)
+// pipe is otherwise idle), so every K/V byte is read once and used for all G heads; for head dim D
+//     S[128 x 64] = Q[128 x D] . K_tile[64 x D]^T      (D/16 MMAs  M128 N64 K16, operands K-major)
+//     O[128 x D] += P[128 x 64] . V_tile[64 x D]        (4 MMAs     M128 N=D K16, V MN-major)
 // One CTA = (sequence, KV head, key range).  Q, K and V tiles arrive by tiled TMA copies with the
-// 128-byte swizzle; S (two buffers) and O live in tensor memory (256 columns).
-// Warps 0-15 = softmax/epilogue.  A warp can only reach the TMEM lanes of its quadrant (warp % 4),
-// so four warps share each block of 32 rows and split the 64 score columns (and the 128 output
-// columns) four ways: with few valid rows per tile the softmax, not the tensor pipe, sets the
-// pace, and its latency is per-thread serial work.  The four threads of a row agree on the row
-// maximum through shared memory once per tile.  Quadrants whose rows are all >= G stay out.
-// Warp 16 = TMA producer, warp 17 = TMEM allocation + MMA issue.  Lazy reference max as in the MLA
-// kernel.  Every wait is bounded (the per-tile rendezvous of the softmax threads is an mbarrier).
+// 128-byte swizzle; S (two buffers) and O live in tensor memory.
+// Softmax/epilogue warps: a warp can only reach the TMEM lanes of its quadrant (warp % 4), so
+// several warps share each block of 32 rows and split the 64 score columns (and the output columns)
+// between them: with few valid rows per tile the softmax, not the tensor pipe, sets the pace, and
+// its latency is per-thread serial work.  The threads of a row agree on the row maximum through
+// shared memory once per tile.  Quadrants whose rows are all >= G stay out.
+// Dims 64 and 128 run two independent softmax streams (even / odd tiles, one accumulator each,
+// merged at the end): 16 softmax warps.  Dim 256 has room for one accumulator only and runs one
+// stream over both S buffers: 8 softmax warps; its 64 KB tiles outlast a tile's softmax chain.
+// Then one TMA producer warp and one warp for TMEM allocation + MMA issue.  Lazy reference max as
+// in the MLA kernel.  Every wait is bounded (the per-tile rendezvous of the softmax threads is an
+// mbarrier).
 #include <type_traits>
 
 #include "da_internal.h"
@@ -28,32 +32,41 @@ namespace da {
 namespace {
 
 constexpr int kRows = 128;                            // M of both contractions (G valid rows)
-constexpr int kDim = 128;
 constexpr int kTile = 64;                             // keys per tile
-constexpr int kStages = 4;
-constexpr int kBlocks = kDim / 64;                    // 64-element (128-byte) column blocks of a row
 constexpr int kQBlockBytes = kRows * 128;             // [128 heads x 64 dims]
 constexpr int kKBlockBytes = kTile * 128;             // [64 keys x 64 dims]
-constexpr int kKStageBytes = kBlocks * kKBlockBytes;  // K tile; the V tile has the same size
 constexpr int kPBytes = kRows * kTile * 2;
-constexpr int kOffQ = 0;
-constexpr int kOffK = kOffQ + kBlocks * kQBlockBytes;
-constexpr int kOffV = kOffK + kStages * kKStageBytes;
-constexpr int kOffP = kOffV + kStages * kKStageBytes;
-constexpr int kColSplit = 4;                          // softmax threads per row: 2 streams x 2 column halves
 constexpr int kColsPer = 32;                          // score columns per thread
-constexpr int kOffRowMax = kOffP + 2 * kPBytes;       // [2][kColSplit][128] floats: per-thread partial row maxima / sums
-constexpr int kOffBar = kOffRowMax + 2 * kColSplit * kRows * 4 + 1024;  // + [2][128] stream maxima for the final merge
-// q_full, kv_full/kv_empty[kStages], s_full[2], s_empty[2], p_full[2], pv_done[2], row_sync[2], fin_sync
-constexpr int kNumBars = 1 + 2 * kStages + 11;
-constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16 + 1024;
-constexpr int kSoftmaxWarps = 4 * kColSplit;
-constexpr int kProducerWarp = kSoftmaxWarps, kMmaWarp = kSoftmaxWarps + 1;
-constexpr int kThreads = (kSoftmaxWarps + 2) * 32;
 constexpr int kTmemCols = 512;
-constexpr int kColS = 0;      // 2 x 64: one S buffer per stream
-constexpr int kColO = 128;    // 2 x 128: one accumulator per stream
-static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+constexpr int kColS = 0;      // 2 x 64: the two S buffers
+constexpr int kColO = 128;    // one accumulator of D columns per stream
+
+// Per head dim D: 64 and 128 run two softmax streams (two accumulators of D columns), 256 runs one (its
+// 64 KB tiles keep the pipe and the memory system busy longer than the softmax chain of a tile takes).
+template <int D>
+struct GqaCfg {
+    static constexpr int kBlocks = D / 64;                    // 64-element (128-byte) column blocks of a row
+    static constexpr int kStreams = D <= 128 ? 2 : 1;
+    static constexpr int kStages = D == 64 ? 8 : (D == 128 ? 4 : 2);
+    static constexpr int kKStageBytes = kBlocks * kKBlockBytes;  // K tile; the V tile has the same size
+    static constexpr int kColSplit = 2 * kStreams;            // softmax threads per row: streams x 2 column halves
+    static constexpr int kOffQ = 0;
+    static constexpr int kOffK = kOffQ + kBlocks * kQBlockBytes;
+    static constexpr int kOffV = kOffK + kStages * kKStageBytes;
+    static constexpr int kOffP = kOffV + kStages * kKStageBytes;
+    static constexpr int kOffRowMax = kOffP + kStreams * kPBytes;  // partial row maxima / sums, stream maxima
+    static constexpr int kOffBar = kOffRowMax + 2 * kColSplit * kRows * 4 + 1024;
+    // q_full, kv_full/kv_empty[kStages], s_full[2], s_empty[2], p_full[2], pv_done[2], row_sync[2], fin_sync
+    static constexpr int kNumBars = 1 + 2 * kStages + 11;
+    static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16 + 1024;
+    static constexpr int kSoftmaxWarps = 4 * kColSplit;
+    static constexpr int kProducerWarp = kSoftmaxWarps, kMmaWarp = kSoftmaxWarps + 1;
+    static constexpr int kThreads = (kSoftmaxWarps + 2) * 32;
+    static constexpr int kOutPer = D / kColSplit;             // output columns per thread in the epilogue
+    static_assert(D == 64 || D == 128 || D == 256, "head dim");
+    static_assert(kColO + kStreams * D <= kTmemCols, "TMEM budget");
+    static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+};
 constexpr float kRescaleThreshold = 8.0f;
 
 #ifdef DA_GQA_PROFILE
@@ -70,10 +83,15 @@ __device__ long long g_gqa_prof[64];
 #define PROF_FLUSH(base)
 #endif
 
-template <typename T>
-__global__ void __launch_bounds__(kThreads, 1)
+template <typename T, int D>
+__global__ void __launch_bounds__(GqaCfg<D>::kThreads, 1)
 da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v) {
+    using C = GqaCfg<D>;
+    constexpr int kDim = D, kBlocks = C::kBlocks, kStreams = C::kStreams, kStages = C::kStages, kKStageBytes = C::kKStageBytes;
+    constexpr int kColSplit = C::kColSplit, kThreads = C::kThreads, kProducerWarp = C::kProducerWarp, kMmaWarp = C::kMmaWarp;
+    constexpr int kOffQ = C::kOffQ, kOffK = C::kOffK, kOffV = C::kOffV, kOffP = C::kOffP, kOffRowMax = C::kOffRowMax;
+    constexpr int kOffBar = C::kOffBar, kNumBars = C::kNumBars, kOutPer = C::kOutPer;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
@@ -138,7 +156,7 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             mbar_init(&pv_done[s], 1);
             mbar_init(&row_sync[s], participants);
         }
-        mbar_init(fin_sync, 2 * participants);
+        mbar_init(fin_sync, kStreams * participants);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -251,12 +269,12 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             if (!ok) break;
             tc_fence_after();
             const int st = t % kStages;
-            const uint64_t pd = p_desc0 + (uint64_t)(((t & 1) * kPBytes) >> 4);
+            const uint64_t pd = p_desc0 + (uint64_t)((((kStreams == 2) ? (t & 1) : 0) * kPBytes) >> 4);
             const uint64_t vd = v_desc0 + (uint64_t)((st * kKStageBytes) >> 4);
 #pragma unroll
             for (int ks = 0; ks < kTile / 16; ++ks) {
-                umma_ss(tmem_base + kColO + (t & 1) * kDim, pd + (uint64_t)((ks * 2 * (kRows * 16)) >> 4),
-                        vd + (uint64_t)((ks * 16 * 128) >> 4), kIdescPV, (t >= 2 || ks > 0) ? 1u : 0u, leader);
+                umma_ss(tmem_base + kColO + ((kStreams == 2) ? (t & 1) : 0) * kDim, pd + (uint64_t)((ks * 2 * (kRows * 16)) >> 4),
+                        vd + (uint64_t)((ks * 16 * 128) >> 4), kIdescPV, (t >= kStreams || ks > 0) ? 1u : 0u, leader);
             }
             umma_commit(&kv_empty[st], leader);
             umma_commit(&pv_done[t & 1], leader);
@@ -271,7 +289,7 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
         // are merged at the end like two key-range splits.  That keeps two tiles' worth of the
         // (latency-bound) softmax chain in flight.  Thread (quad, strm, hf, lane) owns row 32 quad + lane
         // of stream strm and its score columns [32 hf, +32).
-        const int quad = warp & 3, cp = warp >> 2, strm = cp >> 1, hf = cp & 1;
+        const int quad = warp & 3, cp = warp >> 2, strm = (kStreams == 2) ? (cp >> 1) : 0, hf = cp & 1;
         const int r = quad * 32 + lane;
         const bool valid = r < G;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
@@ -283,19 +301,21 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
         float *rm = rowmax_s + strm * (2 * kRows);  // [2 halves][128] partial row maxima of this stream
         PROF_DECL;
         int last_t = -1;
-        for (int t = strm; t < n_tiles; t += 2) {
+        int n_done = 0;  // tiles this thread has finished (use count of its stream's row_sync barrier)
+        for (int t = strm; t < n_tiles; t += kStreams, ++n_done) {
             PROF_BEGIN();
-            const int it = t >> 1;  // use count of this stream's barriers
+            const int sb = (kStreams == 2) ? strm : (t & 1);  // S buffer of this tile (= t & 1) and the barriers that go with it
+            const int it = t >> 1;  // use count of those barriers
             const int key0 = k_begin + t * kTile + hf * kColsPer;
             const int rows = min(kTile, k_end - (k_begin + t * kTile)) - hf * kColsPer;  // valid columns of this thread
-            ok = __all_sync(0xffffffffu, mbar_wait(&s_full[strm], (uint32_t)it & 1u, abort_flag));
+            ok = __all_sync(0xffffffffu, mbar_wait(&s_full[sb], (uint32_t)it & 1u, abort_flag));
             PROF_END(0);
             if (!ok) break;
             tc_fence_after();
-            tmem_ld32(lane_base + kColS + strm * kTile + hf * kColsPer, buf);
+            tmem_ld32(lane_base + kColS + sb * kTile + hf * kColsPer, buf);
             tmem_wait_ld();
             tc_fence_before();
-            mbar_arrive(&s_empty[strm]);
+            mbar_arrive(&s_empty[sb]);
             float s[kColsPer];
             float mx = -INFINITY;
 #pragma unroll
@@ -308,7 +328,7 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             rm[hf * kRows + r] = mx;
             PROF_END(1);
             mbar_arrive(&row_sync[strm]);
-            ok = __all_sync(0xffffffffu, mbar_wait(&row_sync[strm], (uint32_t)it & 1u, abort_flag));
+            ok = __all_sync(0xffffffffu, mbar_wait(&row_sync[strm], (uint32_t)n_done & 1u, abort_flag));
             PROF_END(2);
             if (!ok) break;
             mx = fmaxf(mx, rm[(hf ^ 1) * kRows + r]);
@@ -319,22 +339,23 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                 m_ref = mx;
                 l *= alpha;
             }
-            if (it >= 1) {
-                // This stream's previous P.V has finished: its P buffer and its accumulator are idle.
-                ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[strm], (uint32_t)(it - 1) & 1u, abort_flag));
+            if (n_done >= 1) {
+                // This stream's previous P.V (tile t - kStreams) has finished: its P buffer and its accumulator are idle.
+                const int tp = t - kStreams;
+                ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(kStreams == 2) ? strm : (tp & 1)], (uint32_t)(tp >> 1) & 1u, abort_flag));
                 if (!ok) break;
                 if (__any_sync(0xffffffffu, raise)) {
-                    // Rare: the reference max of some row of this quadrant moved; rescale this thread's 64
-                    // columns of the row in place.
+                    // Rare: the reference max of some row of this quadrant moved; rescale this thread's half
+                    // of the row's accumulator columns in place.
                     tc_fence_after();
 #pragma unroll 1
-                    for (int c = 0; c < 2; ++c) {
+                    for (int c = 0; c < kDim / 64; ++c) {
                         uint32_t ob[32];
-                        tmem_ld32(lane_base + o_col + hf * 64 + c * 32, ob);
+                        tmem_ld32(lane_base + o_col + hf * (kDim / 2) + c * 32, ob);
                         tmem_wait_ld();
 #pragma unroll
                         for (int j = 0; j < 32; ++j) ob[j] = __float_as_uint(__uint_as_float(ob[j]) * alpha);
-                        tmem_st32(lane_base + o_col + hf * 64 + c * 32, ob);
+                        tmem_st32(lane_base + o_col + hf * (kDim / 2) + c * 32, ob);
                     }
                     tmem_wait_st();
                 }
@@ -363,31 +384,32 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             l += sum;
             fence_proxy_async();
             tc_fence_before();
-            mbar_arrive(&p_full[strm]);
+            mbar_arrive(&p_full[sb]);
             last_t = t;
             PROF_END(4);
         }
         if (warp == 0) PROF_FLUSH(16);
-        // ---- merge the two streams and write the row out ----
-        float *l_part = rowmax_s + 2 * 2 * kRows;       // [4 threads of a row][128]
-        float *m_strm = l_part + kColSplit * kRows;     // [2 streams][128]
+        // ---- merge the streams and write the row out ----
+        float *l_part = rowmax_s + kStreams * 2 * kRows;  // [kColSplit threads of a row][128]
+        float *m_strm = l_part + kColSplit * kRows;        // [kStreams][128]
         if (ok) {
             l_part[cp * kRows + r] = l;
             if (hf == 0) m_strm[strm * kRows + r] = m_ref;
             mbar_arrive(fin_sync);
             ok = __all_sync(0xffffffffu, mbar_wait(fin_sync, 0, abort_flag));
         }
-        // both accumulators must be final: the last P.V of either stream
-        if (ok && last_t >= 0) ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[strm], (uint32_t)(last_t >> 1) & 1u, abort_flag));
-        const int other_last = ((n_tiles - 1) & 1) == (strm ^ 1) ? n_tiles - 1 : n_tiles - 2;
-        if (ok && other_last >= 0) {
-            ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[strm ^ 1], (uint32_t)(other_last >> 1) & 1u, abort_flag));
+        // every accumulator must be final: the last P.V that went through either S buffer
+        for (int sb = 0; sb < 2 && ok; ++sb) {
+            const int last = ((n_tiles - 1) & 1) == sb ? n_tiles - 1 : n_tiles - 2;
+            if (last >= 0) ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[sb], (uint32_t)(last >> 1) & 1u, abort_flag));
         }
+        (void)last_t;
         if (ok) {
             tc_fence_after();
-            const float m0 = m_strm[r], m1 = m_strm[kRows + r];
+            const float m0 = m_strm[r];
+            const float m1 = (kStreams == 2) ? m_strm[kRows + r] : -INFINITY;
             const float l0 = l_part[0 * kRows + r] + l_part[1 * kRows + r];
-            const float l1 = l_part[2 * kRows + r] + l_part[3 * kRows + r];
+            const float l1 = (kStreams == 2) ? l_part[2 * kRows + r] + l_part[3 * kRows + r] : 0.0f;
             const float mm = fmaxf(m0, m1);                      // stream 0 always has a tile: finite
             const float w0 = exp2f(m0 - mm), w1 = (m1 == -INFINITY) ? 0.0f : exp2f(m1 - mm);
             const float lsum = l0 * w0 + l1 * w1;
@@ -395,29 +417,36 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             const float lse = (mm + log2f(lsum)) * kLn2;
             const int h = h0 + r;
             const size_t row = ((size_t)b * p.head_q + h) * p.num_splits + split;
-            uint32_t ob[32];
-            tmem_ld32(lane_base + kColO + cp * 32, buf);          // stream 0, this thread's 32 output columns
-            tmem_ld32(lane_base + kColO + kDim + cp * 32, ob);    // stream 1 (never written if it had no tile)
-            tmem_wait_ld();
-            float out[32];
+            constexpr int CW = kOutPer < 32 ? kOutPer : 32;  // columns per TMEM load: 16 (dim 64) or 32
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const float a0 = __uint_as_float(buf[j]) * w0;
-                const float a1 = (w1 > 0.0f) ? __uint_as_float(ob[j]) * w1 : 0.0f;
-                out[j] = (a0 + a1) * inv;
-            }
-            const int d0 = cp * 32;
-            if (valid) {
+            for (int c = 0; c < kOutPer / CW; ++c) {
+                const int d0 = cp * kOutPer + c * CW;  // this thread's output columns [d0, d0 + CW)
+                float out[CW];
+                uint32_t oa[CW], ob[CW];
+                if constexpr (CW == 32) {
+                    tmem_ld32(lane_base + kColO + d0, oa);                          // stream 0
+                    if (kStreams == 2) tmem_ld32(lane_base + kColO + kDim + d0, ob);  // stream 1 (never written if it had no tile)
+                } else {
+                    tmem_ld16(lane_base + kColO + d0, oa);
+                    if (kStreams == 2) tmem_ld16(lane_base + kColO + kDim + d0, ob);
+                }
+                tmem_wait_ld();
+#pragma unroll
+                for (int j = 0; j < CW; ++j) {
+                    const float a0 = __uint_as_float(oa[j]) * w0;
+                    const float a1 = (kStreams == 2 && w1 > 0.0f) ? __uint_as_float(ob[j]) * w1 : 0.0f;
+                    out[j] = (a0 + a1) * inv;
+                }
+                if (!valid) continue;
                 if (p.num_splits > 1) {
                     float4 *dst = reinterpret_cast<float4 *>(p.part_o + row * kDim + d0);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) dst[j] = make_float4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
-                    if (cp == 0) p.part_lse[row] = lse;
+                    for (int j = 0; j < CW / 4; ++j) dst[j] = make_float4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
                 } else {
                     if (o_out) {
                         uint4 *dst = reinterpret_cast<uint4 *>(o_out + (size_t)b * p.o_row_stride + (size_t)h * kDim + d0);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
+                        for (int j = 0; j < CW / 8; ++j) {
                             alignas(16) T tmp[8];
 #pragma unroll
                             for (int e = 0; e < 8; ++e) tmp[e] = from_float<T>(out[8 * j + e]);
@@ -427,9 +456,15 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                     if (p.o_f32) {
                         float *dst = p.o_f32 + ((size_t)b * p.head_q + h) * kDim + d0;
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) dst[j] = out[j];
+                        for (int j = 0; j < CW; ++j) dst[j] = out[j];
                     }
-                    if (p.lse && cp == 0) p.lse[(size_t)b * p.head_q + h] = lse;
+                }
+            }
+            if (valid && cp == 0) {
+                if (p.num_splits > 1) {
+                    p.part_lse[row] = lse;
+                } else if (p.lse) {
+                    p.lse[(size_t)b * p.head_q + h] = lse;
                 }
             }
             tc_fence_before();
@@ -459,29 +494,40 @@ extern "C" void da_debug_gqa_prof(long long *out, int reset) {
 
 SplitVariantInfo split_info_gqa_tc() { return {kTile, kRows, 1}; }
 
-// tm_q: rank-3 map of q [batch][head_q][128], box {64, min(128, head_q), 1}; tm_k / tm_v: rank-3 maps
-// [rows][head_k][128], box {64, 1, 64 keys}; all with the 128-byte swizzle.
-cudaError_t launch_gqa_tc(bool bf16, const SplitParams &p, const CUtensorMap &tm_q, const CUtensorMap &tm_k,
-                          const CUtensorMap &tm_v, cudaStream_t stream) {
+namespace {
+template <int D>
+cudaError_t launch_d(bool bf16, const SplitParams &p, const CUtensorMap &tm_q, const CUtensorMap &tm_k, const CUtensorMap &tm_v,
+                     cudaStream_t stream) {
+    using C = GqaCfg<D>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
     if (dev < 64 && !attr_set[dev]) {
-        err = cudaFuncSetAttribute(da_gqa_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        err = cudaFuncSetAttribute(da_gqa_tc_kernel<__half, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
         if (err != cudaSuccess) return err;
-        err = cudaFuncSetAttribute(da_gqa_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   kSmemBytes);
+        err = cudaFuncSetAttribute(da_gqa_tc_kernel<__nv_bfloat16, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   C::kSmemBytes);
         if (err != cudaSuccess) return err;
         attr_set[dev] = true;
     }
     dim3 grid(p.num_splits, p.head_k, p.batch);
-    if (bf16) {
-        return launch_kernel(da_gqa_tc_kernel<__nv_bfloat16>, grid, kThreads, kSmemBytes, stream, p.batch_order != nullptr, p, tm_q, tm_k, tm_v);
-    } else {
-        return launch_kernel(da_gqa_tc_kernel<__half>, grid, kThreads, kSmemBytes, stream, p.batch_order != nullptr, p, tm_q, tm_k, tm_v);
+    const bool overlap = p.batch_order != nullptr;
+    return bf16 ? launch_kernel(da_gqa_tc_kernel<__nv_bfloat16, D>, grid, C::kThreads, C::kSmemBytes, stream, overlap, p, tm_q, tm_k, tm_v)
+                : launch_kernel(da_gqa_tc_kernel<__half, D>, grid, C::kThreads, C::kSmemBytes, stream, overlap, p, tm_q, tm_k, tm_v);
+}
+}  // namespace
+
+// tm_q: rank-3 map of q [batch][head_q][dim], box {64, min(128, head_q), 1}; tm_k / tm_v: rank-3 maps
+// [rows][head_k][dim], box {64, 1, 64 keys}; all with the 128-byte swizzle.  dim: 64, 128 or 256.
+cudaError_t launch_gqa_tc(bool bf16, int dim, const SplitParams &p, const CUtensorMap &tm_q, const CUtensorMap &tm_k,
+                          const CUtensorMap &tm_v, cudaStream_t stream) {
+    switch (dim) {
+        case 64: return launch_d<64>(bf16, p, tm_q, tm_k, tm_v, stream);
+        case 128: return launch_d<128>(bf16, p, tm_q, tm_k, tm_v, stream);
+        case 256: return launch_d<256>(bf16, p, tm_q, tm_k, tm_v, stream);
+        default: return cudaErrorInvalidValue;
     }
-    return cudaGetLastError();
 }
 
 }  // namespace da

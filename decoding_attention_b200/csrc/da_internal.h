@@ -39,8 +39,8 @@ SplitVariantInfo split_info_mla_simt(int heads);
 cudaError_t launch_mla_tc(bool bf16, const SplitParams &p, const CUtensorMap &tm_q, const CUtensorMap &tm_k,
                           cudaStream_t s);
 SplitVariantInfo split_info_mla_tc();
-// Tensor-core kernel for head dim 128 with 8..128 query heads per KV head (da_gqa_tc_sm100.cu).
-cudaError_t launch_gqa_tc(bool bf16, const SplitParams &p, const CUtensorMap &tm_q, const CUtensorMap &tm_k,
+// Tensor-core kernel for head dims 64 / 128 / 256 and groups of up to 128 query heads per KV head (da_gqa_tc_sm100.cu).
+cudaError_t launch_gqa_tc(bool bf16, int dim, const SplitParams &p, const CUtensorMap &tm_q, const CUtensorMap &tm_k,
                           const CUtensorMap &tm_v, cudaStream_t s);
 SplitVariantInfo split_info_gqa_tc();
 // Cluster-pair variant (da_mla_pair_sm100.cu): the two CTAs of a key range split the 576-long
