@@ -62,7 +62,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + ",".join(self.FIELDS),
-                 "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL,
+                 "--format=csv,noheader,nounits", "-lms", "25"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL,
                 text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -132,7 +132,8 @@ def time_resident(cabi, args, steps, warmup, barrier, flush=None):
     launches = cabi.launch_count() - l0
     total = t0.elapsed_time(t1) * 1e-3
 
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    # (20 calls are enough for the mean; a long second pass only pushes the GPU into its power cap)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(min(steps, 20))]
     for a, b in ev:  # create the underlying events
         a.record()
         b.record()
@@ -497,7 +498,7 @@ def run_profile_config(opt):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seqs", type=int, default=SEQS_PER_GPU,
