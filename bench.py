@@ -397,7 +397,9 @@ def other_configs(cabi, dev, world, rank, barrier, max_over_ranks, hbm_peak):
 
     if world == 1:
         paged("gqa_bf16_b256_varlen_paged64", synth.config_gqa_varlen(), 64)
+        paged("gqa_bf16_b256_varlen_paged16", synth.config_gqa_varlen(), 16)
         paged("mla_bf16_b128_sk4096_paged64", synth.config_mla(batch=128), 64)
+        paged("mla_bf16_b128_sk4096_paged16", synth.config_mla(batch=128), 16)
         one("mha_fp16_b4_sk1024", synth.config_mha_small(), True)
         one("mqa_alibi_fp16_b128_sk2048", synth.config_mqa_alibi(), True)
         for b in (1, 8, 32, 128):

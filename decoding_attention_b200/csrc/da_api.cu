@@ -367,9 +367,9 @@ int check_args(const da_decode_args_t *a) {
         }
     }
     if (a->block_table) {
-        // Every kernel's key tile is 32 or 64 keys; a page must hold whole tiles.
-        if (a->page_size < 64 || (a->page_size & (a->page_size - 1)) != 0) {
-            return fail(DA_ERR_UNSUPPORTED, "page_size %d: paged caches need a power-of-two page size >= 64", a->page_size);
+        // A key tile (32 or 64 keys) is fetched in runs of consecutive rows: whole, or page by page.
+        if (a->page_size < 16 || (a->page_size & (a->page_size - 1)) != 0) {
+            return fail(DA_ERR_UNSUPPORTED, "page_size %d: paged caches need a power-of-two page size >= 16", a->page_size);
         }
         if (a->block_table_stride <= 0) return fail(DA_ERR_INVALID_ARG, "block_table_stride must be positive");
         if (a->max_seq_k > a->block_table_stride * (int64_t)a->page_size) {
@@ -504,8 +504,10 @@ int da_decode_fwd(const da_decode_args_t *a) {
     if ((int64_t)p.head_k * p.head_chunks > 65535) {
         return fail(DA_ERR_INVALID_ARG, "head_k * head chunks exceeds the grid limit");
     }
-    if (a->block_table && a->page_size % plan.tile_keys != 0) {
-        return fail(DA_ERR_UNSUPPORTED, "page_size %d is not a multiple of the %d-key tile", a->page_size, plan.tile_keys);
+    // Rows per TMA box: the tile, or a page when pages are shorter than the tile.
+    const int box_keys = (a->block_table && a->page_size < plan.tile_keys) ? a->page_size : plan.tile_keys;
+    if (a->block_table && a->page_size < 64 && plan.shape == Shape::kMlaTc && mla_pair_enabled()) {
+        return fail(DA_ERR_UNSUPPORTED, "the cluster-pair MLA kernel needs pages of at least 64 keys");
     }
 
     const bool bf16 = a->is_bf16 != 0;
@@ -529,7 +531,7 @@ int da_decode_fwd(const da_decode_args_t *a) {
         const uint64_t kd[3] = {dim, (uint64_t)a->head_k, kMapRows};
         const uint64_t ks[2] = {dim * 2, (uint64_t)p.k_row_stride * 2};
         const uint64_t vs[2] = {dim * 2, (uint64_t)p.v_row_stride * 2};
-        const uint32_t kb[3] = {64, 1, (uint32_t)plan.tile_keys};
+        const uint32_t kb[3] = {64, 1, (uint32_t)box_keys};
         rc = make_tensor_map(p.k, 3, kd, ks, kb, true, bf16, &maps.k);
         if (rc != DA_OK) return rc;
         rc = make_tensor_map(p.v, 3, kd, vs, kb, true, bf16, &maps.v);
@@ -545,14 +547,14 @@ int da_decode_fwd(const da_decode_args_t *a) {
         if (rc != DA_OK) return rc;
         const uint64_t kd[2] = {576, kMapRows};
         const uint64_t ks[1] = {(uint64_t)p.k_row_stride * 2};
-        const uint32_t kb[2] = {64, (uint32_t)plan.tile_keys};
+        const uint32_t kb[2] = {64, (uint32_t)box_keys};
         rc = make_tensor_map(p.k, 2, kd, ks, kb, true, bf16, &maps.v);
         if (rc != DA_OK) return rc;
     }
     if (p.use_tmap) {
-        rc = make_kv_tensor_map(p.k, p.k_row_stride, p.head_k, (int)a->dim, plan.tile_keys, bf16, &maps.k);
+        rc = make_kv_tensor_map(p.k, p.k_row_stride, p.head_k, (int)a->dim, box_keys, bf16, &maps.k);
         if (rc != DA_OK) return rc;
-        rc = make_kv_tensor_map(p.v, p.v_row_stride, p.head_k, (int)a->dim_v, plan.tile_keys, bf16, &maps.v);
+        rc = make_kv_tensor_map(p.v, p.v_row_stride, p.head_k, (int)a->dim_v, box_keys, bf16, &maps.v);
         if (rc != DA_OK) return rc;
     }
     cudaError_t e;

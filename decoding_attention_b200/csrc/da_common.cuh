@@ -46,9 +46,9 @@ struct SplitParams {
     float scale_log2;  // softmax scale * log2(e)
 };
 
-// Row of the cache that holds key `key0` of sequence `b` (key0 is a multiple of the key tile).  Packed
-// cache: the sequence's rows are consecutive from cu_seq_k[b].  Paged cache: the block table names
-// the page; a tile never straddles two pages because the page size is a multiple of the tile.
+// Row of the cache that holds key `key0` of sequence `b`.  Packed cache: the sequence's rows are
+// consecutive from cu_seq_k[b].  Paged cache: the block table names the page.  Rows are consecutive for
+// kv_run_keys() keys from a multiple of that number: a whole tile, or a page when pages are shorter.
 __device__ __forceinline__ size_t kv_tile_row(const SplitParams &p, int b, int seq_begin, int key0) {
     if (!p.block_table) return (size_t)seq_begin + key0;
     const int page = p.block_table[(size_t)b * p.block_table_stride + (key0 >> p.page_shift)];
@@ -62,6 +62,10 @@ __device__ __forceinline__ size_t kv_tile_row(const SplitParams &p, int b, int s
 // no-ops for kernels launched the ordinary way.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+__device__ __forceinline__ int kv_run_keys(const SplitParams &p, int tile) {
+    return (p.block_table && (1 << p.page_shift) < tile) ? (1 << p.page_shift) : tile;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

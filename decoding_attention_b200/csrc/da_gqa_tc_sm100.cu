@@ -185,21 +185,26 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
         }
         const T *k_g = reinterpret_cast<const T *>(p.k) + (size_t)hk * kDim;
         const T *v_g = reinterpret_cast<const T *>(p.v) + (size_t)hk * kDim;
+        const int run = kv_run_keys(p, kTile);
         for (int t = 0; t < n_tiles && ok; ++t) {
             const int st = t % kStages;
             const uint32_t ph = (uint32_t)(t / kStages) & 1u;
             const int key0 = k_begin + t * kTile;
             const int rows = min(kTile, k_end - key0);
             const size_t tok0 = kv_tile_row(p, b, seq_begin, key0);
+            auto row_of = [&](int r) { return run == kTile ? tok0 + r : kv_tile_row(p, b, seq_begin, key0 + r); };
             if (t >= kStages) ok = mbar_wait(&kv_empty[st], ph ^ 1u, abort_flag);
             if (!ok) break;
             uint8_t *kd = k_s + st * kKStageBytes, *vd = v_s + st * kKStageBytes;
             if (rows == kTile) {
                 if (lane == 0) {
                     mbar_arrive_expect_tx(&kv_full[st], 2 * kKStageBytes);
-                    for (int kb = 0; kb < kBlocks; ++kb) {
-                        tma_load_tile_3d(kd + kb * kKBlockBytes, &tm_k, kb * 64, hk, (int)tok0, &kv_full[st]);
-                        tma_load_tile_3d(vd + kb * kKBlockBytes, &tm_v, kb * 64, hk, (int)tok0, &kv_full[st]);
+                    for (int k0 = 0; k0 < kTile; k0 += run) {  // one box per run of consecutive rows (a page, or the tile)
+                        const int row = (int)row_of(k0);
+                        for (int kb = 0; kb < kBlocks; ++kb) {
+                            tma_load_tile_3d(kd + kb * kKBlockBytes + k0 * 128, &tm_k, kb * 64, hk, row, &kv_full[st]);
+                            tma_load_tile_3d(vd + kb * kKBlockBytes + k0 * 128, &tm_v, kb * 64, hk, row, &kv_full[st]);
+                        }
                     }
                 }
             } else {
@@ -210,8 +215,9 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                     const int r = i / kChunks, c = i % kChunks;
                     uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
                     if (r < rows) {
-                        kv = *reinterpret_cast<const uint4 *>(k_g + (tok0 + r) * p.k_row_stride + c * 8);
-                        vv = *reinterpret_cast<const uint4 *>(v_g + (tok0 + r) * p.v_row_stride + c * 8);
+                        const size_t row = row_of(r);
+                        kv = *reinterpret_cast<const uint4 *>(k_g + row * p.k_row_stride + c * 8);
+                        vv = *reinterpret_cast<const uint4 *>(v_g + row * p.v_row_stride + c * 8);
                     }
                     const int off = (c >> 3) * kKBlockBytes + r * 128 + (((c & 7) ^ (r & 7)) << 4);
                     *reinterpret_cast<uint4 *>(kd + off) = kv;

@@ -98,16 +98,18 @@ __device__ long long g_mla_prof[64];
 // tiles go by TMA (lane 0 issues; the bytes are counted on `bar`, whose expect_tx the caller has
 // posted); a ragged last tile is read with plain loads, rows past the end zeroed, because the
 // tensor map must not be asked for rows beyond the sequence.
-template <typename T>
+template <typename T, typename RowOf>
 __device__ __forceinline__ void load_block(uint8_t *dst, const CUtensorMap *tm, const T *k_g, size_t k_row_stride, int block,
-                                           size_t tok0, int rows, uint64_t *bar, int lane) {
+                                           RowOf row_of, int run, int rows, uint64_t *bar, int lane) {
     if (rows == kTile) {
-        if (lane == 0) tma_load_2d(dst, tm, block * 64, (int)tok0, bar);
+        if (lane == 0) {
+            for (int k0 = 0; k0 < kTile; k0 += run) tma_load_2d(dst + k0 * 128, tm, block * 64, (int)row_of(k0), bar);
+        }
     } else {
         for (int i = lane; i < kTile * 8; i += 32) {
             const int r = i >> 3, cc = i & 7;
             uint4 v = make_uint4(0, 0, 0, 0);
-            if (r < rows) v = *reinterpret_cast<const uint4 *>(k_g + (tok0 + r) * k_row_stride + block * 64 + cc * 8);
+            if (r < rows) v = *reinterpret_cast<const uint4 *>(k_g + row_of(r) * k_row_stride + block * 64 + cc * 8);
             *reinterpret_cast<uint4 *>(dst + r * 128 + ((cc ^ (r & 7)) << 4)) = v;
         }
     }
@@ -206,6 +208,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             }
         }
         const T *k_g = reinterpret_cast<const T *>(p.k);
+        const int run = kv_run_keys(p, kTile);
         int a_slot = 0;
         uint32_t a_round = 0;  // how many times the streamed ring has wrapped
         PROF_DECL;
@@ -213,6 +216,8 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             const int key0 = k_begin + t * kTile;
             const int rows = min(kTile, k_end - key0);
             const size_t tok0 = kv_tile_row(p, b, seq_begin, key0);
+            // rows of the tile are consecutive in the cache, except across the pages of a short-page cache
+            auto row_of = [&](int r) { return run == kTile ? tok0 + r : kv_tile_row(p, b, seq_begin, key0 + r); };
             const bool whole = rows == kTile;
             // the five streamed blocks, each into the next slot of the ring (the V blocks come from the loader warps)
             for (int j = 0; j < kABlocks && ok; ++j) {
@@ -221,7 +226,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                 PROF_END(1);
                 if (!ok) break;
                 if (whole && lane == 0) mbar_arrive_expect_tx(&a_full[a_slot], kKBlockBytes);
-                load_block<T>(a_s + a_slot * kKBlockBytes, &tm_k, k_g, p.k_row_stride, a_block(half, j), tok0, rows,
+                load_block<T>(a_s + a_slot * kKBlockBytes, &tm_k, k_g, p.k_row_stride, a_block(half, j), row_of, run, rows,
                               &a_full[a_slot], lane);
                 if (!whole) {
                     fence_proxy_async();
@@ -334,6 +339,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
         // once the next one has been issued, so two are in flight.
         const int lt = tid - 6 * 32;  // 0..127
         const T *k_g = reinterpret_cast<const T *>(p.k);
+        const int run = kv_run_keys(p, kTile);
         PROF_DECL;
         for (int t = 0; t < n_tiles && ok; ++t) {
             const int key0 = k_begin + t * kTile;
@@ -349,7 +355,9 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             for (int n = 0; n < kVBlocks * kTile * 8 / kLoaderThreads; ++n) {
                 const int i = lt + n * kLoaderThreads;
                 const int j = i >> 9, r = (i >> 3) & 63, cc = i & 7;
-                const T *src = k_g + (tok0 + min(r, rows - 1)) * p.k_row_stride + v_block(half, j) * 64 + cc * 8;
+                const int rr = min(r, rows - 1);
+                const size_t row = run == kTile ? tok0 + rr : kv_tile_row(p, b, seq_begin, key0 + rr);
+                const T *src = k_g + row * p.k_row_stride + v_block(half, j) * 64 + cc * 8;
                 cp_async16(slot + j * kKBlockBytes + r * 128 + ((cc ^ (r & 7)) << 4), src, r < rows ? 16u : 0u);  // 0: zero fill
             }
             cp_async_commit();

@@ -194,24 +194,31 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
         }
         bool ok = true;
         int armed_k = 0, armed_v = 0;  // tiles whose full barrier has been armed
+        const int run = kv_run_keys(p, TILE);
         for (int t = 0; t < n_tiles; ++t) {
             const int st = t % STAGES;
             const uint32_t ph = (uint32_t)(t / STAGES) & 1u;
             const int key0 = k_begin + t * TILE;
             const int rows = min(TILE, k_end - key0);
             const size_t tok0 = kv_tile_row(p, b, seq_begin, key0);
+            // rows of the tile are consecutive in the cache, except across the pages of a short-page cache
+            auto row_of = [&](int r) { return run == TILE ? tok0 + r : kv_tile_row(p, b, seq_begin, key0 + r); };
             if (t >= STAGES) ok = mbar_wait(&empty_k[st], ph ^ 1u, abort_flag);
             if (!ok) break;
             const bool whole = p.use_tmap && rows == TILE;  // a partial tile must not read past the sequence
             if (lane == 0) {
                 mbar_arrive_expect_tx(&full_k[st], (uint32_t)rows * C::K_ROW_BYTES);
-                if (whole) tma_load_tile_3d(ks + st * C::K_TILE_BYTES, &tm_k, 0, hk, (int)tok0, &full_k[st]);
+                if (whole) {
+                    for (int k0 = 0; k0 < TILE; k0 += run) {
+                        tma_load_tile_3d(ks + st * C::K_TILE_BYTES + k0 * C::K_ROW_BYTES, &tm_k, 0, hk, (int)row_of(k0), &full_k[st]);
+                    }
+                }
             }
             __syncwarp();
             armed_k = t + 1;
             if (!whole) {
                 for (int r = lane; r < rows; r += 32) {
-                    bulk_copy_g2s(ks + st * C::K_TILE_BYTES + r * C::K_ROW_BYTES, kg + (tok0 + r) * p.k_row_stride,
+                    bulk_copy_g2s(ks + st * C::K_TILE_BYTES + r * C::K_ROW_BYTES, kg + row_of(r) * p.k_row_stride,
                                   C::K_ROW_BYTES, &full_k[st]);
                 }
             }
@@ -220,14 +227,18 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
                 if (!ok) break;
                 if (lane == 0) {
                     mbar_arrive_expect_tx(&full_v[st], (uint32_t)rows * C::V_ROW_BYTES);
-                    if (whole) tma_load_tile_3d(vs + st * C::V_TILE_BYTES, &tm_v, 0, hk, (int)tok0, &full_v[st]);
+                    if (whole) {
+                        for (int k0 = 0; k0 < TILE; k0 += run) {
+                            tma_load_tile_3d(vs + st * C::V_TILE_BYTES + k0 * C::V_ROW_BYTES, &tm_v, 0, hk, (int)row_of(k0), &full_v[st]);
+                        }
+                    }
                 }
                 __syncwarp();
                 armed_v = t + 1;
                 if (!whole) {
                     for (int r = lane; r < rows; r += 32) {
                         bulk_copy_g2s(vs + st * C::V_TILE_BYTES + r * C::V_ROW_BYTES,
-                                      vg + (tok0 + r) * p.v_row_stride, C::V_ROW_BYTES, &full_v[st]);
+                                      vg + row_of(r) * p.v_row_stride, C::V_ROW_BYTES, &full_v[st]);
                     }
                 }
             }

@@ -56,7 +56,7 @@ def paged_fwd(q, k_cache, v_cache, seq_lens, block_table, max_seq_k=None, dim_v=
     q [batch, head_q, dim]; k_cache [num_pages, page_size, head_k, dim]; v_cache the same with dim_v, or
     None for the latent-KV (MLA) shape; seq_lens int32 [batch]; block_table int32 [batch, blocks]: key j
     of sequence b is row ``j % page_size`` of page ``block_table[b, j // page_size]``.  page_size must be a
-    power of two >= 64.  The reference has no paged entry point; its Python benchmark builds such
+    power of two >= 16.  The reference has no paged entry point; its Python benchmark builds such
     layouts for the libraries it compares against (benchmarks/python/benchmark_decoding_attn.py:182-190).
     """
     cu_seq_k = torch.zeros(seq_lens.numel() + 1, dtype=torch.int32, device=seq_lens.device)

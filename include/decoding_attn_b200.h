@@ -73,7 +73,8 @@ typedef struct da_decode_args {
     /* Paged cache (optional; NULL = packed, the reference's layout).  k and v then point to page
      * pools [num_pages * page_size, head_k, dim] and key j of sequence b lives in row
      * block_table[b * block_table_stride + j / page_size] * page_size + j % page_size.
-     * Lengths still come from cu_seq_k (differences only).  page_size: a power of two >= 64.
+     * Lengths still come from cu_seq_k (differences only).  page_size: a power of two >= 16 (pages
+     * shorter than a 64-key tile are fetched one TMA box per page).
      * The reference has no paged input; its Python benchmark builds this layout for the libraries
      * it compares against (benchmarks/python/benchmark_decoding_attn.py:129-151, :182-190). */
     const int32_t *block_table; /* device [batch, block_table_stride] */

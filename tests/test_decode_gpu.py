@@ -281,7 +281,17 @@ PAGED = [
     (torch.float16, 32, 1, 128, 128, [300, 2048, 65], 64, True, 0),            # tensor-core GQA kernel
     (torch.bfloat16, 128, 1, 576, 512, [500, 64, 1000, 1], 64, False, 0),      # tensor-core MLA kernel
     (torch.bfloat16, 128, 1, 576, 512, [900, 130], 128, False, 2),
-    (torch.float16, 16, 1, 576, 512, [200, 70], 64, False, 0),                 # CUDA-core MLA kernel
+    (torch.float16, 16, 1, 576, 512, [200, 70], 64, False, 0),                 # tensor-core MLA kernel, 16 heads
+    (torch.float16, 4, 1, 576, 512, [200, 70], 32, False, 0),                  # CUDA-core MLA kernel, short pages
+    # pages shorter than a key tile (vLLM's default is 16): a tile is fetched page by page
+    (torch.bfloat16, 32, 8, 128, 128, [700, 64, 1, 129, 17], 16, False, 0),
+    (torch.float16, 32, 8, 128, 128, [333, 50], 32, True, 3),
+    (torch.float16, 8, 2, 256, 256, [100, 400], 16, False, 0),
+    (torch.bfloat16, 16, 16, 64, 64, [333, 1000], 16, False, 2),
+    (torch.float16, 32, 1, 128, 128, [300, 2048, 65], 16, True, 0),            # tensor-core GQA kernel
+    (torch.bfloat16, 64, 8, 256, 256, [300, 90], 32, False, 0),
+    (torch.bfloat16, 128, 1, 576, 512, [500, 64, 1000, 1], 16, False, 0),      # tensor-core MLA kernel
+    (torch.float16, 128, 1, 576, 512, [900, 130], 32, True, 2),
 ]
 
 
@@ -313,7 +323,7 @@ def test_paged_cache_argument_errors(native_lib):
     q, k, v, cu = [t.to(DEV) for t in w.make("cpu")]
     o = torch.empty(1, 8, 128, dtype=torch.float16, device=DEV)
     table = torch.zeros(1, 4, dtype=torch.int32, device=DEV)
-    for page in (16, 96):  # too small; not a power of two
+    for page in (8, 96):  # too small; not a power of two
         with pytest.raises(native_lib.DecodingAttnError):
             native_lib.decode_fwd(native_lib.make_args(q, k, v, o, cu, 100, 128, block_table=table, page_size=page))
     with pytest.raises(native_lib.DecodingAttnError):  # table rows too short for max_seq_k

@@ -35,7 +35,7 @@ def make_case(seed):
         lens[0] = top
     return dict(seed=seed, dt=r.choice([torch.float16, torch.bfloat16]), head_q=head_q, head_k=head_k, dim=dim,
                 dim_v=dim_v, mla=mla, lens=lens, alibi=r.random() < 0.3, scale=r.choice([None, None, 0.07]),
-                splits=r.choice([0, 0, 1, 2, 5]), page=r.choice([0, 0, 64, 128]), pad=r.choice([0, 0, 8, 64]))
+                splits=r.choice([0, 0, 1, 2, 5]), page=r.choice([0, 0, 16, 32, 64, 128]), pad=r.choice([0, 0, 8, 64]))
 
 
 @pytest.mark.parametrize("seed", range(150))
