@@ -348,3 +348,34 @@ def test_longest_first_launch_order(native_lib, oracle, splits):
     torch.cuda.synchronize()
     assert native_lib.device_status() == native_lib.DA_OK
     assert_close(o, oracle.attn_cpu(q, k, v, cu), "longest-first order")
+
+
+def test_cuda_graph_replay_with_launch_order_and_overlapped_launches(native_lib, oracle):
+    """The longest-first order kernel, the attention kernel and the merge kernel are chained with
+    programmatic dependent launches; the chain must survive stream capture and replay."""
+    g = torch.Generator().manual_seed(7)
+    lens = torch.randint(900, 2600, (48,), generator=g).tolist()
+    w = synth.Workload("graph_order", torch.float16, 32, 8, 128, 128, lens, dist="normal", scale=0.5, seed=8)
+    q, k, v, cu = w.make("cpu")
+    expect = oracle.attn_cpu(q, k, v, cu)
+    dq, dk, dv, dcu = q.to(DEV), k.to(DEV), v.to(DEV), cu.to(DEV)
+    o = torch.zeros(48, 32, 128, dtype=w.dtype, device=DEV)
+    probe = native_lib.make_args(dq, dk, dv, o, dcu, w.max_seq_k, 128, num_splits=2)
+    need = native_lib.workspace_bytes(probe)
+    assert need > 48 * 32 * 2 * 129 * 4, "the plan must include the launch-order array"
+    ws = torch.empty(need, dtype=torch.uint8, device=DEV)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        args = native_lib.make_args(dq, dk, dv, o, dcu, w.max_seq_k, 128, num_splits=2, workspace=ws,
+                                    stream=side.cuda_stream)
+        native_lib.decode_fwd(args)
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            native_lib.decode_fwd(args)
+    for _ in range(3):
+        o.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert native_lib.device_status() == native_lib.DA_OK
+        assert_close(o, expect, "graph replay with launch order")
