@@ -4,6 +4,7 @@ ALiBi, explicit scale, forced split counts, packed and paged caches, padded row 
 The cases are fixed by their seeds, so a failure names a reproducible case.  Same tolerance as the
 other parity tests: |out - oracle| <= 2e-3 + 1e-2 |oracle|, mean |diff| <= 5e-3.
 """
+import os
 import random
 
 import pytest
@@ -38,7 +39,7 @@ def make_case(seed):
                 splits=r.choice([0, 0, 1, 2, 5]), page=r.choice([0, 0, 16, 32, 64, 128]), pad=r.choice([0, 0, 8, 64]))
 
 
-@pytest.mark.parametrize("seed", range(150))
+@pytest.mark.parametrize("seed", range(int(os.environ.get("DA_FUZZ_SEEDS", "150"))))  # more seeds: DA_FUZZ_SEEDS=1000
 def test_random_case(native_lib, oracle, seed):
     c = make_case(seed)
     w = synth.Workload(f"fuzz{seed}", c["dt"], c["head_q"], c["head_k"], c["dim"], c["dim_v"], c["lens"], is_alibi=c["alibi"],
