@@ -115,7 +115,9 @@ __device__ __forceinline__ void load_block(uint8_t *dst, const CUtensorMap *tm, 
     }
 }
 
-template <typename T>
+// kShortPages: the cache is paged with pages shorter than a key tile, which is then fetched page by page.
+// A separate instantiation, so that the common case keeps its straight-line address arithmetic.
+template <typename T, bool kShortPages>
 __global__ void __launch_bounds__(kThreads, 1)
 da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k) {
     extern __shared__ uint8_t smem_raw[];
@@ -208,7 +210,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             }
         }
         const T *k_g = reinterpret_cast<const T *>(p.k);
-        const int run = kv_run_keys(p, kTile);
+        const int run = kShortPages ? kv_run_keys(p, kTile) : kTile;
         int a_slot = 0;
         uint32_t a_round = 0;  // how many times the streamed ring has wrapped
         PROF_DECL;
@@ -217,7 +219,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             const int rows = min(kTile, k_end - key0);
             const size_t tok0 = kv_tile_row(p, b, seq_begin, key0);
             // rows of the tile are consecutive in the cache, except across the pages of a short-page cache
-            auto row_of = [&](int r) { return run == kTile ? tok0 + r : kv_tile_row(p, b, seq_begin, key0 + r); };
+            auto row_of = [&](int r) { return kShortPages ? kv_tile_row(p, b, seq_begin, key0 + r) : tok0 + r; };
             const bool whole = rows == kTile;
             // the five streamed blocks, each into the next slot of the ring (the V blocks come from the loader warps)
             for (int j = 0; j < kABlocks && ok; ++j) {
@@ -339,7 +341,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
         // once the next one has been issued, so two are in flight.
         const int lt = tid - 6 * 32;  // 0..127
         const T *k_g = reinterpret_cast<const T *>(p.k);
-        const int run = kv_run_keys(p, kTile);
+        const int run = kShortPages ? kv_run_keys(p, kTile) : kTile;
         PROF_DECL;
         for (int t = 0; t < n_tiles && ok; ++t) {
             const int key0 = k_begin + t * kTile;
@@ -351,14 +353,28 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             PROF_END(0);
             if (!ok) break;
             uint8_t *slot = v_s + vs * kVSlotBytes;
+            if (!kShortPages) {  // the tile's rows are consecutive in the cache
 #pragma unroll
-            for (int n = 0; n < kVBlocks * kTile * 8 / kLoaderThreads; ++n) {
-                const int i = lt + n * kLoaderThreads;
-                const int j = i >> 9, r = (i >> 3) & 63, cc = i & 7;
-                const int rr = min(r, rows - 1);
-                const size_t row = run == kTile ? tok0 + rr : kv_tile_row(p, b, seq_begin, key0 + rr);
-                const T *src = k_g + row * p.k_row_stride + v_block(half, j) * 64 + cc * 8;
-                cp_async16(slot + j * kKBlockBytes + r * 128 + ((cc ^ (r & 7)) << 4), src, r < rows ? 16u : 0u);  // 0: zero fill
+                for (int n = 0; n < kVBlocks * kTile * 8 / kLoaderThreads; ++n) {
+                    const int i = lt + n * kLoaderThreads;
+                    const int j = i >> 9, r = (i >> 3) & 63, cc = i & 7;
+                    const T *src = k_g + (tok0 + min(r, rows - 1)) * p.k_row_stride + v_block(half, j) * 64 + cc * 8;
+                    cp_async16(slot + j * kKBlockBytes + r * 128 + ((cc ^ (r & 7)) << 4), src, r < rows ? 16u : 0u);  // 0: zero fill
+                }
+            } else {  // pages shorter than the tile: at most four of them, looked up once per tile
+                size_t page_row[4];
+#pragma unroll
+                for (int g = 0; g < 4; ++g) page_row[g] = g * run < rows ? kv_tile_row(p, b, seq_begin, key0 + g * run) : 0;
+#pragma unroll
+                for (int n = 0; n < kVBlocks * kTile * 8 / kLoaderThreads; ++n) {
+                    const int i = lt + n * kLoaderThreads;
+                    const int j = i >> 9, r = (i >> 3) & 63, cc = i & 7;
+                    const int rr = min(r, rows - 1);
+                    const int g = rr / run;  // run is 16 or 32
+                    const size_t base = g == 0 ? page_row[0] : (g == 1 ? page_row[1] : (g == 2 ? page_row[2] : page_row[3]));
+                    const T *src = k_g + (base + (rr - g * run)) * p.k_row_stride + v_block(half, j) * 64 + cc * 8;
+                    cp_async16(slot + j * kKBlockBytes + r * 128 + ((cc ^ (r & 7)) << 4), src, r < rows ? 16u : 0u);
+                }
             }
             cp_async_commit();
             PROF_BEGIN();
@@ -564,20 +580,24 @@ cudaError_t launch_mla_tc(bool bf16, const SplitParams &p, const CUtensorMap &tm
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
     if (dev < 64 && !attr_set[dev]) {
-        err = cudaFuncSetAttribute(da_mla_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (err != cudaSuccess) return err;
-        err = cudaFuncSetAttribute(da_mla_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   kSmemBytes);
-        if (err != cudaSuccess) return err;
+        const void *kernels[4] = {(const void *)da_mla_tc_kernel<__half, false>, (const void *)da_mla_tc_kernel<__half, true>,
+                                  (const void *)da_mla_tc_kernel<__nv_bfloat16, false>,
+                                  (const void *)da_mla_tc_kernel<__nv_bfloat16, true>};
+        for (const void *k : kernels) {
+            err = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+            if (err != cudaSuccess) return err;
+        }
         attr_set[dev] = true;
     }
     dim3 grid(p.num_splits, 2, p.batch);
+    const bool overlap = p.batch_order != nullptr;
+    const bool short_pages = p.block_table && (1 << p.page_shift) < kTile;
     if (bf16) {
-        return launch_kernel(da_mla_tc_kernel<__nv_bfloat16>, grid, kThreads, kSmemBytes, stream, p.batch_order != nullptr, p, tm_q, tm_k);
-    } else {
-        return launch_kernel(da_mla_tc_kernel<__half>, grid, kThreads, kSmemBytes, stream, p.batch_order != nullptr, p, tm_q, tm_k);
+        return short_pages ? launch_kernel(da_mla_tc_kernel<__nv_bfloat16, true>, grid, kThreads, kSmemBytes, stream, overlap, p, tm_q, tm_k)
+                           : launch_kernel(da_mla_tc_kernel<__nv_bfloat16, false>, grid, kThreads, kSmemBytes, stream, overlap, p, tm_q, tm_k);
     }
-    return cudaGetLastError();
+    return short_pages ? launch_kernel(da_mla_tc_kernel<__half, true>, grid, kThreads, kSmemBytes, stream, overlap, p, tm_q, tm_k)
+                       : launch_kernel(da_mla_tc_kernel<__half, false>, grid, kThreads, kSmemBytes, stream, overlap, p, tm_q, tm_k);
 }
 
 }  // namespace da

@@ -120,6 +120,30 @@ __device__ __forceinline__ float pick(const float (&arr)[N], int idx) {
 
 constexpr float kLazyRaise = 8.0f;
 
+// One K or V tile of a paged cache whose pages are shorter than the tile: one TMA box per page (whole
+// tile) or one bulk copy per row (ragged tail), the page of every run or row looked up in the block table.
+// Out of line, so that the common path's registers do not pay for it.  The caller has posted expect_tx.
+static __device__ __noinline__ void load_tile_short_pages(const int *block_table, long long table_stride, int page_shift, int b, int key0,
+                                                   int rows, int tile, bool whole, uint8_t *dst, int row_bytes,
+                                                   const CUtensorMap *tm, int hk, const uint8_t *g_base,
+                                                   long long g_row_bytes, uint64_t *bar, int lane) {
+    const int run = 1 << page_shift;
+    const int *pages = block_table + (size_t)b * table_stride;
+    if (whole) {
+        if (lane == 0) {
+            for (int k0 = 0; k0 < tile; k0 += run) {
+                const int row = (pages[(key0 + k0) >> page_shift] << page_shift) + ((key0 + k0) & (run - 1));
+                tma_load_tile_3d(dst + (size_t)k0 * row_bytes, tm, 0, hk, row, bar);
+            }
+        }
+    } else {
+        for (int r = lane; r < rows; r += 32) {
+            const size_t row = ((size_t)pages[(key0 + r) >> page_shift] << page_shift) + ((key0 + r) & (run - 1));
+            bulk_copy_g2s(dst + (size_t)r * row_bytes, g_base + row * g_row_bytes, (uint32_t)row_bytes, bar);
+        }
+    }
+}
+
 template <class C>
 __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const SplitParams p,
                                                               const __grid_constant__ CUtensorMap tm_k,
@@ -194,31 +218,29 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
         }
         bool ok = true;
         int armed_k = 0, armed_v = 0;  // tiles whose full barrier has been armed
-        const int run = kv_run_keys(p, TILE);
+        const bool short_pages = kv_run_keys(p, TILE) != TILE;  // paged cache with pages shorter than the tile
         for (int t = 0; t < n_tiles; ++t) {
             const int st = t % STAGES;
             const uint32_t ph = (uint32_t)(t / STAGES) & 1u;
             const int key0 = k_begin + t * TILE;
             const int rows = min(TILE, k_end - key0);
             const size_t tok0 = kv_tile_row(p, b, seq_begin, key0);
-            // rows of the tile are consecutive in the cache, except across the pages of a short-page cache
-            auto row_of = [&](int r) { return run == TILE ? tok0 + r : kv_tile_row(p, b, seq_begin, key0 + r); };
             if (t >= STAGES) ok = mbar_wait(&empty_k[st], ph ^ 1u, abort_flag);
             if (!ok) break;
             const bool whole = p.use_tmap && rows == TILE;  // a partial tile must not read past the sequence
             if (lane == 0) {
                 mbar_arrive_expect_tx(&full_k[st], (uint32_t)rows * C::K_ROW_BYTES);
-                if (whole) {
-                    for (int k0 = 0; k0 < TILE; k0 += run) {
-                        tma_load_tile_3d(ks + st * C::K_TILE_BYTES + k0 * C::K_ROW_BYTES, &tm_k, 0, hk, (int)row_of(k0), &full_k[st]);
-                    }
-                }
+                if (whole && !short_pages) tma_load_tile_3d(ks + st * C::K_TILE_BYTES, &tm_k, 0, hk, (int)tok0, &full_k[st]);
             }
             __syncwarp();
             armed_k = t + 1;
-            if (!whole) {
+            if (short_pages) {
+                load_tile_short_pages(p.block_table, p.block_table_stride, p.page_shift, b, key0, rows, TILE, whole,
+                                      ks + st * C::K_TILE_BYTES, C::K_ROW_BYTES, &tm_k, hk, reinterpret_cast<const uint8_t *>(kg),
+                                      p.k_row_stride * (long long)sizeof(T), &full_k[st], lane);
+            } else if (!whole) {
                 for (int r = lane; r < rows; r += 32) {
-                    bulk_copy_g2s(ks + st * C::K_TILE_BYTES + r * C::K_ROW_BYTES, kg + row_of(r) * p.k_row_stride,
+                    bulk_copy_g2s(ks + st * C::K_TILE_BYTES + r * C::K_ROW_BYTES, kg + (tok0 + r) * p.k_row_stride,
                                   C::K_ROW_BYTES, &full_k[st]);
                 }
             }
@@ -227,18 +249,18 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
                 if (!ok) break;
                 if (lane == 0) {
                     mbar_arrive_expect_tx(&full_v[st], (uint32_t)rows * C::V_ROW_BYTES);
-                    if (whole) {
-                        for (int k0 = 0; k0 < TILE; k0 += run) {
-                            tma_load_tile_3d(vs + st * C::V_TILE_BYTES + k0 * C::V_ROW_BYTES, &tm_v, 0, hk, (int)row_of(k0), &full_v[st]);
-                        }
-                    }
+                    if (whole && !short_pages) tma_load_tile_3d(vs + st * C::V_TILE_BYTES, &tm_v, 0, hk, (int)tok0, &full_v[st]);
                 }
                 __syncwarp();
                 armed_v = t + 1;
-                if (!whole) {
+                if (short_pages) {
+                    load_tile_short_pages(p.block_table, p.block_table_stride, p.page_shift, b, key0, rows, TILE, whole,
+                                          vs + st * C::V_TILE_BYTES, C::V_ROW_BYTES, &tm_v, hk,
+                                          reinterpret_cast<const uint8_t *>(vg), p.v_row_stride * (long long)sizeof(T), &full_v[st], lane);
+                } else if (!whole) {
                     for (int r = lane; r < rows; r += 32) {
                         bulk_copy_g2s(vs + st * C::V_TILE_BYTES + r * C::V_ROW_BYTES,
-                                      vg + row_of(r) * p.v_row_stride, C::V_ROW_BYTES, &full_v[st]);
+                                      vg + (tok0 + r) * p.v_row_stride, C::V_ROW_BYTES, &full_v[st]);
                     }
                 }
             }
