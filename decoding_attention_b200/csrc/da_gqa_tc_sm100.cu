@@ -83,7 +83,9 @@ __device__ long long g_gqa_prof[64];
 #define PROF_FLUSH(base)
 #endif
 
-template <typename T, int D>
+// kShortPages: the cache is paged with pages shorter than a key tile, which is then fetched page by page
+// (a separate instantiation, so that the common case keeps its straight-line address arithmetic).
+template <typename T, int D, bool kShortPages>
 __global__ void __launch_bounds__(GqaCfg<D>::kThreads, 1)
 da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v) {
@@ -185,14 +187,14 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
         }
         const T *k_g = reinterpret_cast<const T *>(p.k) + (size_t)hk * kDim;
         const T *v_g = reinterpret_cast<const T *>(p.v) + (size_t)hk * kDim;
-        const int run = kv_run_keys(p, kTile);
+        const int run = kShortPages ? kv_run_keys(p, kTile) : kTile;
         for (int t = 0; t < n_tiles && ok; ++t) {
             const int st = t % kStages;
             const uint32_t ph = (uint32_t)(t / kStages) & 1u;
             const int key0 = k_begin + t * kTile;
             const int rows = min(kTile, k_end - key0);
             const size_t tok0 = kv_tile_row(p, b, seq_begin, key0);
-            auto row_of = [&](int r) { return run == kTile ? tok0 + r : kv_tile_row(p, b, seq_begin, key0 + r); };
+            auto row_of = [&](int r) { return kShortPages ? kv_tile_row(p, b, seq_begin, key0 + r) : tok0 + r; };
             if (t >= kStages) ok = mbar_wait(&kv_empty[st], ph ^ 1u, abort_flag);
             if (!ok) break;
             uint8_t *kd = k_s + st * kKStageBytes, *vd = v_s + st * kKStageBytes;
@@ -510,17 +512,24 @@ cudaError_t launch_d(bool bf16, const SplitParams &p, const CUtensorMap &tm_q, c
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
     if (dev < 64 && !attr_set[dev]) {
-        err = cudaFuncSetAttribute(da_gqa_tc_kernel<__half, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-        if (err != cudaSuccess) return err;
-        err = cudaFuncSetAttribute(da_gqa_tc_kernel<__nv_bfloat16, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   C::kSmemBytes);
-        if (err != cudaSuccess) return err;
+        const void *kernels[4] = {(const void *)da_gqa_tc_kernel<__half, D, false>, (const void *)da_gqa_tc_kernel<__half, D, true>,
+                                  (const void *)da_gqa_tc_kernel<__nv_bfloat16, D, false>,
+                                  (const void *)da_gqa_tc_kernel<__nv_bfloat16, D, true>};
+        for (const void *k : kernels) {
+            err = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+            if (err != cudaSuccess) return err;
+        }
         attr_set[dev] = true;
     }
     dim3 grid(p.num_splits, p.head_k, p.batch);
     const bool overlap = p.batch_order != nullptr;
-    return bf16 ? launch_kernel(da_gqa_tc_kernel<__nv_bfloat16, D>, grid, C::kThreads, C::kSmemBytes, stream, overlap, p, tm_q, tm_k, tm_v)
-                : launch_kernel(da_gqa_tc_kernel<__half, D>, grid, C::kThreads, C::kSmemBytes, stream, overlap, p, tm_q, tm_k, tm_v);
+    const bool short_pages = p.block_table && (1 << p.page_shift) < kTile;
+    if (bf16) {
+        return short_pages ? launch_kernel(da_gqa_tc_kernel<__nv_bfloat16, D, true>, grid, C::kThreads, C::kSmemBytes, stream, overlap, p, tm_q, tm_k, tm_v)
+                           : launch_kernel(da_gqa_tc_kernel<__nv_bfloat16, D, false>, grid, C::kThreads, C::kSmemBytes, stream, overlap, p, tm_q, tm_k, tm_v);
+    }
+    return short_pages ? launch_kernel(da_gqa_tc_kernel<__half, D, true>, grid, C::kThreads, C::kSmemBytes, stream, overlap, p, tm_q, tm_k, tm_v)
+                       : launch_kernel(da_gqa_tc_kernel<__half, D, false>, grid, C::kThreads, C::kSmemBytes, stream, overlap, p, tm_q, tm_k, tm_v);
 }
 }  // namespace
 
