@@ -13,7 +13,7 @@ LIB_PATH = os.environ.get("DA_LIB_PATH") or os.path.join(_PKG, "libdecoding_attn
 DA_OK, DA_ERR_INVALID_ARG, DA_ERR_UNSUPPORTED, DA_ERR_WORKSPACE, DA_ERR_CUDA, DA_ERR_TIMEOUT = range(6)
 
 EXPORTS = ["da_decode_fwd", "da_decode_fwd_host", "da_decode_fwd_static", "da_static_scratch_bytes", "da_decode_workspace_bytes", "da_decode_num_splits",
-           "da_merge_partials", "da_exchange_merge", "da_exchange_buffer_bytes", "da_set_profile_events", "da_selftest_wait_timeout", "da_device_status", "da_status_string", "da_last_error", "da_launch_count"]
+           "da_merge_partials", "da_exchange_merge", "da_exchange_merge_bounded", "da_exchange_buffer_bytes", "da_set_profile_events", "da_selftest_wait_timeout", "da_device_status", "da_status_string", "da_last_error", "da_launch_count"]
 
 
 class DecodeArgs(ctypes.Structure):
@@ -73,6 +73,8 @@ def lib():
         l.da_exchange_merge.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int32, ctypes.c_int32,
                                         ctypes.c_int64, ctypes.c_int32, ctypes.c_uint32, ctypes.c_void_p,
                                         ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p]
+        l.da_exchange_merge_bounded.restype = ctypes.c_int
+        l.da_exchange_merge_bounded.argtypes = l.da_exchange_merge.argtypes + [ctypes.c_int64]
         l.da_exchange_buffer_bytes.restype = ctypes.c_size_t
         l.da_exchange_buffer_bytes.argtypes = [ctypes.c_int32, ctypes.c_int64, ctypes.c_int32]
         l.da_set_profile_events.restype = None

@@ -9,6 +9,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "../../include/decoding_attn_b200.h"
 #include "da_internal.h"
@@ -29,9 +30,17 @@ int fail(int code, const char *fmt, ...) {
     return code;
 }
 
-// Kernel status word: one per device (a __device__ variable lives in every device's copy of the
-// module); kernels that give up a bounded wait write kStatusWaitTimeout into it.
-__device__ int g_status_word;
+// Kernel status block: one per device (a __device__ variable lives in every device's copy of the
+// module).  [0]: kernels that give up a bounded wait write kStatusWaitTimeout here; [1]: the id of
+// the launch that did, so that only the remaining CTAs of that launch retire early.
+__device__ int g_status_word[2];
+std::atomic<uint32_t> g_launch_id{0};
+
+// Ids of launches: 1, 2, ... (never 0, the "no launch gave up" value of the status block).
+int next_launch_id() {
+    const uint32_t n = g_launch_id.fetch_add(1, std::memory_order_relaxed);
+    return (int)(n % 0x7ffffffeu) + 1;
+}
 
 constexpr int kMaxDevices = 64;
 struct DeviceState {
@@ -39,6 +48,8 @@ struct DeviceState {
     int *status_ptr = nullptr;
     void *scratch = nullptr;
     size_t scratch_bytes = 0;
+    std::vector<void *> retired;  // outgrown scratch buffers, kept until the process ends
+    std::mutex staging_mu;    // held for the whole of a da_decode_fwd_host call
     void *staging = nullptr;  // device copies of host tensors for da_decode_fwd_host
     size_t staging_bytes = 0;
     int sm_count = 0;
@@ -62,7 +73,7 @@ int device_state(DeviceState **out) {
     return DA_OK;
 }
 
-enum class Shape { kD64, kD96, kD128, kD256, kMla, kMlaTc, kGqaTc, kNone };
+enum class Shape { kD64, kD96, kD128, kD256, kMla, kMlaTc, kMla2Sm, kGqaTc, kNone };
 
 Shape shape_of(int64_t dim, int64_t dim_v, bool has_v) {
     if (has_v) {
@@ -76,14 +87,35 @@ Shape shape_of(int64_t dim, int64_t dim_v, bool has_v) {
     return Shape::kNone;
 }
 
+// Environment overrides, read once per process (the reference has none; these exist for benchmarks):
+//   DA_NUM_SPLITS=<n>   key-range splits per sequence when the caller leaves num_splits at 0
+//   DA_KERNEL=simt      keep every shape on the CUDA-core kernel (no tensor-core path)
+//   DA_KERNEL=mla1sm    latent-KV shape on the one-SM-per-CTA tensor-core kernel instead of SM pairs
+struct EnvOverrides {
+    int num_splits = 0;
+    bool force_simt = false;
+    bool mla_1sm = false;
+};
+const EnvOverrides &env_overrides() {
+    static const EnvOverrides env = [] {
+        EnvOverrides e;
+        if (const char *s = getenv("DA_NUM_SPLITS")) e.num_splits = atoi(s) > 0 ? atoi(s) : 0;
+        if (const char *k = getenv("DA_KERNEL")) {
+            e.force_simt = strcmp(k, "simt") == 0;
+            e.mla_1sm = strcmp(k, "mla1sm") == 0;
+        }
+        return e;
+    }();
+    return env;
+}
+
 // The tensor-core kernel covers the shape the latent-KV layout exists for: up to 128 query heads over
 // one KV head (128 in the full model, 16..64 per GPU under tensor parallelism; the reference's suite
 // runs 16, 32, 64 and 128, tests/test_decoding_attn.py:97).  Fewer than 8 heads, or several KV heads,
-// run on the CUDA-core kernel.  The cluster-pair variant is built for exactly 128 heads.
-bool mla_pair_enabled();
+// run on the CUDA-core kernel.
 bool mla_on_tensor_cores(const da_decode_args_t &a) {
-    if (a.v != nullptr || a.dim != 576 || a.dim_v != 512 || a.head_k != 1 || getenv("DA_MLA_SIMT")) return false;
-    return a.head_q == 128 || (a.head_q >= 8 && a.head_q < 128 && !mla_pair_enabled());
+    if (a.v != nullptr || a.dim != 576 || a.dim_v != 512 || a.head_k != 1 || env_overrides().force_simt) return false;
+    return a.head_q >= 8 && a.head_q <= 128;
 }
 
 // Head dims 64, 128 and 256 run on the tensor cores unless the group of query heads per KV head is one
@@ -91,37 +123,21 @@ bool mla_on_tensor_cores(const da_decode_args_t &a) {
 // rate (and 3 heads at dims 64 and 256, where its two chunks still win).  Any other group would cost it
 // one pass over K and V per 1-, 2- or 4-head chunk (dim 128, 7 heads: 344 us against 121 us on the
 // tensor cores for 64 x 4096 keys), and from 8 heads up it is bound by instruction issue anyway (dim
-// 256, 32 heads: 979 against 141 us).  DA_GQA_SIMT=1 keeps everything on the CUDA-core kernel.
+// 256, 32 heads: 979 against 141 us).
 bool gqa_on_tensor_cores(const da_decode_args_t &a) {
     if (!a.v || a.dim != a.dim_v || (a.dim != 64 && a.dim != 128 && a.dim != 256)) return false;
     const int64_t group = a.head_q / a.head_k;
-    const char *e = getenv("DA_GQA_SIMT");
-    if (e && e[0] == '1') return false;
-    const char *m = getenv("DA_GQA_TC_MIN");  // development knob: smallest group that goes to the tensor cores
-    if (m) return group >= atoi(m) && group <= 128;
-    if (group > 128) return false;
+    if (env_overrides().force_simt || group > 128) return false;
     return a.dim == 128 ? (group >= 3 && group != 4) : group >= 5;
 }
 
 int heads_per_cta(Shape s, int group) {
     if (s == Shape::kMla) return 1;
     if (s == Shape::kGqaTc) return group;
-    if (s == Shape::kMlaTc) return group;  // all heads of the KV head in one CTA (rows past them are padding)
-    const char *env = getenv("DA_HEADS_PER_CTA");
-    if (env) {
-        int g = atoi(env);
-        if ((g == 1 || g == 2 || g == 4) && group % g == 0) return g;
-    }
+    if (s == Shape::kMlaTc || s == Shape::kMla2Sm) return group;  // all heads of the KV head in one CTA / CTA pair
     if (group % 4 == 0) return 4;
     if (group % 2 == 0) return 2;
     return 1;
-}
-
-// Which tensor-core MLA kernel runs: the cluster-pair kernel (DA_MLA_PAIR=1) or the one whose two
-// CTAs per key range work independently (default until the pair kernel is the faster one).
-bool mla_pair_enabled() {
-    const char *e = getenv("DA_MLA_PAIR");
-    return e && e[0] == '1';
 }
 
 SplitVariantInfo variant_info(Shape s, int heads) {
@@ -132,7 +148,8 @@ SplitVariantInfo variant_info(Shape s, int heads) {
         case Shape::kD256: return split_info_d256(heads);
         case Shape::kMla: return split_info_mla_simt(heads);
         case Shape::kGqaTc: return split_info_gqa_tc();
-        case Shape::kMlaTc: return mla_pair_enabled() ? split_info_mla_pair() : split_info_mla_tc();
+        case Shape::kMlaTc: return split_info_mla_tc();
+        case Shape::kMla2Sm: return split_info_mla_2sm();
         default: return {0, 0, 0};
     }
 }
@@ -253,30 +270,32 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
                     "with v and (576,512) without",
                     (long long)a.dim, (long long)a.dim_v, has_v ? "given" : "NULL");
     }
-    if (shape == Shape::kMla && mla_on_tensor_cores(a)) shape = Shape::kMlaTc;
+    if (shape == Shape::kMla && mla_on_tensor_cores(a)) {
+        // SM pairs (cta_group::2) unless the cache is paged in pages shorter than the 64 keys one CTA stages at a time
+        shape = (!a.block_table || a.page_size >= 64) && !env_overrides().mla_1sm ? Shape::kMla2Sm : Shape::kMlaTc;
+    }
     if ((shape == Shape::kD64 || shape == Shape::kD128 || shape == Shape::kD256) && gqa_on_tensor_cores(a)) shape = Shape::kGqaTc;
     const int group = (int)(a.head_q / a.head_k);
     const int heads = heads_per_cta(shape, group);
     const SplitVariantInfo info = variant_info(shape, heads);
     const int tile = info.tile_keys;
     // The tensor-core MLA kernel runs two CTAs (one per half of the output columns) per key range.
-    const int64_t units = shape == Shape::kMlaTc ? a.batch * 2 : a.batch * a.head_k * (group / heads);
+    // The tensor-core MLA kernels run two CTAs per key range: apart (each one half of the output columns), or as a pair.
+    const int64_t units = shape == Shape::kMlaTc ? a.batch * 2 : shape == Shape::kMla2Sm ? a.batch : a.batch * a.head_k * (group / heads);
     const int64_t max_len = a.max_seq_k > 0 ? a.max_seq_k : 1;
     const int64_t tiles_per_unit = (max_len + tile - 1) / tile;
 
     // A tensor-core MLA CTA first stages 144 KB of Q: give it at least 256 keys to amortise that.
-    const int kMinTiles = 4, kWaves = 4;
-    const int kMaxTiles = getenv("DA_MAX_TILES") ? atoi(getenv("DA_MAX_TILES")) : 32;
+    const int kMinTiles = 4, kWaves = 4, kMaxTiles = 32;
     int64_t splits;
-    const char *env = getenv("DA_NUM_SPLITS");
     if (a.num_splits > 0) {
         splits = a.num_splits;
-    } else if (env && atoi(env) > 0) {
-        splits = atoi(env);
-    } else if (shape == Shape::kMlaTc || shape == Shape::kGqaTc) {
+    } else if (env_overrides().num_splits > 0) {
+        splits = env_overrides().num_splits;
+    } else if (shape == Shape::kMlaTc || shape == Shape::kMla2Sm || shape == Shape::kGqaTc) {
         // One CTA per SM and long-running CTAs: pick the split count whose CTA total fills whole
         // waves best, weighed against the fixed cost of every extra CTA.
-        const int64_t slots = sm_count;
+        const int64_t slots = shape == Shape::kMla2Sm ? sm_count / 2 : sm_count;
         double best = -1.0;
         splits = 1;
         for (int64_t s = 1; s <= tiles_per_unit && s <= 64; ++s) {
@@ -303,7 +322,7 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
         // Fewer units than CTA slots: one full wave of equal chunks beats several waves of short CTAs
         // (measured: 16 K keys x 32 heads 75.7 -> 50.1 us, 64 K keys 190 -> 167 us), as long as a chunk
         // still amortises a CTA's set-up.
-        if (units <= slots && !getenv("DA_MULTI_WAVE")) {
+        if (units <= slots) {
             const int64_t one_wave = slots / units;
             const bool fills = units * one_wave * 5 >= slots * 4;  // at least 80 % of the slots get a CTA
             if (fills && (tiles_per_unit + one_wave - 1) / one_wave >= kMinTiles) splits = one_wave;
@@ -327,7 +346,7 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
     const int64_t all_slots = (int64_t)sm_count * (info.ctas_per_sm > 0 ? info.ctas_per_sm : 1);
     plan->order_offset = 0;
     // (the order kernel costs 3-4 us: worth it only when a CTA runs long enough for a ragged tail to cost more)
-    if (a.batch >= 16 && units * splits > all_slots && chunk_tiles >= 16 && !getenv("DA_NO_ORDER")) {
+    if (a.batch >= 16 && units * splits > all_slots && chunk_tiles >= 16) {
         plan->scratch_bytes = (plan->scratch_bytes + 15) / 16 * 16;
         plan->order_offset = plan->scratch_bytes + 16;  // never 0
         plan->scratch_bytes = plan->order_offset + (size_t)a.batch * sizeof(int);
@@ -441,20 +460,18 @@ int da_decode_fwd(const da_decode_args_t *a) {
         } else {
             std::lock_guard<std::mutex> lock(st->mu);
             if (st->scratch_bytes < plan.scratch_bytes) {
-                // Grow-only.  The old buffer may still be in use by queued kernels: free it only after
-                // the device has drained (growth is rare: sizes settle after the first few calls).
-                if (st->scratch) {
-                    cudaDeviceSynchronize();
-                    cudaFree(st->scratch);
-                    st->scratch = nullptr;
-                    st->scratch_bytes = 0;
-                }
-                size_t want = plan.scratch_bytes + plan.scratch_bytes / 4;
-                cudaError_t e = cudaMalloc(&st->scratch, want);
+                // Grow-only, at least doubling.  Kernels already queued may still use the old buffer, so it
+                // is parked instead of freed (no device synchronisation inside a decode call); doubling
+                // keeps all parked buffers together below the size of the live one.
+                size_t want = st->scratch_bytes * 2 > plan.scratch_bytes ? st->scratch_bytes * 2 : plan.scratch_bytes;
+                void *fresh = nullptr;
+                cudaError_t e = cudaMalloc(&fresh, want);
                 if (e != cudaSuccess) {
                     return fail(DA_ERR_WORKSPACE, "cudaMalloc(%zu) for split scratch: %s", want,
                                 cudaGetErrorString(e));
                 }
+                if (st->scratch) st->retired.push_back(st->scratch);
+                st->scratch = fresh;
                 st->scratch_bytes = want;
             }
             scratch = static_cast<float *>(st->scratch);
@@ -473,6 +490,7 @@ int da_decode_fwd(const da_decode_args_t *a) {
     p.kv_pos_offset = a->kv_pos_offset;
     p.kv_total_len = a->kv_total_len;
     p.status = st->status_ptr;
+    p.launch_id = next_launch_id();
     p.block_table = a->block_table;
     p.block_table_stride = a->block_table_stride;
     p.page_shift = 0;
@@ -506,17 +524,14 @@ int da_decode_fwd(const da_decode_args_t *a) {
     }
     // Rows per TMA box: the tile, or a page when pages are shorter than the tile.
     const int box_keys = (a->block_table && a->page_size < plan.tile_keys) ? a->page_size : plan.tile_keys;
-    if (a->block_table && a->page_size < 64 && plan.shape == Shape::kMlaTc && mla_pair_enabled()) {
-        return fail(DA_ERR_UNSUPPORTED, "the cluster-pair MLA kernel needs pages of at least 64 keys");
-    }
 
     const bool bf16 = a->is_bf16 != 0;
     KvMaps maps;
     memset(&maps, 0, sizeof(maps));
     // Tiled TMA needs a global stride that is a multiple of 16 bytes (checked above: 8 elements) and
     // a box of at most 256 elements per dimension; the latent-KV rows (576) keep the row-wise path.
-    p.use_tmap = (plan.shape != Shape::kMla) && (plan.shape != Shape::kMlaTc) && (plan.shape != Shape::kGqaTc) &&
-                 !getenv("DA_NO_TMAP");
+    p.use_tmap = (plan.shape != Shape::kMla) && (plan.shape != Shape::kMlaTc) && (plan.shape != Shape::kMla2Sm) &&
+                 (plan.shape != Shape::kGqaTc);
     CUtensorMap tm_q;
     memset(&tm_q, 0, sizeof(tm_q));
     if (plan.shape == Shape::kGqaTc) {
@@ -535,6 +550,20 @@ int da_decode_fwd(const da_decode_args_t *a) {
         rc = make_tensor_map(p.k, 3, kd, ks, kb, true, bf16, &maps.k);
         if (rc != DA_OK) return rc;
         rc = make_tensor_map(p.v, 3, kd, vs, kb, true, bf16, &maps.v);
+        if (rc != DA_OK) return rc;
+    }
+    if (plan.shape == Shape::kMla2Sm) {
+        // q as [batch][head_q][576] in boxes {64, min(64, head_q), 1} (one CTA's heads; rows past head_q read as
+        // zeros); the latent cache as [rows][576] in boxes {64, 64 keys}; both 128-byte-swizzled.
+        const uint64_t qd[3] = {576, (uint64_t)a->head_q, (uint64_t)a->batch};
+        const uint64_t qs[2] = {576 * 2, (uint64_t)p.q_row_stride * 2};
+        const uint32_t qb[3] = {64, (uint32_t)(a->head_q < 64 ? a->head_q : 64), 1};
+        rc = make_tensor_map(p.q, 3, qd, qs, qb, true, bf16, &maps.k);
+        if (rc != DA_OK) return rc;
+        const uint64_t kd[2] = {576, kMapRows};
+        const uint64_t ks[1] = {(uint64_t)p.k_row_stride * 2};
+        const uint32_t kb[2] = {64, 64};
+        rc = make_tensor_map(p.k, 2, kd, ks, kb, true, bf16, &maps.v);
         if (rc != DA_OK) return rc;
     }
     if (plan.shape == Shape::kMlaTc) {
@@ -566,10 +595,8 @@ int da_decode_fwd(const da_decode_args_t *a) {
         case Shape::kD256: e = launch_split_d256(bf16, plan.heads, p, maps, stream); break;
         case Shape::kMla: e = launch_split_mla_simt(bf16, plan.heads, p, maps, stream); break;
         case Shape::kGqaTc: e = launch_gqa_tc(bf16, (int)a->dim, p, tm_q, maps.k, maps.v, stream); break;
-        case Shape::kMlaTc:
-            e = mla_pair_enabled() ? launch_mla_pair(bf16, p, maps.v, stream)
-                                   : launch_mla_tc(bf16, p, maps.k, maps.v, stream);
-            break;
+        case Shape::kMlaTc: e = launch_mla_tc(bf16, p, maps.k, maps.v, stream); break;
+        case Shape::kMla2Sm: e = launch_mla_2sm(bf16, p, maps.k, maps.v, stream); break;
         default: e = cudaErrorInvalidValue; break;
     }
     if (e != cudaSuccess) return fail(DA_ERR_CUDA, "split kernel launch: %s", cudaGetErrorString(e));
@@ -626,19 +653,19 @@ int da_decode_fwd_host(const da_decode_args_t *h) {
     const size_t cu_b = up((size_t)(h->batch + 1) * 4);
     const size_t lse_b = h->lse ? up((size_t)h->batch * h->head_q * 4) : 0;
     const size_t need = q_b + k_b + v_b + o_b + cu_b + lse_b;
-    {
-        std::lock_guard<std::mutex> lock(st->mu);
-        if (st->staging_bytes < need) {
-            if (st->staging) {
-                cudaDeviceSynchronize();
-                cudaFree(st->staging);
-                st->staging = nullptr;
-                st->staging_bytes = 0;
-            }
-            cudaError_t e = cudaMalloc(&st->staging, need);
-            if (e != cudaSuccess) return fail(DA_ERR_WORKSPACE, "cudaMalloc(%zu) staging: %s", need, cudaGetErrorString(e));
-            st->staging_bytes = need;
+    // The staging buffer is one per device and may be regrown: the lock is held until this call has
+    // drained its stream, so concurrent host-buffer calls on one device take turns.
+    std::lock_guard<std::mutex> staging_lock(st->staging_mu);
+    if (st->staging_bytes < need) {
+        if (st->staging) {
+            cudaDeviceSynchronize();
+            cudaFree(st->staging);
+            st->staging = nullptr;
+            st->staging_bytes = 0;
         }
+        cudaError_t e = cudaMalloc(&st->staging, need);
+        if (e != cudaSuccess) return fail(DA_ERR_WORKSPACE, "cudaMalloc(%zu) staging: %s", need, cudaGetErrorString(e));
+        st->staging_bytes = need;
     }
     char *base = static_cast<char *>(st->staging);
     da_decode_args_t d = *h;
@@ -743,8 +770,8 @@ int da_device_status(void) {
     e = cudaMemcpy(&word, st->status_ptr, sizeof(int), cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return fail(DA_ERR_CUDA, "cudaMemcpy(status): %s", cudaGetErrorString(e));
     if (word != kStatusOk) {
-        int zero = 0;
-        cudaMemcpy(st->status_ptr, &zero, sizeof(int), cudaMemcpyHostToDevice);
+        const int zero[2] = {0, 0};
+        cudaMemcpy(st->status_ptr, zero, sizeof(zero), cudaMemcpyHostToDevice);
         return fail(DA_ERR_TIMEOUT, "a kernel gave up a bounded wait (status word %d)", word);
     }
     return DA_OK;

@@ -12,7 +12,9 @@
 namespace da {
 
 // Device status word values (written by a kernel whose bounded wait ran out; read by the host with
-// da_device_status()).  0 means no kernel reported a problem.
+// da_device_status()).  0 means no kernel reported a problem.  The status lives in a two-int block per
+// device: [0] the status word, [1] the id of the launch that timed out (0 = none), which lets the CTAs
+// of that launch that have not started yet retire at once without affecting any later launch.
 enum : int { kStatusOk = 0, kStatusWaitTimeout = 1 };
 
 // Arguments of the split-KV kernels.  It plays the role of the reference's DecodingParams
@@ -29,7 +31,8 @@ struct SplitParams {
     const int *cu_seq_k;       // [batch + 1]
     const int *kv_pos_offset;  // optional [batch]: position of key 0 inside a longer sequence (ALiBi)
     const int *kv_total_len;   // optional [batch]: length of that longer sequence (ALiBi)
-    int *status;               // device status word
+    int *status;               // device status block: [0] status word, [1] id of a launch that gave up
+    int launch_id;             // this launch's id (never 0), compared with status[1]
     const int *batch_order;    // optional [batch]: sequence handled by grid slice z (longest first), else z itself
     const int *block_table;    // optional [batch, block_table_stride]: page of each page_size-key block (paged cache)
     long long block_table_stride;
@@ -45,6 +48,24 @@ struct SplitParams {
     int use_tmap;      // full tiles are fetched with one tiled TMA copy through the tensor maps
     float scale_log2;  // softmax scale * log2(e)
 };
+
+// Has an earlier CTA of this very launch given up a bounded wait?  (Later launches carry another id
+// and are not affected; a replayed CUDA graph repeats its id, so after a timeout inside a replay
+// the host should read da_device_status(), which clears the block, before replaying again.)
+__device__ __forceinline__ bool launch_aborted(const SplitParams &p) {
+    return reinterpret_cast<volatile int *>(p.status)[1] == p.launch_id;
+}
+__device__ __forceinline__ void report_timeout(const SplitParams &p) {
+    atomicExch(p.status, kStatusWaitTimeout);
+    atomicExch(p.status + 1, p.launch_id);
+}
+// Last key (exclusive) of key-range split `split`: splits cover chunk_keys keys each; the last one
+// runs to the end of the sequence, so a sequence longer than the max_seq_k the plan was sized for
+// is still read completely.
+__device__ __forceinline__ int split_key_end(const SplitParams &p, int split, int len) {
+    const long long e = (long long)(split + 1) * p.chunk_keys;
+    return (split == p.num_splits - 1 || e > len) ? len : (int)e;
+}
 
 // Row of the cache that holds key `key0` of sequence `b`.  Packed cache: the sequence's rows are
 // consecutive from cu_seq_k[b].  Paged cache: the block table names the page.  Rows are consecutive for
@@ -129,10 +150,27 @@ __device__ __forceinline__ void bulk_copy_g2s_hint(void *dst_smem, const void *s
         "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
         : "memory");
 }
+// Shared -> global bulk copy (TMA engine, no tensor map): addresses and size multiples of 16 bytes.  The
+// copies of a thread form a group (commit); wait_read returns once their source bytes have been read,
+// which a thread must do before the shared memory is reused or the CTA exits.
+__device__ __forceinline__ void bulk_store_s2g(void *dst_gmem, const void *src_smem, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst_gmem), "r"(smem_u32(src_smem)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 // 16-byte asynchronous copy global -> shared through the load/store unit (not the TMA engine).  With
 // src_bytes = 0 nothing is read and the 16 bytes are zero-filled.
 __device__ __forceinline__ void cp_async16(void *dst_smem, const void *src_gmem, uint32_t src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst_smem)), "l"(src_gmem), "r"(src_bytes)
+                 : "memory");
+}
+// The same asking L2 to fetch the whole 256-byte block around a missing sector (what the tensor maps of this
+// library ask for too): a stream that is the first to touch its rows then reads DRAM in 256-byte pieces.
+__device__ __forceinline__ void cp_async16_l2_256(void *dst_smem, const void *src_gmem, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global.L2::256B [%0], [%1], 16, %2;" ::"r"(smem_u32(dst_smem)), "l"(src_gmem),
+                 "r"(src_bytes)
                  : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }

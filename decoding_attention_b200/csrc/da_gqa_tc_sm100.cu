@@ -69,19 +69,6 @@ struct GqaCfg {
 };
 constexpr float kRescaleThreshold = 8.0f;
 
-#ifdef DA_GQA_PROFILE
-// Development aid (not compiled into the shipped library): cycles CTA (0,0,0) spends in each step.
-__device__ long long g_gqa_prof[64];
-#define PROF_DECL long long prof_t0 = 0, prof_acc[16] = {}; (void)prof_t0
-#define PROF_BEGIN() prof_t0 = clock64()
-#define PROF_END(slot) do { long long now_ = clock64(); prof_acc[(slot) & 15] += now_ - prof_t0; prof_t0 = now_; } while (0)
-#define PROF_FLUSH(base) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0) { for (int i_ = 0; i_ < 16; ++i_) g_gqa_prof[(base) + i_] += prof_acc[i_]; } } while (0)
-#else
-#define PROF_DECL
-#define PROF_BEGIN()
-#define PROF_END(slot)
-#define PROF_FLUSH(base)
-#endif
 
 // kShortPages: the cache is paged with pages shorter than a key tile, which is then fetched page by page
 // (a separate instantiation, so that the common case keeps its straight-line address arithmetic).
@@ -108,9 +95,9 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
     const int seq_begin = p.cu_seq_k[b];
     const int len = p.cu_seq_k[b + 1] - seq_begin;
     const int k_begin = split * p.chunk_keys;
-    const int k_end = min(len, k_begin + p.chunk_keys);
+    const int k_end = split_key_end(p, split, len);
     T *o_out = reinterpret_cast<T *>(p.o);
-    if (*reinterpret_cast<volatile int *>(p.status) != kStatusOk) return;  // an earlier CTA timed out: do not pile up
+    if (launch_aborted(p)) return;  // an earlier CTA of this launch timed out: do not pile up
 
     if (k_begin >= k_end) {
         if (p.num_splits == 1) {  // empty sequence: zero rows, LSE = -inf
@@ -258,22 +245,16 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             tc_fence_after();
             issue_qk(0);
         }
-        PROF_DECL;
         for (int t = 0; t < n_tiles && ok; ++t) {
-            PROF_BEGIN();
             if (t + 1 < n_tiles) {
                 const int t1 = t + 1;
                 ok = mbar_wait(&kv_full[t1 % kStages], (uint32_t)(t1 / kStages) & 1u, abort_flag);
-                PROF_END(0);
                 if (ok && t1 >= 2) ok = mbar_wait(&s_empty[t1 & 1], ((uint32_t)(t1 / 2) & 1u) ^ 1u, abort_flag);
-                PROF_END(1);
                 if (!ok) break;
                 tc_fence_after();
                 issue_qk(t1);
-                PROF_END(2);
             }
             ok = mbar_wait(&p_full[t & 1], (uint32_t)(t / 2) & 1u, abort_flag);
-            PROF_END(3);
             if (!ok) break;
             tc_fence_after();
             const int st = t % kStages;
@@ -286,9 +267,7 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             }
             umma_commit(&kv_empty[st], leader);
             umma_commit(&pv_done[t & 1], leader);
-            PROF_END(4);
         }
-        PROF_FLUSH(0);
         __syncwarp();
     } else if ((warp & 3) < active_quads) {
         // ------- softmax / epilogue -------
@@ -307,17 +286,14 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
         float m_ref = -INFINITY, l = 0.0f;
         uint32_t buf[32];
         float *rm = rowmax_s + strm * (2 * kRows);  // [2 halves][128] partial row maxima of this stream
-        PROF_DECL;
         int last_t = -1;
         int n_done = 0;  // tiles this thread has finished (use count of its stream's row_sync barrier)
         for (int t = strm; t < n_tiles; t += kStreams, ++n_done) {
-            PROF_BEGIN();
             const int sb = (kStreams == 2) ? strm : (t & 1);  // S buffer of this tile (= t & 1) and the barriers that go with it
             const int it = t >> 1;  // use count of those barriers
             const int key0 = k_begin + t * kTile + hf * kColsPer;
             const int rows = min(kTile, k_end - (k_begin + t * kTile)) - hf * kColsPer;  // valid columns of this thread
             ok = __all_sync(0xffffffffu, mbar_wait(&s_full[sb], (uint32_t)it & 1u, abort_flag));
-            PROF_END(0);
             if (!ok) break;
             tc_fence_after();
             tmem_ld32(lane_base + kColS + sb * kTile + hf * kColsPer, buf);
@@ -334,10 +310,8 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             }
             // The two threads of a row agree on the tile's row maximum.
             rm[hf * kRows + r] = mx;
-            PROF_END(1);
             mbar_arrive(&row_sync[strm]);
             ok = __all_sync(0xffffffffu, mbar_wait(&row_sync[strm], (uint32_t)n_done & 1u, abort_flag));
-            PROF_END(2);
             if (!ok) break;
             mx = fmaxf(mx, rm[(hf ^ 1) * kRows + r]);
             const bool raise = mx > m_ref + kRescaleThreshold;
@@ -368,7 +342,6 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                     tmem_wait_st();
                 }
             }
-            PROF_END(3);
             // P = exp2(S - m_ref), rounded to the input type, into the A-operand layout (8-key chunks).
             float sum = 0.0f;
 #pragma unroll
@@ -394,9 +367,7 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             tc_fence_before();
             mbar_arrive(&p_full[sb]);
             last_t = t;
-            PROF_END(4);
         }
-        if (warp == 0) PROF_FLUSH(16);
         // ---- merge the streams and write the row out ----
         float *l_part = rowmax_s + kStreams * 2 * kRows;  // [kColSplit threads of a row][128]
         float *m_strm = l_part + kColSplit * kRows;        // [kStreams][128]
@@ -479,7 +450,7 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
         }
     }
 
-    if (!ok && lane == 0) atomicExch(p.status, kStatusWaitTimeout);
+    if (!ok && lane == 0) report_timeout(p);
     __syncthreads();
     if (warp == kMmaWarp) {
         tc_fence_after();
@@ -489,16 +460,6 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
 
 }  // namespace
 
-#ifdef DA_GQA_PROFILE
-extern "C" void da_debug_gqa_prof(long long *out, int reset) {
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out, g_gqa_prof, sizeof(long long) * 64);
-    if (reset) {
-        long long z[64] = {};
-        cudaMemcpyToSymbol(g_gqa_prof, z, sizeof(z));
-    }
-}
-#endif
 
 SplitVariantInfo split_info_gqa_tc() { return {kTile, kRows, 1}; }
 

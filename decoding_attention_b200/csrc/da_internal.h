@@ -39,14 +39,16 @@ SplitVariantInfo split_info_mla_simt(int heads);
 cudaError_t launch_mla_tc(bool bf16, const SplitParams &p, const CUtensorMap &tm_q, const CUtensorMap &tm_k,
                           cudaStream_t s);
 SplitVariantInfo split_info_mla_tc();
+// The same shape on SM pairs (da_mla_2sm_sm100.cu): clusters of two CTAs issue cta_group::2 MMAs, each CTA
+// holding 64 of the 128 head rows.  tm_q: box {64, min(64, head_q), 1}; tm_k: box {64, 64 keys}.  Needs a
+// packed cache or pages of at least 64 keys.
+cudaError_t launch_mla_2sm(bool bf16, const SplitParams &p, const CUtensorMap &tm_q, const CUtensorMap &tm_k,
+                           cudaStream_t s);
+SplitVariantInfo split_info_mla_2sm();
 // Tensor-core kernel for head dims 64 / 128 / 256 and groups of up to 128 query heads per KV head (da_gqa_tc_sm100.cu).
 cudaError_t launch_gqa_tc(bool bf16, int dim, const SplitParams &p, const CUtensorMap &tm_q, const CUtensorMap &tm_k,
                           const CUtensorMap &tm_v, cudaStream_t s);
 SplitVariantInfo split_info_gqa_tc();
-// Cluster-pair variant (da_mla_pair_sm100.cu): the two CTAs of a key range split the 576-long
-// contraction and the output columns and swap partial scores through distributed shared memory.
-cudaError_t launch_mla_pair(bool bf16, const SplitParams &p, const CUtensorMap &tm_k, cudaStream_t s);
-SplitVariantInfo split_info_mla_pair();
 
 // Merge of split / shard partials (da_merge.cu).  cu_seq_k and chunk_keys (both optional) limit a
 // row to the splits that cover keys; without them every part is read.

@@ -1,0 +1,674 @@
+// Latent-KV (MLA) decode attention on the sm_100a tensor cores, two SMs per key range:
+// tcgen05.mma.cta_group::2 with accumulators in tensor memory (TMEM), operands staged by TMA and
+// cp.async.
+//
+// Shape: up to 128 query heads share one KV head whose rows hold 576 values, V being the first 512
+// of them (the reference runs this shape through its generic kernel, one CTA per query head:
+// csrc/kernel/decoding_attn/decoding_fwd_hd576_hdv512.cu:9-17, so every K row is fetched once per
+// head).  A cluster of two CTAs owns one (sequence, key range) and walks it in tiles of 128 keys:
+//     S[128 heads x 128 keys]  = Q[128 x 576] . K_tile[128 x 576]^T     36 MMAs  M128 N128 K16
+//     O[128 heads x 512]      += P[128 x 128] . V_tile[128 x 512]       16 MMAs  M128 N256 K16
+// Both are pair MMAs: CTA c holds heads 64c..64c+63 (its rows of Q, S, P and O) and supplies one half
+// of every B operand from its own shared memory -- keys 64c..64c+63 of the tile for S, 256 of the 512
+// V columns (dims 256c..256c+255) of all 128 keys for P.V.  Nothing is computed twice, every K row is
+// read by one CTA for S, and the 128 x 512 fp32 output fits because a CTA's 64 x 512 share is 128
+// TMEM lanes x 256 columns.  What a CTA reads per tile: its 64 keys x 576 dims for S (nine 8 KB
+// blocks streamed through a ring, each released by a tcgen05.commit right after its four MMAs) and
+// 128 keys x 256 dims for P.V (two 32 KB half-tile slots), 136 KB against 2 x 72 KB for a kernel
+// whose two CTAs work apart; the second reader of a row hits L2.
+//
+// TMEM columns per CTA: S0 | S1 (64 each: lanes 0-63 keys 0-63 of the tile, lanes 64-127 keys 64-127,
+// rows = this CTA's heads) | O (256: lanes 0-63 dims 0-255, lanes 64-127 dims 256-511) | Q (4 x 32:
+// the first four 64-dim blocks of Q as 16-bit pairs, head r in lanes r and r + 64, read as the A operand).
+// Warp roles (320 threads): warps 0-3 softmax/epilogue -- thread l owns TMEM lane l, i.e. head
+// (l & 63) and key half (l >> 6); the two threads of a head swap their tile maxima through shared
+// memory, keep one reference max, and write P (16-bit, 128-byte-swizzled K-major) to shared memory;
+// warp 4 TMA producer (Q blocks, streamed K blocks); warp 5 TMEM allocation and, in the rank-0 CTA,
+// MMA issue for the pair; warps 6-9 V loaders (16-byte cp.async straight into the swizzled layout,
+// because one SM's TMA engine alone moves only about 21 B/clk).
+// Barriers the MMA thread waits on live in the rank-0 CTA and count arrivals / bytes from both CTAs;
+// barriers that release buffers or publish S are signalled in both CTAs by one multicast commit.
+// Online softmax with a lazy reference max (raised only when exceeded by 2^8), so O is rescaled a
+// handful of times.  Every wait is bounded; on expiry the CTA records the timeout and still frees
+// its TMEM.
+#include <type_traits>
+
+#include "da_internal.h"
+#include "da_tcgen05.cuh"
+
+namespace da {
+namespace {
+
+constexpr int kHeads = 128;        // M of both contractions (pair)
+constexpr int kRows = 64;          // heads per CTA
+constexpr int kDim = 576;
+constexpr int kDimV = 512;
+constexpr int kTile = 128;         // keys per pair tile
+constexpr int kHalf = 64;          // keys per CTA in S / per V half-tile slot
+constexpr int kBlocks = kDim / 64; // 64-element (128-byte) column blocks of a row
+constexpr int kVBlocks = 4;        // V blocks per CTA (256 of the 512 output dims)
+#ifndef DA_MLA2_QTMEM
+#define DA_MLA2_QTMEM 4
+#define DA_MLA2_ASLOTS 9
+#define DA_MLA2_VSLOTS 3
+#define DA_MLA2_PBUFS 1
+#endif
+#ifndef DA_MLA2_TMABLOCKS
+#define DA_MLA2_TMABLOCKS 9
+#endif
+#ifndef DA_MLA2_CPASYNC
+#define DA_MLA2_CPASYNC cp_async16
+#endif
+#ifndef DA_MLA2_LAG
+#define DA_MLA2_LAG 1
+#endif
+constexpr int kQTmemBlocks = DA_MLA2_QTMEM;    // Q blocks 0..3 live in TMEM
+constexpr int kQSmemBlocks = kBlocks - kQTmemBlocks;
+constexpr int kBlockBytes = 64 * 128;  // [64 rows x 64 elements], 128-byte swizzle: a Q, K or P block
+// K blocks 0 .. kTmaBlocks-1 of a tile come by TMA through the ring, the others (if any) by cp.async into one slot.
+// Measured on B200 (batch 128 x 4096 keys): all nine by TMA 181 us; five by TMA and four by cp.async 283 us -- faster
+// per tile on an idle GPU (3 540 against 4 170 cycles) but the load/store path degrades when every SM pulls 96 KB
+// per tile through it (one wave of 74 pairs: 149 us against 90 us).
+constexpr int kTmaBlocks = DA_MLA2_TMABLOCKS;
+constexpr int kLsuBlocks = kBlocks - kTmaBlocks;
+constexpr int kASlots = DA_MLA2_ASLOTS;         // ring of TMA-streamed K blocks
+constexpr int kVSlots = DA_MLA2_VSLOTS;         // ring of V half-tiles
+constexpr int kVSlotBytes = kVBlocks * kBlockBytes;
+constexpr int kPBufs = DA_MLA2_PBUFS;          // P tiles in shared memory
+constexpr int kPBytes = 2 * kBlockBytes;  // [64 heads x 128 keys]
+constexpr int kOffQ = 0;
+constexpr int kOffA = kOffQ + kQSmemBlocks * kBlockBytes;
+constexpr int kOffS4 = kOffA + kASlots * kBlockBytes;   // K blocks 5..8 of the current tile
+constexpr int kOffV = kOffS4 + kLsuBlocks * kBlockBytes;  // (no such slot when all blocks come by TMA)
+constexpr int kOffP = kOffV + kVSlots * kVSlotBytes;
+constexpr int kOffBar = kOffP + kPBufs * kPBytes;
+// q_full, q_tmem, q_stage_full, q_copied, s4_full, s4_empty, a_full/a_empty[kASlots], v_full/v_empty[kVSlots], s_full[2], p_full[2], pv_done[2]
+constexpr int kNumBars = 6 + 2 * kASlots + 2 * kVSlots + 6;
+constexpr int kOffMisc = kOffBar + kNumBars * 8;          // tmem slot, abort flag
+constexpr int kOffXch = kOffMisc + 16;                    // float [2][128] tile maxima, float [128] row sums
+constexpr int kSmemBytes = kOffXch + 3 * 128 * 4 + 1024;  // + alignment slack
+constexpr int kLoaderWarps = 4;
+constexpr int kLoaderThreads = kLoaderWarps * 32;
+constexpr int kThreads = 192 + kLoaderThreads;
+constexpr int kTmemCols = 512;
+constexpr int kColS = 0;      // two S buffers of 64 columns
+constexpr int kColO = 128;    // 256 output columns
+constexpr int kColQ = 384;    // kQTmemBlocks * 32 columns
+static_assert(kColQ + kQTmemBlocks * 32 <= kTmemCols, "TMEM budget");
+static_assert(kLsuBlocks == 0 || kLsuBlocks == 4, "the cp.async slot holds four blocks");
+static_assert(kQTmemBlocks <= kTmaBlocks, "the blocks loaded by cp.async meet Q blocks that live in shared memory");
+static_assert(kQTmemBlocks * kBlockBytes <= kVSlotBytes && kVSlots >= 2, "Q blocks 0..3 are staged in the last V slot");
+static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+static_assert(128 * (256 * 4 + 16) <= kOffP - kOffA, "the epilogue stages its output in the idle rings");
+constexpr float kRescaleThreshold = 8.0f;
+
+template <typename T>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+
+    pdl_launch_dependents();  // the merge kernel may be scheduled behind this grid's last CTAs
+    const uint32_t rank = cluster_ctarank();
+    const int split = blockIdx.y;
+    if (p.batch_order) pdl_wait();  // written by the order kernel launched just before this one
+    const int b = p.batch_order ? p.batch_order[blockIdx.z] : (int)blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int seq_begin = p.cu_seq_k[b];
+    const int len = p.cu_seq_k[b + 1] - seq_begin;
+    const int k_begin = split * p.chunk_keys;
+    const int k_end = split_key_end(p, split, len);
+    T *o_out = reinterpret_cast<T *>(p.o);
+    const int head0 = (int)rank * kRows;  // first head of this CTA
+    // (both CTAs of a pair take the same branch here: the conditions do not depend on the rank)
+    if (launch_aborted(p)) return;  // an earlier CTA of this launch timed out: do not pile up
+
+    if (k_begin >= k_end) {
+        if (p.num_splits == 1) {  // empty sequence: zero rows, LSE = -inf
+            const int nh = min(kRows, p.head_q - head0);
+            for (int idx = tid; idx < nh * kDimV; idx += kThreads) {
+                const int h = head0 + idx / kDimV, d = idx % kDimV;
+                if (o_out) o_out[(size_t)b * p.o_row_stride + (size_t)h * kDimV + d] = from_float<T>(0.0f);
+                if (p.o_f32) p.o_f32[((size_t)b * p.head_q + h) * kDimV + d] = 0.0f;
+            }
+            if (p.lse && tid < nh) p.lse[(size_t)b * p.head_q + head0 + tid] = -INFINITY;
+        }
+        return;
+    }
+    const int n_tiles = (k_end - k_begin + kTile - 1) / kTile;
+
+    uint8_t *q_s = smem + kOffQ;
+    uint8_t *a_s = smem + kOffA;
+    uint8_t *s4_s = smem + kOffS4;
+    uint8_t *v_s = smem + kOffV;
+    uint8_t *p_s = smem + kOffP;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBar);
+    uint64_t *q_full = bars;       // rank 0: Q blocks of both CTAs are in shared memory
+    uint64_t *q_tmem = bars + 1;   // rank 0: Q blocks of both CTAs are in TMEM
+    uint64_t *q_stage_full = bars + 2;  // this CTA: Q blocks 0..3 landed in the staging slot
+    uint64_t *q_copied = bars + 3;      // this CTA: the softmax warps have moved them to TMEM
+    uint64_t *s4_full = bars + 4;       // rank 0: K blocks 5..8 landed in both CTAs
+    uint64_t *s4_empty = bars + 5;
+    uint64_t *a_full = bars + 6;   // rank 0: streamed K block landed in both CTAs
+    uint64_t *a_empty = a_full + kASlots;
+    uint64_t *v_full = a_empty + kASlots;  // rank 0: V half-tile landed in both CTAs
+    uint64_t *v_empty = v_full + kVSlots;
+    uint64_t *s_full = v_empty + kVSlots;
+    uint64_t *p_full = s_full + 2;         // rank 0: P written by both CTAs
+    uint64_t *pv_done = p_full + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + kOffMisc);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    float *x_max = reinterpret_cast<float *>(smem + kOffXch);  // [2][128]
+    float *x_sum = x_max + 256;                                  // [128]
+
+    if (tid == 0) {
+        mbar_init(q_full, 2);
+        mbar_init(q_tmem, 8);
+        mbar_init(q_stage_full, 1);
+        mbar_init(q_copied, 4);
+        mbar_init(s4_full, 2 * kLoaderWarps);
+        mbar_init(s4_empty, 1);
+        for (int s = 0; s < kASlots; ++s) {
+            mbar_init(&a_full[s], 1);
+            mbar_init(&a_empty[s], 1);
+        }
+        for (int s = 0; s < kVSlots; ++s) {
+            mbar_init(&v_full[s], 2 * kLoaderWarps);
+            mbar_init(&v_empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&s_full[s], 1);
+            mbar_init(&p_full[s], 8);
+            mbar_init(&pv_done[s], 1);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 5) tmem_alloc(tmem_slot, kTmemCols);
+    tc_fence_before();
+    cluster_sync_all();  // both CTAs' barriers exist before anybody arrives on them remotely
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // shared::cluster addresses of the rank-0 CTA's barriers (what the peer arrives on)
+    auto lead = [&](uint64_t *bar) { return map_to_cta(smem_u32(bar), 0); };
+
+    constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+    constexpr uint32_t kIdescQK = instr_desc(kFmt, 0, kHeads, kTile);
+    constexpr uint32_t kIdescPV = instr_desc(kFmt, 1, kHeads, 256);
+    bool ok = true;
+    const T *k_g = reinterpret_cast<const T *>(p.k);
+
+    if (warp == 4) {
+        // ---------------- TMA producer: Q blocks 4..8, then this CTA's 64 keys of every tile ----------------
+        const int q_rows = min(kRows, p.head_q - head0);  // rows the Q box holds (<= 0: this CTA is all padding)
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_q);
+            tma_prefetch_desc(&tm_k);
+            if (q_rows > 0) {
+                // a box always delivers its full size: rows past head_q arrive as zeros
+                mbar_arrive_expect_tx_remote(lead(q_full), (uint32_t)(kQSmemBlocks * min(p.head_q, kRows) * 128));
+                for (int j = 0; j < kQSmemBlocks; ++j)
+                    tma2_load_3d(q_s + j * kBlockBytes, &tm_q, (kQTmemBlocks + j) * 64, head0, b, lead(q_full));
+                // blocks 0..3 pass through the last V slot on their way to TMEM
+                mbar_arrive_expect_tx(q_stage_full, (uint32_t)(kQTmemBlocks * min(p.head_q, kRows) * 128));
+                for (int j = 0; j < kQTmemBlocks; ++j)
+                    tma_load_tile_3d(v_s + (kVSlots - 1) * kVSlotBytes + j * kBlockBytes, &tm_q, j * 64, head0, b, q_stage_full);
+            } else {
+                mbar_arrive_remote(lead(q_full));
+            }
+        }
+        int slot = 0;
+        uint32_t round = 0;
+        for (int t = 0; t < n_tiles && ok; ++t) {
+            const int key0 = k_begin + t * kTile + (int)rank * kHalf;  // this CTA's first key of the tile
+            const int rows = max(0, min(kHalf, k_end - key0));
+            const size_t tok0 = rows > 0 ? kv_tile_row(p, b, seq_begin, key0) : 0;
+            for (int j = 0; j < kTmaBlocks && ok; ++j) {
+                if (round > 0) ok = mbar_wait(&a_empty[slot], (round & 1u) ^ 1u, abort_flag);
+                if (!ok) break;
+                uint8_t *dst = a_s + slot * kBlockBytes;
+                // a_full[slot] of the rank-0 CTA takes ONE arrival per use, rank 0's, which also announces the
+                // bytes: its own block when that comes by TMA, and always the peer's 8 KB -- delivered by the
+                // peer's TMA copy, or counted by hand when the peer had to write a ragged block with stores.
+                // (No remote arrival per block: a cluster-scope release costs about a thousand cycles.)
+                if (rows == kHalf) {
+                    if (lane == 0) {
+                        if (rank == 0) mbar_arrive_expect_tx(&a_full[slot], 2 * kBlockBytes);
+                        tma2_load_2d(dst, &tm_k, j * 64, (int)tok0, lead(&a_full[slot]));
+                    }
+                } else {
+                    // ragged end of the key range: plain loads, rows past the end zeroed (the tensor map
+                    // must not be asked for rows beyond the sequence)
+                    for (int i = lane; i < kHalf * 8; i += 32) {
+                        const int r = i >> 3, cc = i & 7;
+                        uint4 v = make_uint4(0, 0, 0, 0);
+                        if (r < rows) v = *reinterpret_cast<const uint4 *>(k_g + (tok0 + r) * p.k_row_stride + j * 64 + cc * 8);
+                        *reinterpret_cast<uint4 *>(dst + r * 128 + ((cc ^ (r & 7)) << 4)) = v;
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (rank == 0) {
+                            mbar_arrive_expect_tx(&a_full[slot], kBlockBytes);
+                        } else {
+                            fence_acq_rel_cluster();
+                            mbar_complete_tx_remote(lead(&a_full[slot]), kBlockBytes);
+                        }
+                    }
+                }
+                if (++slot == kASlots) {
+                    slot = 0;
+                    ++round;
+                }
+            }
+            __syncwarp();
+        }
+    } else if (warp == 5) {
+        // ---------------- MMA issuer (rank 0 issues for the pair) ----------------
+        if (rank == 0) {
+            const uint32_t leader = elect_one();
+            const uint64_t q_desc0 = smem_desc(smem_u32(q_s), 16, 1024, 2);
+            const uint64_t a_desc0 = smem_desc(smem_u32(a_s), 16, 1024, 2);
+            const uint64_t s4_desc0 = smem_desc(smem_u32(s4_s), 16, 1024, 2);
+            const uint64_t p_desc0 = smem_desc(smem_u32(p_s), 16, 1024, 2);
+            const uint64_t v_desc0 = smem_desc(smem_u32(v_s), kBlockBytes, 1024, 2);  // V slot, MN-major
+            const uint32_t q_tmem_addr = tmem_base + kColQ;
+            int a_slot = 0;
+            uint32_t a_round = 0;
+                auto issue_qk = [&](int t) -> bool {
+                const uint32_t d = tmem_base + kColS + (t & 1) * 64;
+#pragma unroll
+                for (int j = 0; j < kTmaBlocks; ++j) {
+                    if (!mbar_wait(&a_full[a_slot], a_round & 1u, abort_flag)) return false;
+                    tc_fence_after();
+                    const uint64_t bd = a_desc0 + (uint64_t)((a_slot * kBlockBytes) >> 4);
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        if (j < kQTmemBlocks) {
+                            umma2_ts(d, q_tmem_addr + j * 32 + ks * 8, bd + (uint64_t)(ks * 2), kIdescQK, (j | ks) ? 1u : 0u, leader);
+                        } else {
+                            umma2_ss(d, q_desc0 + (uint64_t)((((j - kQTmemBlocks) * kBlockBytes) >> 4) + ks * 2),
+                                     bd + (uint64_t)(ks * 2), kIdescQK, (j | ks) ? 1u : 0u, leader);
+                        }
+                    }
+                    umma2_commit_both(&a_empty[a_slot], leader);
+                    if (++a_slot == kASlots) {
+                        a_slot = 0;
+                        ++a_round;
+                    }
+                }
+                if (kLsuBlocks > 0) {
+                    if (!mbar_wait(s4_full, (uint32_t)t & 1u, abort_flag)) return false;
+                    tc_fence_after();
+                }
+#pragma unroll
+                for (int j = kTmaBlocks; j < kBlocks; ++j) {
+                    const uint64_t bd = s4_desc0 + (uint64_t)(((j - kTmaBlocks) * kBlockBytes) >> 4);
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        umma2_ss(d, q_desc0 + (uint64_t)((((j - kQTmemBlocks) * kBlockBytes) >> 4) + ks * 2),
+                                 bd + (uint64_t)(ks * 2), kIdescQK, 1u, leader);
+                    }
+                }
+                if (kLsuBlocks > 0) umma2_commit_both(s4_empty, leader);
+                umma2_commit_both(&s_full[t & 1], leader);
+                return true;
+            };
+            ok = mbar_wait(q_full, 0, abort_flag);
+            if (ok) ok = mbar_wait(q_tmem, 0, abort_flag);
+            if (ok) {
+                tc_fence_after();
+                ok = issue_qk(0);
+            }
+            for (int t = 0; t < n_tiles && ok; ++t) {
+                if (t + 1 < n_tiles) {
+                    ok = issue_qk(t + 1);
+                    if (!ok) break;
+                }
+                ok = mbar_wait(&p_full[t & 1], (uint32_t)(t / 2) & 1u, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d = tmem_base + kColO;
+                const uint64_t pd = p_desc0 + (uint64_t)((((t % kPBufs) * kPBytes)) >> 4);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int i = 2 * t + h;
+                    const int vs = i % kVSlots;
+                    ok = mbar_wait(&v_full[vs], (uint32_t)(i / kVSlots) & 1u, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t vd = v_desc0 + (uint64_t)((vs * kVSlotBytes) >> 4);
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        // A = P[64 heads x 16 keys] of key half h; B = V[16 keys x 128 dims] per CTA, blocks {0,1} then {2,3}
+                        const uint64_t ad = pd + (uint64_t)(((h * kBlockBytes) >> 4) + ks * 2);
+                        const uint64_t bd = vd + (uint64_t)((ks * 16 * 128) >> 4);
+                        umma2_ss(d, ad, bd, kIdescPV, (t | h | ks) ? 1u : 0u, leader);
+                        umma2_ss(d + 128, ad, bd + (uint64_t)((2 * kBlockBytes) >> 4), kIdescPV, (t | h | ks) ? 1u : 0u, leader);
+                    }
+                    umma2_commit_both(&v_empty[vs], leader);
+                }
+                if (!ok) break;
+                umma2_commit_both(&pv_done[t & 1], leader);
+            }
+        }
+        __syncwarp();
+    } else if (warp >= 6) {
+        // ---------------- V loaders: this CTA's 256 dims of all 128 keys of a tile, half-tile by half-tile ----------------
+        // Jobs of 32 KB each, in the order the tensor pipe needs them: K blocks 5..8 of tile 0, then per tile t
+        // the same blocks of tile t+1 and the two V half-tiles of tile t.  A job is published (its barrier in the
+        // rank-0 CTA gets this warp's arrival) once the next one has been issued and its own bytes have landed,
+        // so two jobs are in flight.
+        const int lt = tid - 6 * 32;  // 0..127
+        // Published with a lag of kLag jobs: job n's barrier gets this warp's arrival once jobs n+1 .. n+kLag have
+        // been issued and job n's bytes have landed, so kLag + 1 jobs are in flight.
+        constexpr int kLag = DA_MLA2_LAG;
+        uint32_t pend_bar[kLag];
+        int n_pend = 0;
+        auto publish_oldest = [&](auto newer) {  // newer: jobs issued after the oldest unpublished one
+            cp_async_wait<decltype(newer)::value>();
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_remote_cta(pend_bar[0]);
+#pragma unroll
+            for (int x = 0; x + 1 < kLag; ++x) pend_bar[x] = pend_bar[x + 1];
+            --n_pend;
+        };
+        auto issued = [&](uint32_t bar) {  // a job has just been committed
+            if (n_pend == kLag) publish_oldest(std::integral_constant<int, kLag>());
+            pend_bar[n_pend++] = bar;
+        };
+        // 4 blocks x 64 keys x 128 bytes from column block `first_block` of the rows [key0, key0 + 64) of this key range
+        auto issue_rows = [&](uint8_t *slot, int key0, int first_block) {
+            const int rows = max(0, min(kHalf, k_end - key0));
+            const size_t tok0 = rows > 0 ? kv_tile_row(p, b, seq_begin, key0) : 0;
+#pragma unroll
+            for (int n = 0; n < 4 * kHalf * 8 / kLoaderThreads; ++n) {
+                const int e = lt + n * kLoaderThreads;
+                const int j = e >> 9, r = (e >> 3) & 63, cc = e & 7;
+                const T *src = k_g + (tok0 + max(0, min(r, rows - 1))) * p.k_row_stride + (first_block + j) * 64 + cc * 8;
+                DA_MLA2_CPASYNC(slot + j * kBlockBytes + r * 128 + ((cc ^ (r & 7)) << 4), src, r < rows ? 16u : 0u);  // 0: zero fill
+            }
+            cp_async_commit();
+        };
+        auto load_s4 = [&](int t) {  // K blocks kTmaBlocks..8 of this CTA's 64 keys of tile t
+            if (kLsuBlocks == 0) return;
+            if (t >= 1) ok = mbar_wait(s4_empty, (uint32_t)(t - 1) & 1u, abort_flag);
+            if (!ok) return;
+            issue_rows(s4_s, k_begin + t * kTile + (int)rank * kHalf, kTmaBlocks);
+            issued(lead(s4_full));
+        };
+        auto load_v = [&](int i) {  // this CTA's 256 dims of the 64 keys of half-tile i
+            const int vs = i % kVSlots;
+            if (i >= kVSlots) ok = mbar_wait(&v_empty[vs], ((uint32_t)(i / kVSlots) & 1u) ^ 1u, abort_flag);
+            if (ok && i == kVSlots - 1) ok = mbar_wait(q_copied, 0, abort_flag);  // the slot staged Q blocks until now
+            if (!ok) return;
+            issue_rows(v_s + vs * kVSlotBytes, k_begin + (i >> 1) * kTile + (i & 1) * kHalf, (int)rank * kVBlocks);
+            issued(lead(&v_full[vs]));
+        };
+        // Order: what the tensor pipe needs first comes first, and no job's wait for its slot depends on one of the
+        // kLag jobs before it (those are still unpublished): S4(0) V(0)a S4(1) V(0)b S4(2) | V(t)a V(t)b S4(t+2) ...
+        load_s4(0);
+        if (ok) load_v(0);
+        if (ok && n_tiles > 1) load_s4(1);
+        if (ok) load_v(1);
+        if (ok && n_tiles > 2) load_s4(2);
+        for (int t = 1; t < n_tiles && ok; ++t) {
+            load_v(2 * t);
+            if (ok) load_v(2 * t + 1);
+            if (ok && t + 2 < n_tiles) load_s4(t + 2);
+        }
+        if (ok) {
+            if (kLag >= 2 && n_pend == 2) publish_oldest(std::integral_constant<int, 1>());
+            if (n_pend == 1) publish_oldest(std::integral_constant<int, 0>());
+        }
+        cp_async_wait<0>();
+    } else {
+        // ---------------- softmax / epilogue: thread l <-> TMEM lane l <-> (head l & 63, key half l >> 6) ----------------
+        const int r = tid & 63, kh = tid >> 6;
+        const int head = head0 + r;
+        const bool valid = head < p.head_q;  // rows past head_q are padding
+        const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+        const float slope2 = p.is_alibi ? exp2f(-8.0f * (float)(head + 1) / (float)p.head_q) * kLog2e : 0.0f;
+        const int pos_shift = (p.kv_pos_offset ? p.kv_pos_offset[b] : 0) - ((p.kv_total_len ? p.kv_total_len[b] : len) - 1);
+        float m_ref = -INFINITY, l = 0.0f;
+        uint32_t buf[32];
+        {
+            // Q blocks 0..3 go to TMEM as packed 16-bit pairs, head r in lane r AND lane r + 64: a pair MMA reads an
+            // A operand that lives in TMEM lane by lane, lanes 64-127 for the second half of the N columns.  The
+            // blocks arrive by TMA in the last V slot (which the loaders leave alone until q_copied completes) and
+            // each thread moves its own row: 16-byte loads of one row per lane straight from global memory would
+            // cost one L1 wavefront per lane and instruction, about four thousand cycles per CTA.
+            const uint8_t *q_stage = v_s + (kVSlots - 1) * kVSlotBytes;
+            const bool have_q = head0 < p.head_q;
+            if (have_q) ok = __all_sync(0xffffffffu, mbar_wait(q_stage_full, 0, abort_flag)) != 0;
+#pragma unroll
+            for (int j = 0; j < kQTmemBlocks; ++j) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint4 v = (valid && ok) ? *reinterpret_cast<const uint4 *>(q_stage + j * kBlockBytes + r * 128 + ((i ^ (r & 7)) << 4))
+                                                  : make_uint4(0, 0, 0, 0);
+                    buf[4 * i] = v.x, buf[4 * i + 1] = v.y, buf[4 * i + 2] = v.z, buf[4 * i + 3] = v.w;
+                }
+                tmem_st32(lane_base + kColQ + j * 32, buf);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(q_copied);
+                if (ok) mbar_arrive_remote_cta(lead(q_tmem));
+            }
+        }
+        // `ok` is kept warp-uniform, and a warp that has given up still walks the loop so that the named
+        // barriers below always see all 128 threads.
+        auto wait_all = [&](uint64_t *bar, uint32_t parity) {
+            return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag)) != 0;
+        };
+        for (int t = 0; t < n_tiles; ++t) {
+            const int key0 = k_begin + t * kTile + kh * kHalf;  // first key of this thread's 64 columns
+            const int rows = k_end - key0;                       // columns >= rows are past the end
+            const uint32_t s_addr = lane_base + kColS + (t & 1) * 64;
+            if (ok) ok = wait_all(&s_full[t & 1], (uint32_t)(t / 2) & 1u);
+            float s[kHalf];
+            float mx = -INFINITY;
+            if (ok) {
+                tc_fence_after();
+                uint32_t buf2[32];
+                tmem_ld32(s_addr, buf);       // both halves of the row are requested before the wait:
+                tmem_ld32(s_addr + 32, buf2);  // a TMEM load takes a few hundred cycles to return
+                tmem_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const float x0 = __uint_as_float(buf[j]) * p.scale_log2 + slope2 * (float)(key0 + j + pos_shift);
+                    const float x1 = __uint_as_float(buf2[j]) * p.scale_log2 + slope2 * (float)(key0 + 32 + j + pos_shift);
+                    s[j] = (j < rows) ? (valid ? x0 : 0.0f) : -INFINITY;
+                    s[32 + j] = (32 + j < rows) ? (valid ? x1 : 0.0f) : -INFINITY;
+                    mx = fmaxf(mx, fmaxf(s[j], s[32 + j]));
+                }
+            }
+            // one reference per head: the two threads of a head swap their maxima
+            x_max[(t & 1) * 128 + tid] = mx;
+            named_bar_sync(1, 128);
+            if (!ok) continue;
+            mx = fmaxf(mx, x_max[(t & 1) * 128 + (tid ^ 64)]);
+            const bool raise = mx > m_ref + kRescaleThreshold;
+            float alpha = 1.0f;
+            if (raise) {
+                alpha = exp2f(m_ref - mx);  // 0 on the first tile
+                m_ref = mx;
+                l *= alpha;
+            }
+            if (t >= 1 && __any_sync(0xffffffffu, raise)) {
+                // Rare: the reference max of some row in this warp moved.  O must be idle (P.V of tile
+                // t-1 complete) while its rows are rescaled in place.
+                ok = wait_all(&pv_done[(t - 1) & 1], (uint32_t)((t - 1) / 2) & 1u);
+                if (!ok) continue;
+                tc_fence_after();
+#pragma unroll 1
+                for (int c = 0; c < 256 / 32; ++c) {
+                    tmem_ld32(lane_base + kColO + c * 32, buf);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) buf[j] = __float_as_uint(__uint_as_float(buf[j]) * alpha);
+                    tmem_st32(lane_base + kColO + c * 32, buf);
+                }
+                tmem_wait_st();
+            } else if (kPBufs == 1 && t >= 1) {
+                // the single P buffer is still being read by P.V of tile t-1
+                ok = wait_all(&pv_done[(t - 1) & 1], (uint32_t)((t - 1) / 2) & 1u);
+                if (!ok) continue;
+            }
+            // P = exp2(S - m_ref), rounded to the input type: row r, keys kh*64.. of the tile, K-major swizzled
+            uint8_t *p_row = p_s + (t % kPBufs) * kPBytes + kh * kBlockBytes + r * 128;
+            float sum = 0.0f;
+#pragma unroll
+            for (int cc = 0; cc < 8; ++cc) {
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float p0 = exp2f(s[cc * 8 + 2 * j] - m_ref), p1 = exp2f(s[cc * 8 + 2 * j + 1] - m_ref);
+                    sum += p0 + p1;
+                    if (std::is_same<T, __nv_bfloat16>::value) {
+                        __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+                        w[j] = *reinterpret_cast<uint32_t *>(&hh);
+                    } else {
+                        __half2 hh = __floats2half2_rn(p0, p1);
+                        w[j] = *reinterpret_cast<uint32_t *>(&hh);
+                    }
+                }
+                *reinterpret_cast<uint4 *>(p_row + ((cc ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            l += sum;
+            fence_proxy_async();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_remote_cta(lead(&p_full[t & 1]));
+        }
+        if (ok) ok = wait_all(&pv_done[(n_tiles - 1) & 1], (uint32_t)((n_tiles - 1) / 2) & 1u);
+        x_sum[tid] = l;
+        named_bar_sync(1, 128);
+        if (ok) {
+            tc_fence_after();
+            l += x_sum[tid ^ 64];
+            const float inv = 1.0f / l;
+            const float lse = (m_ref + log2f(l)) * kLn2;
+            const size_t row = ((size_t)b * p.head_q + head) * p.num_splits + split;
+            // This thread's 256 output values are staged in shared memory (the rings are idle now: every MMA
+            // of the pair has finished) and leave as one bulk copy per destination, so the writes reach
+            // memory as whole lines whatever the row pitch.  Regions are 16 bytes longer than their data:
+            // the float4 / uint4 stores of a quarter warp then fall into different banks.
+            uint8_t *stage = smem + kOffA;
+            const int d_first = kh * 256;
+            auto stage_f32 = [&](float *dst_g) {
+                float *mine = reinterpret_cast<float *>(stage + (size_t)tid * (256 * 4 + 16));
+                uint32_t buf2[32];
+#pragma unroll 1
+                for (int c = 0; c < 256 / 32; c += 2) {
+                    tmem_ld32(lane_base + kColO + c * 32, buf);
+                    tmem_ld32(lane_base + kColO + c * 32 + 32, buf2);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        reinterpret_cast<float4 *>(mine + c * 32)[j] =
+                            make_float4(__uint_as_float(buf[4 * j]) * inv, __uint_as_float(buf[4 * j + 1]) * inv,
+                                        __uint_as_float(buf[4 * j + 2]) * inv, __uint_as_float(buf[4 * j + 3]) * inv);
+                        reinterpret_cast<float4 *>(mine + c * 32 + 32)[j] =
+                            make_float4(__uint_as_float(buf2[4 * j]) * inv, __uint_as_float(buf2[4 * j + 1]) * inv,
+                                        __uint_as_float(buf2[4 * j + 2]) * inv, __uint_as_float(buf2[4 * j + 3]) * inv);
+                    }
+                }
+                fence_proxy_async();
+                if (valid) bulk_store_s2g(dst_g, mine, 256 * 4);
+                bulk_store_commit();
+            };
+            auto stage_t = [&](T *dst_g) {
+                uint8_t *mine = stage + (size_t)tid * (256 * 2 + 16);
+                uint32_t buf2[32];
+#pragma unroll 1
+                for (int c = 0; c < 256 / 32; c += 2) {
+                    tmem_ld32(lane_base + kColO + c * 32, buf);
+                    tmem_ld32(lane_base + kColO + c * 32 + 32, buf2);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        alignas(16) T tmp[8], tmp2[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            tmp[e] = from_float<T>(__uint_as_float(buf[8 * j + e]) * inv);
+                            tmp2[e] = from_float<T>(__uint_as_float(buf2[8 * j + e]) * inv);
+                        }
+                        reinterpret_cast<uint4 *>(mine + c * 64)[j] = *reinterpret_cast<uint4 *>(tmp);
+                        reinterpret_cast<uint4 *>(mine + c * 64 + 64)[j] = *reinterpret_cast<uint4 *>(tmp2);
+                    }
+                }
+                fence_proxy_async();
+                if (valid) bulk_store_s2g(dst_g, mine, 256 * 2);
+                bulk_store_commit();
+            };
+            if (p.num_splits > 1) {
+                stage_f32(p.part_o + row * kDimV + d_first);
+            } else {
+                if (p.o_f32) {
+                    stage_f32(p.o_f32 + ((size_t)b * p.head_q + head) * kDimV + d_first);
+                    if (o_out) bulk_store_wait_read();  // the staging bytes are about to be reused
+                }
+                if (o_out) stage_t(o_out + (size_t)b * p.o_row_stride + (size_t)head * kDimV + d_first);
+            }
+            bulk_store_wait_read();
+            if (kh == 0 && valid) {
+                if (p.num_splits > 1) {
+                    p.part_lse[row] = lse;
+                } else if (p.lse) {
+                    p.lse[(size_t)b * p.head_q + head] = lse;
+                }
+            }
+            tc_fence_before();
+        }
+    }
+
+    if (!ok && lane == 0) report_timeout(p);
+    __syncthreads();
+    if (*abort_flag) {
+        // give copies that may still be in flight a bounded time to land before the CTA retires
+        const long long t0 = clock64();
+        while (clock64() - t0 < 200000) {
+        }
+    }
+    tc_fence_before();
+    cluster_sync_all();  // the peer may still read this CTA's shared memory (pair MMAs) or arrive on its barriers
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+}  // namespace
+
+
+SplitVariantInfo split_info_mla_2sm() { return {kTile, kHeads, 1}; }
+
+// tm_q: rank-3 map over q [batch][head_q][576], box {64, min(64, head_q), 1}; tm_k: rank-2 map over the latent
+// cache [rows][576], box {64, 64 keys}; both with the 128-byte swizzle.  Grid (2, splits, batch) in clusters of
+// two along x: the two CTAs of a key range.
+cudaError_t launch_mla_2sm(bool bf16, const SplitParams &p, const CUtensorMap &tm_q, const CUtensorMap &tm_k,
+                           cudaStream_t stream) {
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    if (dev < 64 && !attr_set[dev]) {
+        err = cudaFuncSetAttribute(da_mla_2sm_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (err != cudaSuccess) return err;
+        err = cudaFuncSetAttribute(da_mla_2sm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (err != cudaSuccess) return err;
+        attr_set[dev] = true;
+    }
+    dim3 grid(2, p.num_splits, p.batch);
+    const bool overlap = p.batch_order != nullptr;
+    return bf16 ? launch_kernel(da_mla_2sm_kernel<__nv_bfloat16>, grid, kThreads, kSmemBytes, stream, overlap, p, tm_q, tm_k)
+                : launch_kernel(da_mla_2sm_kernel<__half>, grid, kThreads, kSmemBytes, stream, overlap, p, tm_q, tm_k);
+}
+
+}  // namespace da

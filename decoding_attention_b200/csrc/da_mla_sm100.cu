@@ -78,21 +78,6 @@ constexpr float kRescaleThreshold = 8.0f;
 __device__ __forceinline__ int a_block(int h, int j) { return j < 4 ? (h ? j : 4 + j) : 8; }
 __device__ __forceinline__ int v_block(int h, int j) { return 4 * h + j; }
 
-#ifdef DA_MLA_PROFILE
-// Development aid (not compiled into the shipped library): cycles the warps of CTA (0,0,0) spend in
-// each wait, accumulated in registers and written out once per role.
-__device__ long long g_mla_prof[64];
-#define PROF_DECL long long prof_t0 = 0, prof_a0 = 0, prof_a1 = 0, prof_a2 = 0, prof_a3 = 0; (void)prof_t0, (void)prof_a0, (void)prof_a1, (void)prof_a2, (void)prof_a3
-#define PROF_BEGIN() prof_t0 = clock64()
-#define PROF_END(i) prof_a##i += clock64() - prof_t0
-#define PROF_FLUSH(base) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0) { \
-    g_mla_prof[(base)] += prof_a0; g_mla_prof[(base) + 1] += prof_a1; g_mla_prof[(base) + 2] += prof_a2; g_mla_prof[(base) + 3] += prof_a3; } } while (0)
-#else
-#define PROF_DECL
-#define PROF_BEGIN()
-#define PROF_END(i)
-#define PROF_FLUSH(base)
-#endif
 
 // One [64 keys x 64 dims] block of the latent cache into a 128-byte-swizzled 8 KB slot.  Whole
 // tiles go by TMA (lane 0 issues; the bytes are counted on `bar`, whose expect_tx the caller has
@@ -132,9 +117,9 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
     const int seq_begin = p.cu_seq_k[b];
     const int len = p.cu_seq_k[b + 1] - seq_begin;
     const int k_begin = split * p.chunk_keys;
-    const int k_end = min(len, k_begin + p.chunk_keys);
+    const int k_end = split_key_end(p, split, len);
     T *o_out = reinterpret_cast<T *>(p.o);
-    if (*reinterpret_cast<volatile int *>(p.status) != kStatusOk) return;  // an earlier CTA timed out: do not pile up
+    if (launch_aborted(p)) return;  // an earlier CTA of this launch timed out: do not pile up
 
     if (k_begin >= k_end) {
         if (p.num_splits == 1) {  // empty sequence: zero row, LSE = -inf
@@ -213,7 +198,6 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
         const int run = kShortPages ? kv_run_keys(p, kTile) : kTile;
         int a_slot = 0;
         uint32_t a_round = 0;  // how many times the streamed ring has wrapped
-        PROF_DECL;
         for (int t = 0; t < n_tiles && ok; ++t) {
             const int key0 = k_begin + t * kTile;
             const int rows = min(kTile, k_end - key0);
@@ -223,9 +207,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             const bool whole = rows == kTile;
             // the five streamed blocks, each into the next slot of the ring (the V blocks come from the loader warps)
             for (int j = 0; j < kABlocks && ok; ++j) {
-                PROF_BEGIN();
                 if (a_round > 0) ok = mbar_wait(&a_empty[a_slot], (a_round & 1u) ^ 1u, abort_flag);
-                PROF_END(1);
                 if (!ok) break;
                 if (whole && lane == 0) mbar_arrive_expect_tx(&a_full[a_slot], kKBlockBytes);
                 load_block<T>(a_s + a_slot * kKBlockBytes, &tm_k, k_g, p.k_row_stride, a_block(half, j), row_of, run, rows,
@@ -242,7 +224,6 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             }
             __syncwarp();
         }
-        PROF_FLUSH(0);
     } else if (warp == 5) {
         // ---------------- MMA issuer ----------------
         {
@@ -258,14 +239,11 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             const uint32_t q_tmem_addr = tmem_base + kColQ;
             int a_slot = 0;
             uint32_t a_round = 0;
-            PROF_DECL;
             auto issue_qk = [&](int t) -> bool {
                 const uint32_t d = tmem_base + kColS + (t & 1) * kTile;
 #pragma unroll
                 for (int j = 0; j < kABlocks; ++j) {
-                    PROF_BEGIN();
                     if (!mbar_wait(&a_full[a_slot], a_round & 1u, abort_flag)) return false;
-                    PROF_END(1);
                     tc_fence_after();
                     const uint64_t bd = a_desc0 + (uint64_t)((a_slot * kKBlockBytes) >> 4);
 #pragma unroll
@@ -282,9 +260,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                         ++a_round;
                     }
                 }
-                PROF_BEGIN();
                 if (!mbar_wait(&v_full[t % kVSlots], (uint32_t)(t / kVSlots) & 1u, abort_flag)) return false;
-                PROF_END(2);
                 tc_fence_after();
                 const uint64_t vd = vk_desc0 + (uint64_t)(((t % kVSlots) * kVSlotBytes) >> 4);
 #pragma unroll
@@ -298,10 +274,8 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                 umma_commit(&s_full[t & 1], leader);
                 return true;
             };
-            PROF_BEGIN();
             ok = mbar_wait(q_full, 0, abort_flag);
             if (ok) ok = mbar_wait(q_tmem, 0, abort_flag);
-            PROF_END(0);
             if (ok) {
                 tc_fence_after();
                 ok = issue_qk(0);
@@ -311,9 +285,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                     ok = issue_qk(t + 1);
                     if (!ok) break;
                 }
-                PROF_BEGIN();
                 ok = mbar_wait(&p_full[t & 1], (uint32_t)(t / 2) & 1u, abort_flag);
-                PROF_END(3);
                 if (!ok) break;
                 tc_fence_after();
                 const int vs = t % kVSlots;
@@ -329,7 +301,6 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                 umma_commit(&v_empty[vs], leader);
                 umma_commit(&pv_done[t & 1], leader);
             }
-            PROF_FLUSH(8);
         }
         __syncwarp();
     } else if (warp >= 6) {
@@ -342,15 +313,12 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
         const int lt = tid - 6 * 32;  // 0..127
         const T *k_g = reinterpret_cast<const T *>(p.k);
         const int run = kShortPages ? kv_run_keys(p, kTile) : kTile;
-        PROF_DECL;
         for (int t = 0; t < n_tiles && ok; ++t) {
             const int key0 = k_begin + t * kTile;
             const int rows = min(kTile, k_end - key0);
             const size_t tok0 = kv_tile_row(p, b, seq_begin, key0);
             const int vs = t % kVSlots;
-            PROF_BEGIN();
             if (t >= kVSlots) ok = mbar_wait(&v_empty[vs], ((uint32_t)(t / kVSlots) & 1u) ^ 1u, abort_flag);
-            PROF_END(0);
             if (!ok) break;
             uint8_t *slot = v_s + vs * kVSlotBytes;
             if (!kShortPages) {  // the tile's rows are consecutive in the cache
@@ -377,18 +345,15 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                 }
             }
             cp_async_commit();
-            PROF_BEGIN();
             if (t >= 1) {  // the tile issued one iteration ago has landed: publish it to the tensor pipe
                 cp_async_wait<1>();
                 fence_proxy_async();
                 mbar_arrive(&v_full[(t - 1) % kVSlots]);
             }
-            PROF_END(1);
         }
         cp_async_wait<0>();
         fence_proxy_async();
         if (ok) mbar_arrive(&v_full[(n_tiles - 1) % kVSlots]);
-        if (warp == 6) PROF_FLUSH(4);
     } else {
         // ---------------- softmax / epilogue: thread r <-> TMEM lane r <-> head r ----------------
         const int r = tid;
@@ -398,9 +363,6 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
         const int pos_shift = (p.kv_pos_offset ? p.kv_pos_offset[b] : 0) - ((p.kv_total_len ? p.kv_total_len[b] : len) - 1);
         float m_ref = -INFINITY, l = 0.0f;
         uint32_t buf[32];
-        PROF_DECL;
-        const long long prof_start = clock64();
-        (void)prof_start;
         {
             // The Q columns that meet the first four streamed blocks go to TMEM as packed 16-bit pairs.
             const T *q_row = reinterpret_cast<const T *>(p.q) + (size_t)b * p.q_row_stride + (size_t)r * kDim;
@@ -422,15 +384,9 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             const int key0 = k_begin + t * kTile;
             const int rows = min(kTile, k_end - key0);
             const uint32_t s_addr = lane_base + kColS + (t & 1) * kTile;
-            PROF_BEGIN();
             ok = mbar_wait(&s_full[t & 1], (uint32_t)(t / 2) & 1u, abort_flag);
-            PROF_END(0);
-#ifdef DA_MLA_PROFILE
-            if (t == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0) g_mla_prof[34] += clock64() - prof_start;
-#endif
             if (!ok) break;
             tc_fence_after();
-            PROF_BEGIN();
             float s[kTile];
             float mx = -INFINITY;
 #pragma unroll
@@ -451,8 +407,6 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                 m_ref = mx;
                 l *= alpha;
             }
-            PROF_END(1);
-            PROF_BEGIN();
             if (t >= 1 && __any_sync(0xffffffffu, raise)) {
                 // Rare: the reference max of some row in this warp moved.  O must be idle (P.V of tile
                 // t-1 complete) while its rows are rescaled in place.
@@ -469,8 +423,6 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                 }
                 tmem_wait_st();
             }
-            PROF_END(2);
-            PROF_BEGIN();
             // P = exp2(S - m_ref), rounded to the input type, packed in pairs over the first half of S(t).
             // (The tile that used these columns before, t-2, is past its P.V: S(t) was issued after it.)
             float sum = 0.0f;
@@ -491,15 +443,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&p_full[t & 1]);
-            PROF_END(3);
         }
-#ifdef DA_MLA_PROFILE
-        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0) {
-            g_mla_prof[32] += clock64() - prof_start;
-            g_mla_prof[33] += n_tiles;
-        }
-        PROF_FLUSH(16 + 4 * warp);
-#endif
         if (ok) ok = mbar_wait(&pv_done[(n_tiles - 1) & 1], (uint32_t)((n_tiles - 1) / 2) & 1u, abort_flag);
         if (ok) {
             tc_fence_after();
@@ -548,7 +492,7 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
         }
     }
 
-    if (!ok && lane == 0) atomicExch(p.status, kStatusWaitTimeout);
+    if (!ok && lane == 0) report_timeout(p);
     __syncthreads();
     if (warp == 5) {
         tc_fence_after();
@@ -558,16 +502,6 @@ da_mla_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
 
 }  // namespace
 
-#ifdef DA_MLA_PROFILE
-extern "C" void da_debug_mla_prof(long long *out, int reset) {
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out, g_mla_prof, sizeof(long long) * 64);
-    if (reset) {
-        long long z[64] = {};
-        cudaMemcpyToSymbol(g_mla_prof, z, sizeof(z));
-    }
-}
-#endif
 
 SplitVariantInfo split_info_mla_tc() { return {kTile, kHeads, 1}; }
 

@@ -166,7 +166,7 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
     const int seq_begin = p.cu_seq_k[b];
     const int len = p.cu_seq_k[b + 1] - seq_begin;
     const int k_begin = split * p.chunk_keys;
-    const int k_end = min(len, k_begin + p.chunk_keys);
+    const int k_end = split_key_end(p, split, len);
     const float neg_inf = -INFINITY;
 
     if (k_begin >= k_end) {
@@ -268,7 +268,7 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
         if (!ok) {
             // A wait ran out.  Report it, then give the copies that are still in flight a bounded time
             // to land before this warp (the last user of the stage buffers) retires.
-            if (lane == 0) atomicExch(p.status, kStatusWaitTimeout);
+            if (lane == 0) report_timeout(p);
             for (int back = 1; back <= STAGES; ++back) {
                 const int tk = armed_k - back, tv = armed_v - back;
                 for (uint32_t spin = 0; tk >= 0 && spin < (1u << 20); ++spin)
@@ -440,7 +440,7 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
         __syncwarp();
         if (lane == 0) mbar_arrive(C::MLA ? &empty_k[st] : &empty_v[st]);
     }
-    if (!ok && lane == 0) atomicExch(p.status, kStatusWaitTimeout);
+    if (!ok && lane == 0) report_timeout(p);
 
     // ---------------- merge the groups of the CTA ----------------
     // Every consumer has passed its last full-barrier wait, so every copy has landed and the stage

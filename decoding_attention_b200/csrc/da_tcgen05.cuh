@@ -123,6 +123,63 @@ __host__ __device__ constexpr uint32_t instr_desc(uint32_t ab_fmt, uint32_t b_mn
     return (1u << 4) | (ab_fmt << 7) | (ab_fmt << 10) | (b_mn_major << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
+// ---- cta_group::2: one MMA over the two CTAs (SMs) of a cluster pair ---------------------------
+// The pair's M rows are split in halves (CTA rank c holds rows c*M/2 ..), each CTA stages its own A
+// rows and its own half of B's N columns at the SAME shared-memory offsets, and the instruction is
+// issued by one thread of the rank-0 CTA.  Accumulators (M = 128): a CTA's 64 rows x N columns sit
+// in its TMEM as lane l < 64 -> row l, columns 0..N/2-1 and lane l >= 64 -> row l-64, columns
+// N/2..N-1 (measured on B200); an A operand in TMEM is read lane by lane the same way: row r must be
+// present in lane r (for the first half of the N columns) and in lane r + 64 (for the second half).
+__device__ __forceinline__ void umma2_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate, uint32_t leader) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.ne.b32 q, %5, 0;\n\t"
+        "@q tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        :
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(leader));
+}
+__device__ __forceinline__ void umma2_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate, uint32_t leader) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.ne.b32 q, %5, 0;\n\t"
+        "@q tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        :
+        : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(leader));
+}
+// One arrival on the mbarrier at this shared-memory offset in BOTH CTAs of the pair once every
+// cta_group::2 MMA issued so far by this thread has finished.
+__device__ __forceinline__ void umma2_commit_both(uint64_t *bar, uint32_t leader) {
+    asm volatile(
+        "{\n\t.reg .pred q;\n\t"
+        "setp.ne.b32 q, %1, 0;\n\t"
+        "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %2;\n\t}" ::"r"(
+            smem_u32(bar)),
+        "r"(leader), "h"((uint16_t)3)
+        : "memory");
+}
+// Tiled TMA loads into this CTA's shared memory whose byte count is signalled on an mbarrier that may
+// live in the peer CTA of the pair (`bar_cluster_addr`: a shared::cluster address, see map_to_cta).
+__device__ __forceinline__ void tma2_load_2d(void *dst, const CUtensorMap *tm, int c0, int c1, uint32_t bar_cluster_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
+            "r"(smem_u32(dst)),
+        "l"(tm), "r"(c0), "r"(c1), "r"(bar_cluster_addr)
+        : "memory");
+}
+__device__ __forceinline__ void tma2_load_3d(void *dst, const CUtensorMap *tm, int c0, int c1, int c2,
+                                             uint32_t bar_cluster_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], "
+        "[%5];" ::"r"(smem_u32(dst)),
+        "l"(tm), "r"(c0), "r"(c1), "r"(c2), "r"(bar_cluster_addr)
+        : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
 // ---- thread-block-cluster helpers (distributed shared memory between the two CTAs of a pair) ----
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -143,12 +200,27 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, float a, fl
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_bar_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar_addr) : "memory");
 }
+// The same with the default (CTA-scope) release: enough when what the arrival announces is data in THIS
+// CTA's shared or tensor memory that this CTA's own tensor core will read on behalf of a pair MMA (the
+// writer has already run fence.proxy.async / tcgen05.fence).  A cluster-scope release costs the arriving
+// thread a few thousand cycles, this one does not.
+__device__ __forceinline__ void mbar_arrive_remote_cta(uint32_t cluster_bar_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar_addr) : "memory");
+}
 // one arrival plus `bytes` of expected transfer on an mbarrier of another CTA
 __device__ __forceinline__ void mbar_arrive_expect_tx_remote(uint32_t cluster_bar_addr, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_bar_addr),
                  "r"(bytes)
                  : "memory");
 }
+// Adds `bytes` of completed transfer to an mbarrier of another CTA (the counterpart of a TMA copy's
+// complete_tx, for data this CTA wrote with ordinary stores).  Relaxed: order the stores before it
+// with fence_acq_rel_cluster().
+__device__ __forceinline__ void mbar_complete_tx_remote(uint32_t cluster_bar_addr, uint32_t bytes) {
+    asm volatile("mbarrier.complete_tx.relaxed.cluster.shared::cluster.b64 [%0], %1;" ::"r"(cluster_bar_addr), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void fence_acq_rel_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
 // bulk copy from this CTA's shared memory into another CTA's, bytes counted on an mbarrier over there
 __device__ __forceinline__ void bulk_copy_s2peer(uint32_t dst_cluster_addr, const void *src_smem, uint32_t bytes,
                                                  uint32_t cluster_bar_addr) {

@@ -35,6 +35,7 @@ struct XMergeParams {
     long long slot_floats;   // floats per (parity, rank) slot = record size rounded up to 4
     int dim_v, world, rank, is_bf16;
     unsigned epoch;
+    long long max_wait_cycles;  // bound of the flag poll, in SM clocks
 };
 
 // buffer layout (floats): [2 parities][world][slot_floats] records, then [2][world][kMaxCtas] flags (uint32)
@@ -88,7 +89,7 @@ __global__ void __launch_bounds__(kThreads) da_xmerge_kernel(const XMergeParams 
                 got = true;
                 break;
             }
-            if (clock64() - t0 > kMaxWaitCycles) break;
+            if (clock64() - t0 > p.max_wait_cycles) break;
         }
         if (!got) {
             s_ok = 0;
@@ -148,7 +149,14 @@ extern "C" size_t da_exchange_buffer_bytes(int32_t world, int64_t rows, int32_t 
 
 extern "C" int da_exchange_merge(const float *rec, void *const *peer_bufs, int32_t world, int32_t rank, int64_t rows,
                                  int32_t dim_v, uint32_t epoch, void *o, float *lse, int32_t is_bf16, void *stream) {
+    return da_exchange_merge_bounded(rec, peer_bufs, world, rank, rows, dim_v, epoch, o, lse, is_bf16, stream, 0);
+}
+
+extern "C" int da_exchange_merge_bounded(const float *rec, void *const *peer_bufs, int32_t world, int32_t rank,
+                                         int64_t rows, int32_t dim_v, uint32_t epoch, void *o, float *lse,
+                                         int32_t is_bf16, void *stream, int64_t max_wait_cycles) {
     using namespace da;
+    if (max_wait_cycles < 0) return report_error(DA_ERR_INVALID_ARG, "max_wait_cycles must not be negative");
     if (!rec || !peer_bufs || !o) return report_error(DA_ERR_INVALID_ARG, "rec, peer_bufs and o must not be NULL");
     if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world) {
         return report_error(DA_ERR_INVALID_ARG, "world must be 1..16 and rank inside it");
@@ -177,6 +185,7 @@ extern "C" int da_exchange_merge(const float *rec, void *const *peer_bufs, int32
     p.rank = rank;
     p.is_bf16 = is_bf16;
     p.epoch = epoch;
+    p.max_wait_cycles = max_wait_cycles > 0 ? max_wait_cycles : kMaxWaitCycles;
     const unsigned ctas = (unsigned)((rows + kRowsPerCta - 1) / kRowsPerCta);
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     // Launched for overlap with the preceding kernel of the stream (it waits for that kernel's results itself).

@@ -4,7 +4,7 @@
 //   fwd(q, k, v_, o_, cu_seq_k, max_seq_k, dim_v, is_alibi) -> o      same positional signature and
 //       checks as the reference's dmha_fwd (decoding_torch.cpp:19-80); v_ = None selects MLA.
 //   dmha_fwd(q, k, v, cu_seq_k, max_seq_k, is_alibi, softmax_scale=None, out=None, return_lse=False)
-//   dmla_fwd(q, kv, cu_seq_k, max_seq_k, dim_v=512, softmax_scale=None, out=None, return_lse=False)
+//   dmla_fwd(q, kv, cu_seq_k, max_seq_k, dim_v=512, is_alibi=False, softmax_scale=None, out=None, return_lse=False)
 //       the two named entry points with an explicit softmax scale; their defaults reproduce fwd().
 //   merge_partials(part_o, part_lse, out_dtype) -> (o, lse)           LSE merge of key-range shards.
 //
@@ -135,6 +135,16 @@ Outputs run(const at::Tensor &q, const at::Tensor &k, const std::optional<at::Te
         a.page_size = (int32_t)page_size;
     }
 
+    // Split partials come from torch's caching allocator, which is ordered on the current stream: calls
+    // on different streams of one device never share scratch, and nothing is allocated from the driver
+    // once the allocator has warmed up (so the call can be captured in a CUDA graph).
+    at::Tensor workspace;
+    const size_t ws_bytes = da_decode_workspace_bytes(&a);
+    if (ws_bytes > 0) {
+        workspace = torch::empty({(int64_t)ws_bytes}, q.options().dtype(torch::kUInt8));
+        a.workspace = workspace.data_ptr();
+        a.workspace_bytes = ws_bytes;
+    }
     const int rc = da_decode_fwd(&a);
     TORCH_CHECK(rc == DA_OK, "decoding_attn: ", da_status_string(rc), ": ", da_last_error());
     return out;
@@ -156,9 +166,10 @@ pybind11::object dmha_fwd(const at::Tensor &q, const at::Tensor &k, const at::Te
 }
 
 pybind11::object dmla_fwd(const at::Tensor &q, const at::Tensor &kv, const at::Tensor &cu_seq_k, int64_t max_seq_k,
-                          int64_t dim_v, std::optional<double> softmax_scale, std::optional<at::Tensor> out,
-                          bool return_lse) {
-    Outputs r = run(q, kv, std::nullopt, out, cu_seq_k, max_seq_k, dim_v, false, softmax_scale, return_lse);
+                          int64_t dim_v, bool is_alibi, std::optional<double> softmax_scale,
+                          std::optional<at::Tensor> out, bool return_lse) {
+    // The reference's fwd() keeps is_alibi when v_ is None (csrc/torch/decoding_torch.cpp:19-21, :76-77).
+    Outputs r = run(q, kv, std::nullopt, out, cu_seq_k, max_seq_k, dim_v, is_alibi, softmax_scale, return_lse);
     if (return_lse) return pybind11::cast(std::make_tuple(r.o, r.lse));
     return pybind11::cast(r.o);
 }
@@ -225,8 +236,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("max_seq_k"), py::arg("is_alibi") = false, py::arg("softmax_scale") = py::none(),
           py::arg("out") = py::none(), py::arg("return_lse") = false);
     m.def("dmla_fwd", &dmla_fwd, "MLA decode (latent KV)", py::arg("q"), py::arg("kv"), py::arg("cu_seq_k"),
-          py::arg("max_seq_k"), py::arg("dim_v") = 512, py::arg("softmax_scale") = py::none(),
-          py::arg("out") = py::none(), py::arg("return_lse") = false);
+          py::arg("max_seq_k"), py::arg("dim_v") = 512, py::arg("is_alibi") = false,
+          py::arg("softmax_scale") = py::none(), py::arg("out") = py::none(), py::arg("return_lse") = false);
     m.def("paged_fwd", &paged_fwd, "Decode over a paged KV cache", py::arg("q"), py::arg("k_cache"), py::arg("v_cache"),
           py::arg("cu_seq_k"), py::arg("block_table"), py::arg("max_seq_k"), py::arg("dim_v"), py::arg("is_alibi") = false,
           py::arg("softmax_scale") = py::none(), py::arg("out") = py::none(), py::arg("return_lse") = false);

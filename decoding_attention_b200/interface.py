@@ -33,7 +33,7 @@ def decoding_attn_fwd(q, k, v, cu_seq_k, max_seq_k, dim_v, is_alibi, *, softmax_
     if softmax_scale is None:
         return decoding_attn_cuda.fwd(q, k, v, None, cu_seq_k, max_seq_k, dim_v, is_alibi)
     if v is None:
-        return decoding_attn_cuda.dmla_fwd(q, k, cu_seq_k, max_seq_k, dim_v, softmax_scale)
+        return decoding_attn_cuda.dmla_fwd(q, k, cu_seq_k, max_seq_k, dim_v, is_alibi, softmax_scale)
     return decoding_attn_cuda.dmha_fwd(q, k, v, cu_seq_k, max_seq_k, is_alibi, softmax_scale)
 
 
@@ -43,10 +43,10 @@ def dmha_fwd(q, k, v, cu_seq_k, max_seq_k, is_alibi=False, softmax_scale=None, o
     return decoding_attn_cuda.dmha_fwd(q, k, v, cu_seq_k, max_seq_k, is_alibi, softmax_scale, out, return_lse)
 
 
-def dmla_fwd(q, kv, cu_seq_k, max_seq_k, dim_v=512, softmax_scale=None, out=None, return_lse=False):
+def dmla_fwd(q, kv, cu_seq_k, max_seq_k, dim_v=512, softmax_scale=None, out=None, return_lse=False, is_alibi=False):
     """MLA decode attention over the latent KV cache ``kv`` [total_k, 1, 576]; V = kv[..., :dim_v]."""
     q, kv = [maybe_contiguous(x) for x in (q, kv)]
-    return decoding_attn_cuda.dmla_fwd(q, kv, cu_seq_k, max_seq_k, dim_v, softmax_scale, out, return_lse)
+    return decoding_attn_cuda.dmla_fwd(q, kv, cu_seq_k, max_seq_k, dim_v, is_alibi, softmax_scale, out, return_lse)
 
 
 def paged_fwd(q, k_cache, v_cache, seq_lens, block_table, max_seq_k=None, dim_v=None, is_alibi=False, softmax_scale=None,

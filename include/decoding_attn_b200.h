@@ -47,7 +47,9 @@ typedef struct da_decode_args {
     void *o;                 /* device [batch, head_q, dim_v]; may be NULL if o_f32 is given */
     const int32_t *cu_seq_k; /* device [batch + 1], cumulative sequence lengths */
 
-    int64_t max_seq_k; /* upper bound of every sequence length; a scheduling hint, not a limit */
+    int64_t max_seq_k; /* expected longest sequence: sizes the key-range splits.  Longer sequences are
+                        * still read to their end (by their last split), only less evenly balanced;
+                        * with a block table, its rows must cover every real length. */
     int64_t batch, head_q, head_k, dim, dim_v;
 
     /* Row strides in elements (distance between consecutive tokens); 0 = packed, i.e. what the
@@ -92,7 +94,12 @@ typedef struct da_decode_args {
  * the reference; any other pair returns DA_ERR_UNSUPPORTED instead of silently doing nothing.
  * A zero-length sequence gives a zero row (LSE = -inf) instead of an unwritten one.
  * With workspace == NULL the library keeps one grow-only scratch buffer per device; calls that may
- * overlap on one device (different streams) must then pass their own workspace. */
+ * overlap on one device (different streams) must then pass their own workspace, and so must a call
+ * made during stream capture (growing the buffer calls cudaMalloc).
+ * Bounded waits: a kernel whose wait runs out records it for da_device_status(); the CTAs of that
+ * same launch that have not started yet retire at once, later launches are not affected.  A replayed
+ * CUDA graph repeats its launch ids: after a timeout inside a replay, read da_device_status() (which
+ * clears the record) before replaying again. */
 int da_decode_fwd(const da_decode_args_t *args);
 
 /* The same call for a caller whose tensors live in HOST memory (q, k, v, o, cu_seq_k, lse are host
@@ -151,6 +158,13 @@ int da_merge_partials(const float *part_o, const float *part_lse, int32_t num_pa
 int da_exchange_merge(const float *rec, void *const *peer_bufs, int32_t world, int32_t rank, int64_t rows,
                       int32_t dim_v, uint32_t epoch, void *o, float *lse, int32_t is_bf16, void *stream);
 size_t da_exchange_buffer_bytes(int32_t world, int64_t rows, int32_t dim_v);
+/* The same with the bound of the wait for the peers' flags given in SM clocks (0 = the default, about a
+ * quarter of a second).  A short bound lets a host that watches its peers give up on a dead one quickly;
+ * the tests use it to run the give-up path (a peer that never posts) without stalling a GPU.
+ * No reference counterpart. */
+int da_exchange_merge_bounded(const float *rec, void *const *peer_bufs, int32_t world, int32_t rank, int64_t rows,
+                              int32_t dim_v, uint32_t epoch, void *o, float *lse, int32_t is_bf16, void *stream,
+                              int64_t max_wait_cycles);
 
 /* Profiling hook for the calling thread: while both are non-NULL, da_decode_fwd records the CUDA
  * event `start_event` on the stream just before its main (key-streaming) kernel and `stop_event`

@@ -40,37 +40,34 @@ def check(cabi, oracle, w, num_splits=0, **kw):
     return o
 
 
-# The reference suite's grid (tests/test_decoding_attn.py:61-66), thinned: every dim, both head
-# ratios, both dtypes, the three sequence lengths; batch 16 only for dim 128.
-REF_GRID = [(hq, hk, d, b, s, dt)
-            for d in (64, 96, 128, 256) for (hq, hk) in ((32, 8), (32, 32), (64, 8))
-            for (b, s) in ((1, 1), (2, 128), (2, 512)) for dt in (torch.float16, torch.bfloat16)
-            if not (hq == 64 and d in (96, 256))] + [(32, 8, 128, 16, 128, torch.float16),
-                                                      (64, 32, 128, 16, 512, torch.bfloat16)]
-
-
-@pytest.mark.parametrize("hq,hk,d,b,s,dt", REF_GRID)
+# The reference suite's whole grid (tests/test_decoding_attn.py:61-66): 2 x 2 x 4 x 3 x 3 x 2 = 288 cases.
+@pytest.mark.parametrize("hq", [32, 64])
+@pytest.mark.parametrize("hk", [8, 32])
+@pytest.mark.parametrize("d", [64, 96, 128, 256])
+@pytest.mark.parametrize("b", [1, 2, 16])
+@pytest.mark.parametrize("s", [1, 128, 512])
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
 def test_reference_grid_mha_gqa(native_lib, oracle, hq, hk, d, b, s, dt):
     w = synth.Workload(f"grid_{hq}_{hk}_{d}_{b}_{s}", dt, hq, hk, d, d, [s] * b, dist="normal", seed=11)
     check(native_lib, oracle, w)
 
 
+# tests/test_decoding_attn.py:97-104: 4 x 3 x 3 x 2 = 72 cases.
 @pytest.mark.parametrize("hq", [16, 32, 64, 128])
-@pytest.mark.parametrize("b,s", [(1, 1), (2, 128), (2, 512)])
+@pytest.mark.parametrize("b", [1, 2, 16])
+@pytest.mark.parametrize("s", [1, 128, 512])
 @pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
 def test_reference_grid_mla(native_lib, oracle, hq, b, s, dt):
-    # tests/test_decoding_attn.py:97-104
     w = synth.Workload(f"mla_{hq}_{b}_{s}", dt, hq, 1, 576, 512, [s] * b, dist="normal", scale=0.5, mla=True, seed=12)
     check(native_lib, oracle, w)
 
 
-@pytest.mark.parametrize("lens", [[64], [33], [1], [700, 0, 129], [2100]])
-@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
-def test_mla_cluster_pair_kernel(native_lib, oracle, monkeypatch, lens, dt):
-    """The opt-in MLA kernel whose two CTAs per key range form a cluster, split the 576-long contraction
-    and swap partial scores through distributed shared memory (DA_MLA_PAIR=1)."""
-    monkeypatch.setenv("DA_MLA_PAIR", "1")
-    w = synth.Workload(f"mla_pair_{lens}", dt, 128, 1, 576, 512, lens, is_alibi=(len(lens) > 1), dist="normal",
+@pytest.mark.parametrize("lens", [[128], [64], [33], [1], [129, 0, 700], [2100], [257, 256, 255]])
+@pytest.mark.parametrize("hq", [128, 96, 64, 16, 8])
+def test_mla_pair_kernel_edges(native_lib, oracle, lens, hq):
+    """The latent-KV kernel on SM pairs: ragged last tiles (one or both CTAs of the pair past the end), empty
+    sequences, head counts that leave the second CTA partly or wholly padding, splits, ALiBi."""
+    w = synth.Workload(f"mla2_{hq}_{lens}", torch.bfloat16, hq, 1, 576, 512, lens, is_alibi=(len(lens) > 1), dist="normal",
                        scale=0.3, mla=True, seed=23)
     check(native_lib, oracle, w)
     check(native_lib, oracle, w, num_splits=3)

@@ -84,6 +84,53 @@ def test_named_entry_points_scale_out_and_lse(api, oracle):
     assert_close(api.dmla_fwd(q.to(DEV), kv.to(DEV), cu.to(DEV), 200, softmax_scale=0.05), expect, "dmla_fwd")
 
 
+def test_mla_keeps_alibi_with_and_without_scale(api, oracle):
+    """The reference's fwd() honours is_alibi when v is None (csrc/torch/decoding_torch.cpp:19-21, :76-77)."""
+    wm = synth.Workload("mla_alibi", torch.bfloat16, 128, 1, 576, 512, [333, 70], is_alibi=True, dist="normal", scale=0.3,
+                        mla=True, seed=12)
+    q, kv, _, cu = wm.make("cpu")
+    dq, dkv, dcu = q.to(DEV), kv.to(DEV), cu.to(DEV)
+    plain = oracle.attn_cpu(q, kv, None, cu, dim_v=512, is_alibi=False)
+    expect = oracle.attn_cpu(q, kv, None, cu, dim_v=512, is_alibi=True)
+    assert (plain.float() - expect.float()).abs().max().item() > 1e-2, "the case must be sensitive to the bias"
+    assert_close(api.decoding_attn_fwd(dq, dkv, None, dcu, 333, 512, True), expect, "fwd, v None, alibi")
+    expect_s = oracle.attn_cpu(q, kv, None, cu, dim_v=512, is_alibi=True, softmax_scale=0.05)
+    assert_close(api.decoding_attn_fwd(dq, dkv, None, dcu, 333, 512, True, softmax_scale=0.05), expect_s,
+                 "decoding_attn_fwd, v None, alibi, scale")
+    assert_close(api.dmla_fwd(dq, dkv, dcu, 333, softmax_scale=0.05, is_alibi=True), expect_s, "dmla_fwd alibi")
+
+
+def test_two_streams_and_graph_capture_through_the_binding(api, oracle):
+    """The binding takes its split scratch from torch's stream-ordered allocator: calls on two streams of one
+    device do not share it, and a call can be captured in a CUDA graph and replayed."""
+    w = synth.Workload("streams", torch.bfloat16, 32, 8, 128, 128, [4000, 900, 2500], dist="normal", scale=0.5, seed=13)
+    q, k, v, cu = w.make("cpu")
+    expect = oracle.attn_cpu(q, k, v, cu)
+    dq, dk, dv, dcu = q.to(DEV), k.to(DEV), v.to(DEV), cu.to(DEV)
+    torch.cuda.synchronize()
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    outs = []
+    for _ in range(4):
+        for st in (s1, s2):
+            with torch.cuda.stream(st):
+                outs.append(api.decoding_attn_fwd(dq, dk, dv, dcu, 4000, 128, False))
+    torch.cuda.synchronize()
+    for o in outs:
+        assert_close(o, expect, "two streams")
+    out = torch.zeros(3, 32, 128, dtype=w.dtype, device=DEV)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        api.dmha_fwd(dq, dk, dv, dcu, 4000, out=out)  # warm-up outside the capture
+        side.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            api.dmha_fwd(dq, dk, dv, dcu, 4000, out=out)
+    out.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    assert_close(out, expect, "graph replay through the binding")
+
+
 def test_non_contiguous_inputs_are_made_contiguous(api, oracle):
     """decoding_attn_interface.py:20-21, :50: maybe_contiguous on q, k, v."""
     w = synth.Workload("noncontig", torch.float16, 8, 8, 64, 64, [90, 40], dist="normal", seed=9)
