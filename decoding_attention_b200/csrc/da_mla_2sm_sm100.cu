@@ -53,24 +53,9 @@ constexpr int kVBlocks = 4;        // V blocks per CTA (256 of the 512 output di
 #define DA_MLA2_VSLOTS 3
 #define DA_MLA2_PBUFS 1
 #endif
-#ifndef DA_MLA2_TMABLOCKS
-#define DA_MLA2_TMABLOCKS 9
-#endif
-#ifndef DA_MLA2_CPASYNC
-#define DA_MLA2_CPASYNC cp_async16
-#endif
-#ifndef DA_MLA2_LAG
-#define DA_MLA2_LAG 1
-#endif
 constexpr int kQTmemBlocks = DA_MLA2_QTMEM;    // Q blocks 0..3 live in TMEM
 constexpr int kQSmemBlocks = kBlocks - kQTmemBlocks;
 constexpr int kBlockBytes = 64 * 128;  // [64 rows x 64 elements], 128-byte swizzle: a Q, K or P block
-// K blocks 0 .. kTmaBlocks-1 of a tile come by TMA through the ring, the others (if any) by cp.async into one slot.
-// Measured on B200 (batch 128 x 4096 keys): all nine by TMA 181 us; five by TMA and four by cp.async 283 us -- faster
-// per tile on an idle GPU (3 540 against 4 170 cycles) but the load/store path degrades when every SM pulls 96 KB
-// per tile through it (one wave of 74 pairs: 149 us against 90 us).
-constexpr int kTmaBlocks = DA_MLA2_TMABLOCKS;
-constexpr int kLsuBlocks = kBlocks - kTmaBlocks;
 constexpr int kASlots = DA_MLA2_ASLOTS;         // ring of TMA-streamed K blocks
 constexpr int kVSlots = DA_MLA2_VSLOTS;         // ring of V half-tiles
 constexpr int kVSlotBytes = kVBlocks * kBlockBytes;
@@ -78,12 +63,11 @@ constexpr int kPBufs = DA_MLA2_PBUFS;          // P tiles in shared memory
 constexpr int kPBytes = 2 * kBlockBytes;  // [64 heads x 128 keys]
 constexpr int kOffQ = 0;
 constexpr int kOffA = kOffQ + kQSmemBlocks * kBlockBytes;
-constexpr int kOffS4 = kOffA + kASlots * kBlockBytes;   // K blocks 5..8 of the current tile
-constexpr int kOffV = kOffS4 + kLsuBlocks * kBlockBytes;  // (no such slot when all blocks come by TMA)
+constexpr int kOffV = kOffA + kASlots * kBlockBytes;
 constexpr int kOffP = kOffV + kVSlots * kVSlotBytes;
 constexpr int kOffBar = kOffP + kPBufs * kPBytes;
-// q_full, q_tmem, q_stage_full, q_copied, s4_full, s4_empty, a_full/a_empty[kASlots], v_full/v_empty[kVSlots], s_full[2], p_full[2], pv_done[2]
-constexpr int kNumBars = 6 + 2 * kASlots + 2 * kVSlots + 6;
+// q_full, q_tmem, q_stage_full, q_copied, a_full/a_empty[kASlots], v_full/v_empty[kVSlots], s_full[2], p_full[2], pv_done[2]
+constexpr int kNumBars = 4 + 2 * kASlots + 2 * kVSlots + 6;
 constexpr int kOffMisc = kOffBar + kNumBars * 8;          // tmem slot, abort flag
 constexpr int kOffXch = kOffMisc + 16;                    // float [2][128] tile maxima, float [128] row sums
 constexpr int kSmemBytes = kOffXch + 3 * 128 * 4 + 1024;  // + alignment slack
@@ -95,8 +79,6 @@ constexpr int kColS = 0;      // two S buffers of 64 columns
 constexpr int kColO = 128;    // 256 output columns
 constexpr int kColQ = 384;    // kQTmemBlocks * 32 columns
 static_assert(kColQ + kQTmemBlocks * 32 <= kTmemCols, "TMEM budget");
-static_assert(kLsuBlocks == 0 || kLsuBlocks == 4, "the cp.async slot holds four blocks");
-static_assert(kQTmemBlocks <= kTmaBlocks, "the blocks loaded by cp.async meet Q blocks that live in shared memory");
 static_assert(kQTmemBlocks * kBlockBytes <= kVSlotBytes && kVSlots >= 2, "Q blocks 0..3 are staged in the last V slot");
 static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 static_assert(128 * (256 * 4 + 16) <= kOffP - kOffA, "the epilogue stages its output in the idle rings");
@@ -139,7 +121,6 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
 
     uint8_t *q_s = smem + kOffQ;
     uint8_t *a_s = smem + kOffA;
-    uint8_t *s4_s = smem + kOffS4;
     uint8_t *v_s = smem + kOffV;
     uint8_t *p_s = smem + kOffP;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBar);
@@ -147,9 +128,7 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
     uint64_t *q_tmem = bars + 1;   // rank 0: Q blocks of both CTAs are in TMEM
     uint64_t *q_stage_full = bars + 2;  // this CTA: Q blocks 0..3 landed in the staging slot
     uint64_t *q_copied = bars + 3;      // this CTA: the softmax warps have moved them to TMEM
-    uint64_t *s4_full = bars + 4;       // rank 0: K blocks 5..8 landed in both CTAs
-    uint64_t *s4_empty = bars + 5;
-    uint64_t *a_full = bars + 6;   // rank 0: streamed K block landed in both CTAs
+    uint64_t *a_full = bars + 4;   // rank 0: streamed K block landed in both CTAs
     uint64_t *a_empty = a_full + kASlots;
     uint64_t *v_full = a_empty + kASlots;  // rank 0: V half-tile landed in both CTAs
     uint64_t *v_empty = v_full + kVSlots;
@@ -166,8 +145,6 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
         mbar_init(q_tmem, 8);
         mbar_init(q_stage_full, 1);
         mbar_init(q_copied, 4);
-        mbar_init(s4_full, 2 * kLoaderWarps);
-        mbar_init(s4_empty, 1);
         for (int s = 0; s < kASlots; ++s) {
             mbar_init(&a_full[s], 1);
             mbar_init(&a_empty[s], 1);
@@ -224,7 +201,7 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             const int key0 = k_begin + t * kTile + (int)rank * kHalf;  // this CTA's first key of the tile
             const int rows = max(0, min(kHalf, k_end - key0));
             const size_t tok0 = rows > 0 ? kv_tile_row(p, b, seq_begin, key0) : 0;
-            for (int j = 0; j < kTmaBlocks && ok; ++j) {
+            for (int j = 0; j < kBlocks && ok; ++j) {
                 if (round > 0) ok = mbar_wait(&a_empty[slot], (round & 1u) ^ 1u, abort_flag);
                 if (!ok) break;
                 uint8_t *dst = a_s + slot * kBlockBytes;
@@ -270,7 +247,6 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             const uint32_t leader = elect_one();
             const uint64_t q_desc0 = smem_desc(smem_u32(q_s), 16, 1024, 2);
             const uint64_t a_desc0 = smem_desc(smem_u32(a_s), 16, 1024, 2);
-            const uint64_t s4_desc0 = smem_desc(smem_u32(s4_s), 16, 1024, 2);
             const uint64_t p_desc0 = smem_desc(smem_u32(p_s), 16, 1024, 2);
             const uint64_t v_desc0 = smem_desc(smem_u32(v_s), kBlockBytes, 1024, 2);  // V slot, MN-major
             const uint32_t q_tmem_addr = tmem_base + kColQ;
@@ -278,19 +254,22 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             uint32_t a_round = 0;
                 auto issue_qk = [&](int t) -> bool {
                 const uint32_t d = tmem_base + kColS + (t & 1) * 64;
-#pragma unroll
-                for (int j = 0; j < kTmaBlocks; ++j) {
+                // (rolled over the blocks, unrolled over the four 16-element steps of a block: small code, and the
+                // descriptors of a block differ from the previous block's by constants)
+#pragma unroll 1
+                for (int j = 0; j < kBlocks; ++j) {
                     if (!mbar_wait(&a_full[a_slot], a_round & 1u, abort_flag)) return false;
                     tc_fence_after();
                     const uint64_t bd = a_desc0 + (uint64_t)((a_slot * kBlockBytes) >> 4);
+                    if (j < kQTmemBlocks) {
 #pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        if (j < kQTmemBlocks) {
+                        for (int ks = 0; ks < 4; ++ks)
                             umma2_ts(d, q_tmem_addr + j * 32 + ks * 8, bd + (uint64_t)(ks * 2), kIdescQK, (j | ks) ? 1u : 0u, leader);
-                        } else {
-                            umma2_ss(d, q_desc0 + (uint64_t)((((j - kQTmemBlocks) * kBlockBytes) >> 4) + ks * 2),
-                                     bd + (uint64_t)(ks * 2), kIdescQK, (j | ks) ? 1u : 0u, leader);
-                        }
+                    } else {
+                        const uint64_t qd = q_desc0 + (uint64_t)(((j - kQTmemBlocks) * kBlockBytes) >> 4);
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks)
+                            umma2_ss(d, qd + (uint64_t)(ks * 2), bd + (uint64_t)(ks * 2), kIdescQK, (j | ks) ? 1u : 0u, leader);
                     }
                     umma2_commit_both(&a_empty[a_slot], leader);
                     if (++a_slot == kASlots) {
@@ -298,34 +277,20 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
                         ++a_round;
                     }
                 }
-                if (kLsuBlocks > 0) {
-                    if (!mbar_wait(s4_full, (uint32_t)t & 1u, abort_flag)) return false;
-                    tc_fence_after();
-                }
-#pragma unroll
-                for (int j = kTmaBlocks; j < kBlocks; ++j) {
-                    const uint64_t bd = s4_desc0 + (uint64_t)(((j - kTmaBlocks) * kBlockBytes) >> 4);
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        umma2_ss(d, q_desc0 + (uint64_t)((((j - kQTmemBlocks) * kBlockBytes) >> 4) + ks * 2),
-                                 bd + (uint64_t)(ks * 2), kIdescQK, 1u, leader);
-                    }
-                }
-                if (kLsuBlocks > 0) umma2_commit_both(s4_empty, leader);
                 umma2_commit_both(&s_full[t & 1], leader);
                 return true;
             };
             ok = mbar_wait(q_full, 0, abort_flag);
             if (ok) ok = mbar_wait(q_tmem, 0, abort_flag);
-            if (ok) {
-                tc_fence_after();
-                ok = issue_qk(0);
-            }
-            for (int t = 0; t < n_tiles && ok; ++t) {
+            if (ok) tc_fence_after();
+            // Issue order S(0) S(1) P.V(0) S(2) P.V(1) ...: one call site for S keeps the kernel's code small
+            // (the unrolled issue sequences of all roles have to share the instruction cache).
+            for (int t = -1; t < n_tiles && ok; ++t) {
                 if (t + 1 < n_tiles) {
                     ok = issue_qk(t + 1);
                     if (!ok) break;
                 }
+                if (t < 0) continue;
                 ok = mbar_wait(&p_full[t & 1], (uint32_t)(t / 2) & 1u, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
@@ -360,70 +325,40 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
         // the same blocks of tile t+1 and the two V half-tiles of tile t.  A job is published (its barrier in the
         // rank-0 CTA gets this warp's arrival) once the next one has been issued and its own bytes have landed,
         // so two jobs are in flight.
+        // One copy of the copy code for every half-tile (the kernel's unrolled loops share the instruction cache: a
+        // version of this loop that was inlined four times made the whole kernel 30 % slower).  A half-tile's
+        // barrier gets this warp's arrival once the next one has been issued and its own bytes have landed: two
+        // half-tiles are in flight.
         const int lt = tid - 6 * 32;  // 0..127
-        // Published with a lag of kLag jobs: job n's barrier gets this warp's arrival once jobs n+1 .. n+kLag have
-        // been issued and job n's bytes have landed, so kLag + 1 jobs are in flight.
-        constexpr int kLag = DA_MLA2_LAG;
-        uint32_t pend_bar[kLag];
-        int n_pend = 0;
-        auto publish_oldest = [&](auto newer) {  // newer: jobs issued after the oldest unpublished one
-            cp_async_wait<decltype(newer)::value>();
-            fence_proxy_async();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_remote_cta(pend_bar[0]);
-#pragma unroll
-            for (int x = 0; x + 1 < kLag; ++x) pend_bar[x] = pend_bar[x + 1];
-            --n_pend;
-        };
-        auto issued = [&](uint32_t bar) {  // a job has just been committed
-            if (n_pend == kLag) publish_oldest(std::integral_constant<int, kLag>());
-            pend_bar[n_pend++] = bar;
-        };
-        // 4 blocks x 64 keys x 128 bytes from column block `first_block` of the rows [key0, key0 + 64) of this key range
-        auto issue_rows = [&](uint8_t *slot, int key0, int first_block) {
+        const int n_halves = 2 * n_tiles;
+        for (int i = 0; i < n_halves && ok; ++i) {
+            const int key0 = k_begin + (i >> 1) * kTile + (i & 1) * kHalf;
             const int rows = max(0, min(kHalf, k_end - key0));
             const size_t tok0 = rows > 0 ? kv_tile_row(p, b, seq_begin, key0) : 0;
-#pragma unroll
-            for (int n = 0; n < 4 * kHalf * 8 / kLoaderThreads; ++n) {
-                const int e = lt + n * kLoaderThreads;
-                const int j = e >> 9, r = (e >> 3) & 63, cc = e & 7;
-                const T *src = k_g + (tok0 + max(0, min(r, rows - 1))) * p.k_row_stride + (first_block + j) * 64 + cc * 8;
-                DA_MLA2_CPASYNC(slot + j * kBlockBytes + r * 128 + ((cc ^ (r & 7)) << 4), src, r < rows ? 16u : 0u);  // 0: zero fill
-            }
-            cp_async_commit();
-        };
-        auto load_s4 = [&](int t) {  // K blocks kTmaBlocks..8 of this CTA's 64 keys of tile t
-            if (kLsuBlocks == 0) return;
-            if (t >= 1) ok = mbar_wait(s4_empty, (uint32_t)(t - 1) & 1u, abort_flag);
-            if (!ok) return;
-            issue_rows(s4_s, k_begin + t * kTile + (int)rank * kHalf, kTmaBlocks);
-            issued(lead(s4_full));
-        };
-        auto load_v = [&](int i) {  // this CTA's 256 dims of the 64 keys of half-tile i
             const int vs = i % kVSlots;
             if (i >= kVSlots) ok = mbar_wait(&v_empty[vs], ((uint32_t)(i / kVSlots) & 1u) ^ 1u, abort_flag);
             if (ok && i == kVSlots - 1) ok = mbar_wait(q_copied, 0, abort_flag);  // the slot staged Q blocks until now
-            if (!ok) return;
-            issue_rows(v_s + vs * kVSlotBytes, k_begin + (i >> 1) * kTile + (i & 1) * kHalf, (int)rank * kVBlocks);
-            issued(lead(&v_full[vs]));
-        };
-        // Order: what the tensor pipe needs first comes first, and no job's wait for its slot depends on one of the
-        // kLag jobs before it (those are still unpublished): S4(0) V(0)a S4(1) V(0)b S4(2) | V(t)a V(t)b S4(t+2) ...
-        load_s4(0);
-        if (ok) load_v(0);
-        if (ok && n_tiles > 1) load_s4(1);
-        if (ok) load_v(1);
-        if (ok && n_tiles > 2) load_s4(2);
-        for (int t = 1; t < n_tiles && ok; ++t) {
-            load_v(2 * t);
-            if (ok) load_v(2 * t + 1);
-            if (ok && t + 2 < n_tiles) load_s4(t + 2);
-        }
-        if (ok) {
-            if (kLag >= 2 && n_pend == 2) publish_oldest(std::integral_constant<int, 1>());
-            if (n_pend == 1) publish_oldest(std::integral_constant<int, 0>());
+            if (!ok) break;
+            uint8_t *slot = v_s + vs * kVSlotBytes;
+#pragma unroll
+            for (int n = 0; n < kVBlocks * kHalf * 8 / kLoaderThreads; ++n) {
+                const int e = lt + n * kLoaderThreads;
+                const int j = e >> 9, r = (e >> 3) & 63, cc = e & 7;
+                const T *src = k_g + (tok0 + max(0, min(r, rows - 1))) * p.k_row_stride + ((int)rank * kVBlocks + j) * 64 + cc * 8;
+                cp_async16(slot + j * kBlockBytes + r * 128 + ((cc ^ (r & 7)) << 4), src, r < rows ? 16u : 0u);  // 0: zero fill
+            }
+            cp_async_commit();
+            if (i >= 1) {  // the half-tile issued one iteration ago has landed: publish it to the tensor pipe
+                cp_async_wait<1>();
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_remote_cta(lead(&v_full[(i - 1) % kVSlots]));
+            }
         }
         cp_async_wait<0>();
+        fence_proxy_async();
+        __syncwarp();
+        if (ok && lane == 0) mbar_arrive_remote_cta(lead(&v_full[(n_halves - 1) % kVSlots]));
     } else {
         // ---------------- softmax / epilogue: thread l <-> TMEM lane l <-> (head l & 63, key half l >> 6) ----------------
         const int r = tid & 63, kh = tid >> 6;
@@ -607,15 +542,14 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
                 if (valid) bulk_store_s2g(dst_g, mine, 256 * 2);
                 bulk_store_commit();
             };
-            if (p.num_splits > 1) {
-                stage_f32(p.part_o + row * kDimV + d_first);
-            } else {
-                if (p.o_f32) {
-                    stage_f32(p.o_f32 + ((size_t)b * p.head_q + head) * kDimV + d_first);
-                    if (o_out) bulk_store_wait_read();  // the staging bytes are about to be reused
-                }
-                if (o_out) stage_t(o_out + (size_t)b * p.o_row_stride + (size_t)head * kDimV + d_first);
+            float *dst_f32 = p.num_splits > 1 ? p.part_o + row * kDimV + d_first
+                                              : (p.o_f32 ? p.o_f32 + ((size_t)b * p.head_q + head) * kDimV + d_first : nullptr);
+            const bool want_t = p.num_splits == 1 && o_out != nullptr;
+            if (dst_f32) {
+                stage_f32(dst_f32);
+                if (want_t) bulk_store_wait_read();  // the staging bytes are about to be reused
             }
+            if (want_t) stage_t(o_out + (size_t)b * p.o_row_stride + (size_t)head * kDimV + d_first);
             bulk_store_wait_read();
             if (kh == 0 && valid) {
                 if (p.num_splits > 1) {

@@ -6,8 +6,11 @@
 // loop that forbids calls which may block on the driver's allocation path) -- cannot let this
 // library call cudaMalloc for the split-KV partials, and may not have a spare buffer to lend as
 // `workspace` either.  For them the partials live in a fixed array that is part of the library
-// image: it costs kStaticScratchBytes on every GPU that loads the library, from load to exit,
-// whether this entry point is used or not.
+// image: kStaticScratchBytes on every GPU that uses this entry point.  The CUDA runtime loads a
+// module's device code lazily, so the array is materialised on a device by the first call there
+// (the cudaGetSymbolAddress below), not when the library is loaded: a host that is about to commit
+// all of its memory should make one call per device at start-up, while the memory is still there,
+// and nothing is allocated by any later call.
 //
 // The array is shared by all calls on a device and keeps whatever the last call left in it.  That
 // is harmless here: the split kernels write every partial (row, split) that the merge kernel will

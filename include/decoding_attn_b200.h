@@ -111,15 +111,17 @@ int da_decode_fwd(const da_decode_args_t *args);
 int da_decode_fwd_host(const da_decode_args_t *host_args);
 
 /* da_decode_fwd for a caller that cannot allocate device memory and has no buffer to lend: the
- * split partials go to a fixed 16 MiB array inside the library image (da_static_scratch_bytes()),
- * present on every GPU that loads the library.  Meant for hosts whose memory is fully planned by
- * someone else -- an engine that gave all of HBM to its KV-cache pool, code running where calls
- * into the CUDA allocator are forbidden.  Leave args->workspace NULL.  Returns DA_ERR_WORKSPACE,
- * without launching anything, when the call would need more than the array holds (num_splits = 1
- * needs at most 4 bytes per sequence and always fits).  It calls no cudaMalloc / cudaFree.  The first call on a device looks up
- * the array's device address (cudaGetSymbolAddress); make that first call outside any stream
- * capture.  All calls on a device share the array, which keeps the previous call's bytes (nothing
- * in it needs clearing): calls that overlap on the GPU race, so keep them on one stream.
+ * split partials go to a fixed 16 MiB array inside the library image (da_static_scratch_bytes()).
+ * Meant for hosts whose memory is fully planned by someone else -- an engine that gave all of HBM
+ * to its KV-cache pool, code running where calls into the CUDA allocator are forbidden.  Leave
+ * args->workspace NULL.  Returns DA_ERR_WORKSPACE, without launching anything, when the call would
+ * need more than the array holds (num_splits = 1 needs at most 4 bytes per sequence and always
+ * fits).  It calls no cudaMalloc / cudaFree.  The first call on a device looks up the array's
+ * device address (cudaGetSymbolAddress), which is also the moment the runtime puts the array on
+ * that device (device code is loaded lazily): make that first call at start-up, before the host
+ * commits the rest of the memory, and outside any stream capture.  All calls on a device share the
+ * array, which keeps the previous call's bytes (nothing in it needs clearing): calls that overlap
+ * on the GPU race, so keep them on one stream.
  * This entry point has no counterpart in the reference, whose kernel keeps its only scratch in
  * shared memory. */
 int da_decode_fwd_static(const da_decode_args_t *args);

@@ -107,8 +107,11 @@ def test_exchange_kernel_gives_up_on_a_peer_that_never_posts(native_lib, oracle)
     assert native_lib.device_status() == native_lib.DA_ERR_TIMEOUT
     assert native_lib.device_status() == native_lib.DA_OK
     assert (o == 7.0).all(), "rows must be left unwritten when the exchange gives up"
-    # rank 0's record did reach slot 0 of "rank 1"'s buffer (the push happens before the wait)
-    assert torch.equal(bufs[1][:rows * dv], rec[:rows * dv])
+    # rank 0's record did reach its slot of "rank 1"'s buffer (the push happens before the wait): slots are laid
+    # out [epoch parity][rank], each rows * (dv + 1) floats rounded up to a multiple of 4
+    slot = (rows * (dv + 1) + 3) // 4 * 4
+    at = (1 * 2 + 0) * slot
+    assert torch.equal(bufs[1][at:at + rows * dv], rec[:rows * dv])
     w = synth.Workload("after_xchg", torch.float16, 8, 2, 128, 128, [300], dist="normal", seed=66)
     q, k, v, cu = w.make("cpu")
     o2 = torch.empty(1, 8, 128, dtype=w.dtype, device=DEV)

@@ -5,8 +5,10 @@ that has given the whole GPU to its own cache pool, or code that runs where the 
 not be entered.  For them the split partials live in a fixed array inside the library.  This test
 calls that entry point through the C ABI twice in a row -- the second call on a different, smaller
 problem, so that it runs over whatever the first one left in the array -- and requires each result
-to match the ordinary entry point's within the parity tolerance of the other GPU tests.  It sits in
-a file that pytest collects last, so a run that stops at the first failure has already run
+to match the ordinary entry point's within the parity tolerance of the other GPU tests (in fact bit
+for bit: both run the same kernels on the same split plan) and the CPU oracle's.  After the first
+call on the device, further calls must leave the amount of free device memory unchanged.  It sits
+in a file that pytest collects last, so a run that stops at the first failure has already run
 everything else.
 """
 import pytest
@@ -34,7 +36,7 @@ def _both(cabi, w, num_splits):
     return outs
 
 
-def test_static_scratch_matches_ordinary_entry_point_twice(native_lib):
+def test_static_scratch_matches_ordinary_entry_point_twice(native_lib, oracle):
     first = synth.Workload("noalloc_a", torch.bfloat16, 32, 8, 128, 128, [3000, 517, 64, 1900], dist="normal",
                            scale=0.5, seed=31)
     second = synth.Workload("noalloc_b", torch.float16, 16, 16, 64, 64, [700, 0, 129], is_alibi=True, dist="uniform",
@@ -42,6 +44,25 @@ def test_static_scratch_matches_ordinary_entry_point_twice(native_lib):
     for w, splits in ((first, 6), (second, 3)):
         ref, got = _both(native_lib, w, splits)
         assert_close(got, ref, w.name)
+        assert torch.equal(got, ref), "same kernels, same split plan: the two entry points must agree bit for bit"
+        assert_close(got, oracle.attn_cpu(*w.make("cpu"), dim_v=w.dim_v, is_alibi=w.is_alibi), w.name + " vs oracle")
+
+
+def test_static_scratch_calls_allocate_nothing(native_lib):
+    """Once the first call on the device has resolved the array, a call must not change the free device memory."""
+    w = synth.Workload("noalloc_mem", torch.bfloat16, 32, 8, 128, 128, [2500, 900], dist="normal", scale=0.5, seed=34)
+    q, k, v, cu = [t.to(DEV) for t in w.make("cpu")]
+    o = torch.empty(w.batch, w.head_q, w.dim_v, dtype=w.dtype, device=DEV)
+    args = native_lib.make_args(q, k, v, o, cu, w.max_seq_k, w.dim_v, num_splits=5,
+                                stream=torch.cuda.current_stream().cuda_stream)
+    native_lib.decode_fwd_static(args)  # the warm-up call an allocation-free host makes at start-up
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        native_lib.decode_fwd_static(args)
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, f"free device memory changed by {free_before - free_after} bytes"
 
 
 def test_static_scratch_rejects_oversized_and_foreign_workspace(native_lib):
