@@ -33,7 +33,8 @@ class DecodeArgs(ctypes.Structure):
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
         ("stream", ctypes.c_void_p),
         ("block_table", ctypes.c_void_p), ("block_table_stride", ctypes.c_int64),
-        ("page_size", ctypes.c_int32), ("reserved1", ctypes.c_int32),
+        ("page_size", ctypes.c_int32),
+        ("kv_dtype", ctypes.c_int32), ("k_scale", ctypes.c_float), ("v_scale", ctypes.c_float),
     ]
 
 
@@ -101,11 +102,13 @@ def _ptr(t):
 
 def make_args(q, k, v, o, cu_seq_k, max_seq_k, dim_v, is_alibi=False, softmax_scale=None, lse=None, o_f32=None,
               kv_pos_offset=None, kv_total_len=None, workspace=None, num_splits=0, stream=0, packed=False,
-              block_table=None, page_size=0):
+              block_table=None, page_size=0, k_scale=None, v_scale=None):
     """Fill a DecodeArgs from torch tensors (device tensors, or host tensors for the *_host call).
 
     Paged cache: pass ``block_table`` (int32 [batch, blocks]) and ``page_size``; ``k`` / ``v`` are then the
-    page pools, either [num_pages * page_size, head_k, dim] or [num_pages, page_size, head_k, dim]."""
+    page pools, either [num_pages * page_size, head_k, dim] or [num_pages, page_size, head_k, dim].
+    FP8 cache: ``k`` / ``v`` of dtype torch.float8_e4m3fn (q and o stay fp16 / bf16) with per-tensor
+    ``k_scale`` / ``v_scale`` (default 1)."""
     import torch
     a = DecodeArgs()
     a.struct_size = ctypes.sizeof(DecodeArgs)
@@ -132,6 +135,10 @@ def make_args(q, k, v, o, cu_seq_k, max_seq_k, dim_v, is_alibi=False, softmax_sc
         a.workspace = workspace.data_ptr()
         a.workspace_bytes = workspace.numel() * workspace.element_size()
     a.stream = int(stream) if stream else None
+    if k.dtype == getattr(torch, "float8_e4m3fn", None):
+        a.kv_dtype = 1
+        a.k_scale = float(k_scale) if k_scale else 1.0
+        a.v_scale = float(v_scale) if v_scale else 1.0
     if block_table is not None:
         a.block_table = block_table.data_ptr()
         a.block_table_stride = block_table.stride(0)

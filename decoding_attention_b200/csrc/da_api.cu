@@ -183,7 +183,7 @@ struct MapKey {
     uint64_t dims[3];
     uint64_t strides[2];
     uint32_t box[3];
-    int rank, swizzle128, bf16;
+    int rank, swizzle128, dtype;  // dtype: 0 fp16, 1 bf16, 2 one-byte elements
 };
 struct MapCacheEntry {
     MapKey key;
@@ -193,16 +193,16 @@ struct MapCacheEntry {
 thread_local MapCacheEntry g_map_cache[8];
 thread_local int g_map_next = 0;
 
-// Tiled tensor map over 16-bit elements; dims/strides/box innermost first, strides in bytes for
+// Tiled tensor map over 16-bit (or, dtype 2, one-byte) elements; dims/strides/box innermost first, strides in bytes for
 // dimensions 1.. (dimension 0 is contiguous).  Recently built maps are kept per thread.
 int make_tensor_map(const void *base, int rank, const uint64_t *dims, const uint64_t *strides, const uint32_t *box,
-                    bool swizzle128, bool bf16, CUtensorMap *out) {
+                    bool swizzle128, int dtype, CUtensorMap *out) {
     MapKey key;
     memset(&key, 0, sizeof(key));
     key.base = base;
     key.rank = rank;
     key.swizzle128 = swizzle128;
-    key.bf16 = bf16;
+    key.dtype = dtype;
     for (int i = 0; i < rank; ++i) {
         key.dims[i] = dims[i];
         key.box[i] = box[i];
@@ -224,7 +224,9 @@ int make_tensor_map(const void *base, int rank, const uint64_t *dims, const uint
         bx[i] = box[i];
         if (i + 1 < rank) st[i] = strides[i];
     }
-    CUresult r = fn(out, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)rank,
+    const CUtensorMapDataType dt = dtype == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                              : (dtype == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+    CUresult r = fn(out, dt, (cuuint32_t)rank,
                     const_cast<void *>(base), d, st, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -237,12 +239,13 @@ int make_tensor_map(const void *base, int rank, const uint64_t *dims, const uint
     return DA_OK;
 }
 
-int make_kv_tensor_map(const void *base, long long row_stride, int head_k, int dim, int tile, bool bf16,
+int make_kv_tensor_map(const void *base, long long row_stride, int head_k, int dim, int tile, int dtype,
                        CUtensorMap *out) {
+    const uint64_t eb = dtype == 2 ? 1 : 2;
     const uint64_t dims[3] = {(uint64_t)dim, (uint64_t)head_k, kMapRows};
-    const uint64_t strides[2] = {(uint64_t)dim * 2, (uint64_t)row_stride * 2};
+    const uint64_t strides[2] = {(uint64_t)dim * eb, (uint64_t)row_stride * eb};
     const uint32_t box[3] = {(uint32_t)dim, 1, (uint32_t)tile};
-    return make_tensor_map(base, 3, dims, strides, box, false, bf16, out);
+    return make_tensor_map(base, 3, dims, strides, box, false, dtype, out);
 }
 
 struct Plan {
@@ -270,11 +273,18 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
                     "with v and (576,512) without",
                     (long long)a.dim, (long long)a.dim_v, has_v ? "given" : "NULL");
     }
-    if (shape == Shape::kMla && mla_on_tensor_cores(a)) {
+    if (a.kv_dtype == DA_KV_FP8_E4M3) {
+        if (shape == Shape::kMla) {
+            return fail(DA_ERR_UNSUPPORTED, "an FP8 cache is supported for (dim, dim_v) (64,64) (96,96) (128,128) (256,256) with v given");
+        }
+    } else if (shape == Shape::kMla && mla_on_tensor_cores(a)) {
         // SM pairs (cta_group::2) unless the cache is paged in pages shorter than the 64 keys one CTA stages at a time
         shape = (!a.block_table || a.page_size >= 64) && !env_overrides().mla_1sm ? Shape::kMla2Sm : Shape::kMlaTc;
     }
-    if ((shape == Shape::kD64 || shape == Shape::kD128 || shape == Shape::kD256) && gqa_on_tensor_cores(a)) shape = Shape::kGqaTc;
+    if (a.kv_dtype != DA_KV_FP8_E4M3 && (shape == Shape::kD64 || shape == Shape::kD128 || shape == Shape::kD256) &&
+        gqa_on_tensor_cores(a)) {
+        shape = Shape::kGqaTc;  // (an FP8 cache is read by the CUDA-core kernel, whatever the group size)
+    }
     const int group = (int)(a.head_q / a.head_k);
     const int heads = heads_per_cta(shape, group);
     const SplitVariantInfo info = variant_info(shape, heads);
@@ -381,10 +391,15 @@ int check_args(const da_decode_args_t *a) {
                              a->head_q * a->dim_v};
     for (int i = 0; i < 4; ++i) {
         if (strides[i] == 0) continue;
-        if (strides[i] < mins[i] || strides[i] % 8 != 0) {
-            return fail(DA_ERR_INVALID_ARG, "row stride %d must be a multiple of 8 elements and cover a row", i);
+        const int64_t unit = (a->kv_dtype == DA_KV_FP8_E4M3 && (i == 1 || i == 2)) ? 16 : 8;  // 16 bytes either way
+        if (strides[i] < mins[i] || strides[i] % unit != 0) {
+            return fail(DA_ERR_INVALID_ARG, "row stride %d must be a multiple of 16 bytes and cover a row", i);
         }
     }
+    if (a->kv_dtype != DA_KV_SAME_AS_Q && a->kv_dtype != DA_KV_FP8_E4M3) {
+        return fail(DA_ERR_INVALID_ARG, "kv_dtype %d: 0 (the type of q) or 1 (FP8 e4m3) expected", a->kv_dtype);
+    }
+    if (a->kv_dtype == DA_KV_FP8_E4M3 && !a->v) return fail(DA_ERR_UNSUPPORTED, "an FP8 cache needs a separate v tensor");
     if (a->block_table) {
         // A key tile (32 or 64 keys) is fetched in runs of consecutive rows: whole, or page by page.
         if (a->page_size < 16 || (a->page_size & (a->page_size - 1)) != 0) {
@@ -509,6 +524,11 @@ int da_decode_fwd(const da_decode_args_t *a) {
     p.is_alibi = a->is_alibi ? 1 : 0;
     const float scale = a->softmax_scale > 0.0f ? a->softmax_scale : (float)(1.0 / std::sqrt((double)a->dim));
     p.scale_log2 = scale * kLog2e;
+    p.out_scale = 1.0f;
+    if (a->kv_dtype == DA_KV_FP8_E4M3) {  // the cache stands for k * k_scale, v * v_scale: both factors leave the loops
+        p.scale_log2 *= a->k_scale > 0.0f ? a->k_scale : 1.0f;
+        p.out_scale = a->v_scale > 0.0f ? a->v_scale : 1.0f;
+    }
     if (plan.order_offset) {
         int *order = reinterpret_cast<int *>(reinterpret_cast<char *>(scratch) + plan.order_offset);
         cudaError_t oe = launch_order(a->cu_seq_k, (int)a->batch, a->max_seq_k, order, stream);
@@ -526,6 +546,7 @@ int da_decode_fwd(const da_decode_args_t *a) {
     const int box_keys = (a->block_table && a->page_size < plan.tile_keys) ? a->page_size : plan.tile_keys;
 
     const bool bf16 = a->is_bf16 != 0;
+    const bool fp8 = a->kv_dtype == DA_KV_FP8_E4M3;
     KvMaps maps;
     memset(&maps, 0, sizeof(maps));
     // Tiled TMA needs a global stride that is a multiple of 16 bytes (checked above: 8 elements) and
@@ -541,15 +562,15 @@ int da_decode_fwd(const da_decode_args_t *a) {
         const uint64_t qd[3] = {dim, (uint64_t)a->head_q, (uint64_t)a->batch};
         const uint64_t qs[2] = {dim * 2, (uint64_t)p.q_row_stride * 2};
         const uint32_t qb[3] = {64, (uint32_t)(a->head_q < 128 ? a->head_q : 128), 1};
-        rc = make_tensor_map(p.q, 3, qd, qs, qb, true, bf16, &tm_q);
+        rc = make_tensor_map(p.q, 3, qd, qs, qb, true, bf16 ? 1 : 0, &tm_q);
         if (rc != DA_OK) return rc;
         const uint64_t kd[3] = {dim, (uint64_t)a->head_k, kMapRows};
         const uint64_t ks[2] = {dim * 2, (uint64_t)p.k_row_stride * 2};
         const uint64_t vs[2] = {dim * 2, (uint64_t)p.v_row_stride * 2};
         const uint32_t kb[3] = {64, 1, (uint32_t)box_keys};
-        rc = make_tensor_map(p.k, 3, kd, ks, kb, true, bf16, &maps.k);
+        rc = make_tensor_map(p.k, 3, kd, ks, kb, true, bf16 ? 1 : 0, &maps.k);
         if (rc != DA_OK) return rc;
-        rc = make_tensor_map(p.v, 3, kd, vs, kb, true, bf16, &maps.v);
+        rc = make_tensor_map(p.v, 3, kd, vs, kb, true, bf16 ? 1 : 0, &maps.v);
         if (rc != DA_OK) return rc;
     }
     if (plan.shape == Shape::kMla2Sm) {
@@ -558,12 +579,12 @@ int da_decode_fwd(const da_decode_args_t *a) {
         const uint64_t qd[3] = {576, (uint64_t)a->head_q, (uint64_t)a->batch};
         const uint64_t qs[2] = {576 * 2, (uint64_t)p.q_row_stride * 2};
         const uint32_t qb[3] = {64, (uint32_t)(a->head_q < 64 ? a->head_q : 64), 1};
-        rc = make_tensor_map(p.q, 3, qd, qs, qb, true, bf16, &maps.k);
+        rc = make_tensor_map(p.q, 3, qd, qs, qb, true, bf16 ? 1 : 0, &maps.k);
         if (rc != DA_OK) return rc;
         const uint64_t kd[2] = {576, kMapRows};
         const uint64_t ks[1] = {(uint64_t)p.k_row_stride * 2};
         const uint32_t kb[2] = {64, 64};
-        rc = make_tensor_map(p.k, 2, kd, ks, kb, true, bf16, &maps.v);
+        rc = make_tensor_map(p.k, 2, kd, ks, kb, true, bf16 ? 1 : 0, &maps.v);
         if (rc != DA_OK) return rc;
     }
     if (plan.shape == Shape::kMlaTc) {
@@ -572,27 +593,28 @@ int da_decode_fwd(const da_decode_args_t *a) {
         const uint64_t qd[3] = {576, (uint64_t)a->head_q, (uint64_t)a->batch};
         const uint64_t qs[2] = {576 * 2, (uint64_t)p.q_row_stride * 2};
         const uint32_t qb[3] = {64, (uint32_t)a->head_q, 1};  // head_q <= 128 rows
-        rc = make_tensor_map(p.q, 3, qd, qs, qb, true, bf16, &maps.k);
+        rc = make_tensor_map(p.q, 3, qd, qs, qb, true, bf16 ? 1 : 0, &maps.k);
         if (rc != DA_OK) return rc;
         const uint64_t kd[2] = {576, kMapRows};
         const uint64_t ks[1] = {(uint64_t)p.k_row_stride * 2};
         const uint32_t kb[2] = {64, (uint32_t)box_keys};
-        rc = make_tensor_map(p.k, 2, kd, ks, kb, true, bf16, &maps.v);
+        rc = make_tensor_map(p.k, 2, kd, ks, kb, true, bf16 ? 1 : 0, &maps.v);
         if (rc != DA_OK) return rc;
     }
     if (p.use_tmap) {
-        rc = make_kv_tensor_map(p.k, p.k_row_stride, p.head_k, (int)a->dim, box_keys, bf16, &maps.k);
+        const int kv_dt = fp8 ? 2 : (bf16 ? 1 : 0);
+        rc = make_kv_tensor_map(p.k, p.k_row_stride, p.head_k, (int)a->dim, box_keys, kv_dt, &maps.k);
         if (rc != DA_OK) return rc;
-        rc = make_kv_tensor_map(p.v, p.v_row_stride, p.head_k, (int)a->dim_v, box_keys, bf16, &maps.v);
+        rc = make_kv_tensor_map(p.v, p.v_row_stride, p.head_k, (int)a->dim_v, box_keys, kv_dt, &maps.v);
         if (rc != DA_OK) return rc;
     }
     cudaError_t e;
     if (g_prof_start) cudaEventRecord(g_prof_start, stream);
     switch (plan.shape) {
-        case Shape::kD64: e = launch_split_d64(bf16, plan.heads, p, maps, stream); break;
-        case Shape::kD96: e = launch_split_d96(bf16, plan.heads, p, maps, stream); break;
-        case Shape::kD128: e = launch_split_d128(bf16, plan.heads, p, maps, stream); break;
-        case Shape::kD256: e = launch_split_d256(bf16, plan.heads, p, maps, stream); break;
+        case Shape::kD64: e = launch_split_d64(bf16, fp8, plan.heads, p, maps, stream); break;
+        case Shape::kD96: e = launch_split_d96(bf16, fp8, plan.heads, p, maps, stream); break;
+        case Shape::kD128: e = launch_split_d128(bf16, fp8, plan.heads, p, maps, stream); break;
+        case Shape::kD256: e = launch_split_d256(bf16, fp8, plan.heads, p, maps, stream); break;
         case Shape::kMla: e = launch_split_mla_simt(bf16, plan.heads, p, maps, stream); break;
         case Shape::kGqaTc: e = launch_gqa_tc(bf16, (int)a->dim, p, tm_q, maps.k, maps.v, stream); break;
         case Shape::kMlaTc: e = launch_mla_tc(bf16, p, maps.k, maps.v, stream); break;
@@ -647,8 +669,9 @@ int da_decode_fwd_host(const da_decode_args_t *h) {
     if (total_k < 0) return fail(DA_ERR_INVALID_ARG, "cu_seq_k must not decrease");
     auto up = [](size_t x) { return (x + 255) / 256 * 256; };
     const size_t q_b = up((size_t)h->batch * h->head_q * h->dim * 2);
-    const size_t k_b = up((size_t)total_k * h->head_k * h->dim * 2);
-    const size_t v_b = h->v ? up((size_t)total_k * h->head_k * h->dim_v * 2) : 0;
+    const size_t kv_eb = h->kv_dtype == DA_KV_FP8_E4M3 ? 1 : 2;  // bytes per cache element
+    const size_t k_b = up((size_t)total_k * h->head_k * h->dim * kv_eb);
+    const size_t v_b = h->v ? up((size_t)total_k * h->head_k * h->dim_v * kv_eb) : 0;
     const size_t o_b = up((size_t)h->batch * h->head_q * h->dim_v * 2);
     const size_t cu_b = up((size_t)(h->batch + 1) * 4);
     const size_t lse_b = h->lse ? up((size_t)h->batch * h->head_q * 4) : 0;
@@ -680,9 +703,9 @@ int da_decode_fwd_host(const da_decode_args_t *h) {
     if (e == cudaSuccess)
         e = cudaMemcpyAsync(dq, h->q, (size_t)h->batch * h->head_q * h->dim * 2, cudaMemcpyHostToDevice, stream);
     if (e == cudaSuccess)
-        e = cudaMemcpyAsync(dk, h->k, (size_t)total_k * h->head_k * h->dim * 2, cudaMemcpyHostToDevice, stream);
+        e = cudaMemcpyAsync(dk, h->k, (size_t)total_k * h->head_k * h->dim * kv_eb, cudaMemcpyHostToDevice, stream);
     if (e == cudaSuccess && h->v)
-        e = cudaMemcpyAsync(dv, h->v, (size_t)total_k * h->head_k * h->dim_v * 2, cudaMemcpyHostToDevice, stream);
+        e = cudaMemcpyAsync(dv, h->v, (size_t)total_k * h->head_k * h->dim_v * kv_eb, cudaMemcpyHostToDevice, stream);
     if (e != cudaSuccess) return fail(DA_ERR_CUDA, "host-to-device copy: %s", cudaGetErrorString(e));
     rc = da_decode_fwd(&d);
     if (rc != DA_OK) return rc;

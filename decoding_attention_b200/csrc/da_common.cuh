@@ -5,6 +5,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -46,7 +47,8 @@ struct SplitParams {
     int chunk_keys;    // keys per split (multiple of the tile)
     int is_alibi;
     int use_tmap;      // full tiles are fetched with one tiled TMA copy through the tensor maps
-    float scale_log2;  // softmax scale * log2(e)
+    float scale_log2;  // softmax scale * log2(e) (times the K scale of an FP8 cache)
+    float out_scale;   // factor on the output: the V scale of an FP8 cache, else 1
 };
 
 // Has an earlier CTA of this very launch given up a bounded wait?  (Later launches carry another id
@@ -223,6 +225,28 @@ __device__ __forceinline__ void unpack8<__nv_bfloat16>(const uint4 &raw, float (
     for (int i = 0; i < 4; ++i) {
         f[2 * i] = __uint_as_float(w[i] << 16);
         f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+// Eight FP8 e4m3 values (8 bytes) to fp32.
+__device__ __forceinline__ void unpack8_e4m3(const uint2 &raw, float (&f)[8]) {
+    const uint32_t w[2] = {raw.x, raw.y};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __nv_fp8x2_storage_t pair = (__nv_fp8x2_storage_t)((w[i >> 1] >> ((i & 1) * 16)) & 0xffffu);
+        const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(pair, __NV_E4M3);
+        const float2 t = __half22float2(*reinterpret_cast<const __half2 *>(&h));
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+// One lane's chunk of a K or V row in shared memory: eight elements of the 16-bit type T, or eight FP8 bytes.
+template <typename T, bool FP8>
+__device__ __forceinline__ void load_chunk8(const uint8_t *ptr, float (&f)[8]) {
+    if (FP8) {
+        unpack8_e4m3(*reinterpret_cast<const uint2 *>(ptr), f);
+    } else {
+        unpack8<T>(*reinterpret_cast<const uint4 *>(ptr), f);
     }
 }
 

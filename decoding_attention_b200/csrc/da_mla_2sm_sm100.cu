@@ -201,6 +201,15 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             const int key0 = k_begin + t * kTile + (int)rank * kHalf;  // this CTA's first key of the tile
             const int rows = max(0, min(kHalf, k_end - key0));
             const size_t tok0 = rows > 0 ? kv_tile_row(p, b, seq_begin, key0) : 0;
+#ifdef DA_MLA2_PREFETCH
+            {   // ask L2 for this CTA's rows of a later tile as one contiguous run (packed rows only)
+                const int kp = key0 + DA_MLA2_PREFETCH * kTile;
+                if (lane == 0 && p.k_row_stride == kDim && !p.block_table && kp + kHalf <= k_end) {
+                    const T *src = k_g + ((size_t)seq_begin + kp) * kDim;
+                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(kHalf * kDim * 2) : "memory");
+                }
+            }
+#endif
             for (int j = 0; j < kBlocks && ok; ++j) {
                 if (round > 0) ok = mbar_wait(&a_empty[slot], (round & 1u) ^ 1u, abort_flag);
                 if (!ok) break;

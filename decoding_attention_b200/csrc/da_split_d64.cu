@@ -6,22 +6,24 @@
 namespace da {
 namespace {
 // lanes per key row, keys per lane-group and tile, consumer warps, pipeline stages
-template <typename T, int G, int KPT>
-using Cfg = SplitCfg<T, 64, 64, 8, G, KPT, 4, 4, false>;
+template <typename T, int G, int KPT, bool FP8 = false>
+using Cfg = SplitCfg<T, 64, 64, 8, G, KPT, 4, 4, false, 1, FP8>;
 
-template <typename T>
+template <typename T, bool FP8>
 cudaError_t launch_t(int heads, const SplitParams &p, const KvMaps &m, cudaStream_t s) {
     switch (heads) {
-        case 1: return launch_split<Cfg<T, 1, 4>>(p, m.k, m.v, s);
-        case 2: return launch_split<Cfg<T, 2, 4>>(p, m.k, m.v, s);
-        case 4: return launch_split<Cfg<T, 4, 4>>(p, m.k, m.v, s);
+        case 1: return launch_split<Cfg<T, 1, 4, FP8>>(p, m.k, m.v, s);
+        case 2: return launch_split<Cfg<T, 2, 4, FP8>>(p, m.k, m.v, s);
+        case 4: return launch_split<Cfg<T, 4, 4, FP8>>(p, m.k, m.v, s);
         default: return cudaErrorInvalidValue;
     }
 }
 }  // namespace
 
-cudaError_t launch_split_d64(bool bf16, int heads, const SplitParams &p, const KvMaps &m, cudaStream_t s) {
-    return bf16 ? launch_t<__nv_bfloat16>(heads, p, m, s) : launch_t<__half>(heads, p, m, s);
+// fp8: K and V are FP8 e4m3 bytes (q and o stay 16-bit)
+cudaError_t launch_split_d64(bool bf16, bool fp8, int heads, const SplitParams &p, const KvMaps &m, cudaStream_t s) {
+    if (fp8) return bf16 ? launch_t<__nv_bfloat16, true>(heads, p, m, s) : launch_t<__half, true>(heads, p, m, s);
+    return bf16 ? launch_t<__nv_bfloat16, false>(heads, p, m, s) : launch_t<__half, false>(heads, p, m, s);
 }
 
 SplitVariantInfo split_info_d64(int heads) {

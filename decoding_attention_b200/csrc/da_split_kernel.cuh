@@ -22,9 +22,14 @@
 
 namespace da {
 
-template <typename T_, int D_, int DV_, int LANES_, int G_, int KPT_, int NWARPS_, int STAGES_, bool MLA_, int MINB_ = 1>
+// FP8_: K and V hold one-byte FP8 e4m3 values (q and o keep the 16-bit type T); a lane then owns 8-byte chunks.
+template <typename T_, int D_, int DV_, int LANES_, int G_, int KPT_, int NWARPS_, int STAGES_, bool MLA_, int MINB_ = 1,
+          bool FP8_ = false>
 struct SplitCfg {
     using T = T_;
+    static constexpr bool FP8 = FP8_;
+    static constexpr int KV_BYTES = FP8_ ? 1 : 2;      // bytes per K / V element
+    static constexpr int CHUNK_BYTES = 8 * KV_BYTES;   // eight elements: what one lane reads at a time
     static constexpr int D = D_, DV = DV_, LANES = LANES_, G = G_, KPT = KPT_, NWARPS = NWARPS_, STAGES = STAGES_;
     static constexpr bool MLA = MLA_;
     static constexpr int MINB = MINB_;             // resident CTAs per SM the register budget must allow              // V is the first DV elements of each K row
@@ -36,7 +41,7 @@ struct SplitCfg {
     static constexpr int NV = KPT * G;             // scores per group per tile
     static constexpr int RV = NV >= LANES ? NV / LANES : 1;   // scores a lane holds after the reduce-scatter
     static constexpr int REP = NV >= LANES ? 1 : LANES / NV;  // lanes holding the same score
-    static constexpr int K_ROW_BYTES = D * 2, V_ROW_BYTES = DV * 2;
+    static constexpr int K_ROW_BYTES = D * KV_BYTES, V_ROW_BYTES = DV * KV_BYTES;
     static constexpr int K_TILE_BYTES = TILE * K_ROW_BYTES;
     static constexpr int V_TILE_BYTES = MLA ? 0 : TILE * V_ROW_BYTES;
     static constexpr int THREADS = (NWARPS + 1) * 32;
@@ -54,6 +59,7 @@ struct SplitCfg {
     static_assert((LANES & (LANES - 1)) == 0 && LANES <= 32, "LANES must be a power of two");
     static_assert((NV & (NV - 1)) == 0, "KPT*G must be a power of two");
     static_assert(!MLA || DV <= D, "latent-KV: V is a prefix of the K row");
+    static_assert(K_ROW_BYTES % 16 == 0 && V_ROW_BYTES % 16 == 0, "rows are copied in 16-byte units");
 };
 
 constexpr int ilog2(int x) { return x <= 1 ? 0 : 1 + ilog2(x / 2); }
@@ -210,8 +216,9 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
 
     if (warp == C::NWARPS) {
         // ---------------- producer warp ----------------
-        const T *kg = reinterpret_cast<const T *>(p.k) + (size_t)hk * D;
-        const T *vg = reinterpret_cast<const T *>(p.v) + (size_t)hk * (C::MLA ? D : DV);
+        constexpr int EB = C::KV_BYTES;  // element size of the cache
+        const uint8_t *kg = reinterpret_cast<const uint8_t *>(p.k) + (size_t)hk * D * EB;
+        const uint8_t *vg = reinterpret_cast<const uint8_t *>(p.v) + (size_t)hk * (C::MLA ? D : DV) * EB;
         if (p.use_tmap && lane == 0) {
             tma_prefetch_desc(&tm_k);
             if (!C::MLA) tma_prefetch_desc(&tm_v);
@@ -236,11 +243,11 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
             armed_k = t + 1;
             if (short_pages) {
                 load_tile_short_pages(p.block_table, p.block_table_stride, p.page_shift, b, key0, rows, TILE, whole,
-                                      ks + st * C::K_TILE_BYTES, C::K_ROW_BYTES, &tm_k, hk, reinterpret_cast<const uint8_t *>(kg),
-                                      p.k_row_stride * (long long)sizeof(T), &full_k[st], lane);
+                                      ks + st * C::K_TILE_BYTES, C::K_ROW_BYTES, &tm_k, hk, kg,
+                                      p.k_row_stride * (long long)EB, &full_k[st], lane);
             } else if (!whole) {
                 for (int r = lane; r < rows; r += 32) {
-                    bulk_copy_g2s(ks + st * C::K_TILE_BYTES + r * C::K_ROW_BYTES, kg + (tok0 + r) * p.k_row_stride,
+                    bulk_copy_g2s(ks + st * C::K_TILE_BYTES + r * C::K_ROW_BYTES, kg + (tok0 + r) * p.k_row_stride * EB,
                                   C::K_ROW_BYTES, &full_k[st]);
                 }
             }
@@ -255,12 +262,12 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
                 armed_v = t + 1;
                 if (short_pages) {
                     load_tile_short_pages(p.block_table, p.block_table_stride, p.page_shift, b, key0, rows, TILE, whole,
-                                          vs + st * C::V_TILE_BYTES, C::V_ROW_BYTES, &tm_v, hk,
-                                          reinterpret_cast<const uint8_t *>(vg), p.v_row_stride * (long long)sizeof(T), &full_v[st], lane);
+                                          vs + st * C::V_TILE_BYTES, C::V_ROW_BYTES, &tm_v, hk, vg,
+                                          p.v_row_stride * (long long)EB, &full_v[st], lane);
                 } else if (!whole) {
                     for (int r = lane; r < rows; r += 32) {
                         bulk_copy_g2s(vs + st * C::V_TILE_BYTES + r * C::V_ROW_BYTES,
-                                      vg + (tok0 + r) * p.v_row_stride, C::V_ROW_BYTES, &full_v[st]);
+                                      vg + (tok0 + r) * p.v_row_stride * EB, C::V_ROW_BYTES, &full_v[st]);
                     }
                 }
             }
@@ -343,9 +350,8 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
             const int kl = (i ^ slot_perm) * NG + gi;  // key slot in the tile (register slot i)
 #pragma unroll
             for (int n = 0; n < NCH; ++n) {
-                const uint4 raw = *reinterpret_cast<const uint4 *>(kt + kl * C::K_ROW_BYTES + (c + n * LANES) * 16);
                 float kf[8];
-                unpack8<T>(raw, kf);
+                load_chunk8<T, C::FP8>(kt + kl * C::K_ROW_BYTES + (c + n * LANES) * C::CHUNK_BYTES, kf);
 #pragma unroll
                 for (int g = 0; g < G; ++g) {
 #pragma unroll
@@ -426,9 +432,8 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
                 for (int g = 0; g < G; ++g) pg[g] = p_grp[i * G + g];
 #pragma unroll
                 for (int n = 0; n < NCHV; ++n) {
-                    const uint4 raw = *reinterpret_cast<const uint4 *>(vt + kl * VROW + (c + n * LANES) * 16);
                     float vf[8];
-                    unpack8<T>(raw, vf);
+                    load_chunk8<T, C::FP8>(vt + kl * VROW + (c + n * LANES) * C::CHUNK_BYTES, vf);
 #pragma unroll
                     for (int g = 0; g < G; ++g) {
 #pragma unroll
@@ -487,7 +492,7 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
             l = fmaf(red_l[x * G + g], w, l);
             o = fmaf(red_o[(size_t)(x * G + g) * DV + d], w, o);
         }
-        const float out = o / l;
+        const float out = o / l * p.out_scale;
         const int h = h0 + g;
         const float lse = (mx + log2f(l)) * kLn2;
         if (p.num_splits == 1) {

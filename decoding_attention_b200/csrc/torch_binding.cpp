@@ -3,7 +3,8 @@
 //
 //   fwd(q, k, v_, o_, cu_seq_k, max_seq_k, dim_v, is_alibi) -> o      same positional signature and
 //       checks as the reference's dmha_fwd (decoding_torch.cpp:19-80); v_ = None selects MLA.
-//   dmha_fwd(q, k, v, cu_seq_k, max_seq_k, is_alibi, softmax_scale=None, out=None, return_lse=False)
+//   dmha_fwd(q, k, v, cu_seq_k, max_seq_k, is_alibi, softmax_scale=None, out=None, return_lse=False, k_scale=1, v_scale=1)
+//       (k, v may be torch.float8_e4m3fn: an FP8 cache standing for k * k_scale, v * v_scale)
 //   dmla_fwd(q, kv, cu_seq_k, max_seq_k, dim_v=512, is_alibi=False, softmax_scale=None, out=None, return_lse=False)
 //       the two named entry points with an explicit softmax scale; their defaults reproduce fwd().
 //   merge_partials(part_o, part_lse, out_dtype) -> (o, lse)           LSE merge of key-range shards.
@@ -37,12 +38,15 @@ struct Outputs {
 Outputs run(const at::Tensor &q, const at::Tensor &k, const std::optional<at::Tensor> &v_,
             const std::optional<at::Tensor> &o_, const at::Tensor &cu_seq_k, int64_t max_seq_k, int64_t dim_v,
             bool is_alibi, std::optional<double> softmax_scale, bool want_lse, const at::Tensor *block_table = nullptr,
-            int64_t page_size = 0) {
+            int64_t page_size = 0, double k_scale = 1.0, double v_scale = 1.0) {
     auto q_dtype = q.dtype();
     TORCH_CHECK(q_dtype == torch::kFloat16 || q_dtype == torch::kBFloat16,
                 "Decoding-Attention only support FP16 and BF16 data type");
     const bool is_bf16 = q_dtype == torch::kBFloat16;
-    TORCH_CHECK(k.dtype() == q_dtype, "query and key must have the same dtype");
+    // An FP8 e4m3 cache (k and v both) is an extension; the reference requires the dtype of q
+    // (csrc/torch/decoding_torch.cpp:28, :57).
+    const bool fp8_cache = k.scalar_type() == at::kFloat8_e4m3fn;
+    TORCH_CHECK(fp8_cache || k.dtype() == q_dtype, "query and key must have the same dtype");
     TORCH_CHECK(cu_seq_k.dtype() == torch::kInt32, "cu_seq_k must have dtype int32");
 
     DA_CHECK_DEVICE(q);
@@ -87,7 +91,7 @@ Outputs run(const at::Tensor &q, const at::Tensor &k, const std::optional<at::Te
 
     if (v_.has_value()) {
         const at::Tensor &v = v_.value();
-        TORCH_CHECK(v.dtype() == q_dtype, "query and value must have the same dtype");
+        TORCH_CHECK(v.dtype() == k.dtype(), fp8_cache ? "key and value must both be FP8" : "query and value must have the same dtype");
         DA_CHECK_DEVICE(v);
         TORCH_CHECK(v.device() == q.device(), "all tensors must be on one device");
         TORCH_CHECK(v.stride(-1) == 1, "value must have contiguous last dimension");
@@ -125,6 +129,12 @@ Outputs run(const at::Tensor &q, const at::Tensor &k, const std::optional<at::Te
     a.dim_v = dim_v;
     a.softmax_scale = softmax_scale.has_value() ? (float)softmax_scale.value() : 0.0f;
     a.stream = stream;
+    if (fp8_cache) {
+        TORCH_CHECK(v_.has_value(), "an FP8 cache needs a value tensor");
+        a.kv_dtype = DA_KV_FP8_E4M3;
+        a.k_scale = (float)k_scale;
+        a.v_scale = (float)v_scale;
+    }
     if (block_table) {
         TORCH_CHECK(block_table->dtype() == torch::kInt32, "block_table must have dtype int32");
         TORCH_CHECK(block_table->is_cuda() && block_table->device() == q.device(), "all tensors must be on one device");
@@ -158,9 +168,10 @@ at::Tensor fwd(const at::Tensor &q, const at::Tensor &k, std::optional<at::Tenso
 
 pybind11::object dmha_fwd(const at::Tensor &q, const at::Tensor &k, const at::Tensor &v, const at::Tensor &cu_seq_k,
                           int64_t max_seq_k, bool is_alibi, std::optional<double> softmax_scale,
-                          std::optional<at::Tensor> out, bool return_lse) {
+                          std::optional<at::Tensor> out, bool return_lse, double k_scale, double v_scale) {
     TORCH_CHECK(v.dim() == 3, "value must be 3-D");
-    Outputs r = run(q, k, v, out, cu_seq_k, max_seq_k, v.size(2), is_alibi, softmax_scale, return_lse);
+    Outputs r = run(q, k, v, out, cu_seq_k, max_seq_k, v.size(2), is_alibi, softmax_scale, return_lse, nullptr, 0,
+                    k_scale, v_scale);
     if (return_lse) return pybind11::cast(std::make_tuple(r.o, r.lse));
     return pybind11::cast(r.o);
 }
@@ -234,7 +245,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("max_seq_k"), py::arg("dim_v"), py::arg("is_alibi"));
     m.def("dmha_fwd", &dmha_fwd, "MHA/GQA/MQA decode", py::arg("q"), py::arg("k"), py::arg("v"), py::arg("cu_seq_k"),
           py::arg("max_seq_k"), py::arg("is_alibi") = false, py::arg("softmax_scale") = py::none(),
-          py::arg("out") = py::none(), py::arg("return_lse") = false);
+          py::arg("out") = py::none(), py::arg("return_lse") = false, py::arg("k_scale") = 1.0, py::arg("v_scale") = 1.0);
     m.def("dmla_fwd", &dmla_fwd, "MLA decode (latent KV)", py::arg("q"), py::arg("kv"), py::arg("cu_seq_k"),
           py::arg("max_seq_k"), py::arg("dim_v") = 512, py::arg("is_alibi") = false,
           py::arg("softmax_scale") = py::none(), py::arg("out") = py::none(), py::arg("return_lse") = false);

@@ -37,10 +37,13 @@ def decoding_attn_fwd(q, k, v, cu_seq_k, max_seq_k, dim_v, is_alibi, *, softmax_
     return decoding_attn_cuda.dmha_fwd(q, k, v, cu_seq_k, max_seq_k, is_alibi, softmax_scale)
 
 
-def dmha_fwd(q, k, v, cu_seq_k, max_seq_k, is_alibi=False, softmax_scale=None, out=None, return_lse=False):
-    """MHA / GQA / MQA decode attention; ``return_lse`` adds the fp32 natural-log LSE [batch, head_q]."""
+def dmha_fwd(q, k, v, cu_seq_k, max_seq_k, is_alibi=False, softmax_scale=None, out=None, return_lse=False,
+             k_scale=1.0, v_scale=1.0):
+    """MHA / GQA / MQA decode attention; ``return_lse`` adds the fp32 natural-log LSE [batch, head_q].
+    ``k`` / ``v`` may be an FP8 cache (torch.float8_e4m3fn) standing for ``k * k_scale`` / ``v * v_scale``."""
     q, k, v = [maybe_contiguous(x) for x in (q, k, v)]
-    return decoding_attn_cuda.dmha_fwd(q, k, v, cu_seq_k, max_seq_k, is_alibi, softmax_scale, out, return_lse)
+    return decoding_attn_cuda.dmha_fwd(q, k, v, cu_seq_k, max_seq_k, is_alibi, softmax_scale, out, return_lse,
+                                       k_scale, v_scale)
 
 
 def dmla_fwd(q, kv, cu_seq_k, max_seq_k, dim_v=512, softmax_scale=None, out=None, return_lse=False, is_alibi=False):

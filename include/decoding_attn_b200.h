@@ -82,8 +82,18 @@ typedef struct da_decode_args {
     const int32_t *block_table; /* device [batch, block_table_stride] */
     int64_t block_table_stride; /* elements per row, >= ceil(longest sequence / page_size) */
     int32_t page_size;
-    int32_t reserved1;
+
+    /* Quantised cache (optional).  kv_dtype 0: k and v hold the type of q (the reference's only case);
+     * DA_KV_FP8_E4M3: k and v hold one-byte FP8 e4m3 values and stand for k * k_scale and v * v_scale
+     * (one scale per tensor; <= 0 selects 1).  q, o and all arithmetic stay as they are; strides and
+     * dims still count elements.  Supported with v given and (dim, dim_v) one of (64,64) (96,96)
+     * (128,128) (256,256); the latent-KV shape returns DA_ERR_UNSUPPORTED.  The reference lists KV-cache
+     * quantisation as not done (README.md:154-156). */
+    int32_t kv_dtype;
+    float k_scale, v_scale;
 } da_decode_args_t;
+
+enum { DA_KV_SAME_AS_Q = 0, DA_KV_FP8_E4M3 = 1 };
 
 /* Runs decode attention.  Stands in for decoding_attn() (csrc/ops/decoding_attn.h:29-30,
  * csrc/ops/decoding_attn.cpp:70-76) and everything below it: run_dmha_fwd / DA_FP16_SWITCH /

@@ -251,8 +251,9 @@ def to_pages(k, v, cu, page_size, seed):
     blocks = [(n + page_size - 1) // page_size for n in lens]
     n_pages = sum(blocks) + 2
     order = torch.randperm(n_pages, generator=g).tolist()
-    k_pool = torch.full((n_pages, page_size) + tuple(k.shape[1:]), float("nan"), dtype=k.dtype)
-    v_pool = torch.full((n_pages, page_size) + tuple(v.shape[1:]), float("nan"), dtype=v.dtype) if v is not None else None
+    fill = 0x7F if k.dtype == torch.uint8 else float("nan")  # 0x7f is NaN in FP8 e4m3 (pools passed as raw bytes)
+    k_pool = torch.full((n_pages, page_size) + tuple(k.shape[1:]), fill, dtype=k.dtype)
+    v_pool = torch.full((n_pages, page_size) + tuple(v.shape[1:]), fill, dtype=v.dtype) if v is not None else None
     table = torch.zeros(len(lens), max(max(blocks), 1) + 1, dtype=torch.int32)
     nxt = 0
     for b, n in enumerate(lens):
@@ -376,3 +377,70 @@ def test_cuda_graph_replay_with_launch_order_and_overlapped_launches(native_lib,
         torch.cuda.synchronize()
         assert native_lib.device_status() == native_lib.DA_OK
         assert_close(o, expect, "graph replay with launch order")
+
+
+def quantise_e4m3(x, scale):
+    """(FP8 bytes, dequantised tensor in x's dtype): x / scale rounded to e4m3.  Every e4m3 value is exact in fp16 and
+    bf16 and the scales used here are powers of two, so the dequantised cache the oracle sees is exactly what the
+    kernel reconstructs."""
+    x8 = (x.float() / scale).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+    return x8, (x8.float() * scale).to(x.dtype)
+
+
+FP8_CASES = [
+    # dtype, head_q, head_k, dim, lens, alibi, splits, k_scale, v_scale
+    (torch.bfloat16, 32, 8, 128, [700, 64, 1, 129, 0], False, 0, 1.0, 1.0),
+    (torch.float16, 32, 8, 128, [2100, 333], True, 3, 0.5, 0.25),
+    (torch.float16, 32, 32, 128, [513], False, 0, 0.125, 2.0),
+    (torch.bfloat16, 16, 4, 64, [333, 1000], False, 2, 0.5, 0.5),
+    (torch.float16, 12, 4, 96, [257, 31], True, 0, 0.25, 1.0),
+    (torch.bfloat16, 8, 2, 256, [100, 400], False, 0, 0.5, 0.5),
+    (torch.float16, 32, 1, 128, [300, 65], True, 0, 0.25, 0.25),   # a group of 32: eight 4-head chunks on the CUDA-core kernel
+]
+
+
+@pytest.mark.parametrize("dt,hq,hk,d,lens,alibi,splits,ks,vs", FP8_CASES)
+def test_fp8_kv_cache(native_lib, oracle, dt, hq, hk, d, lens, alibi, splits, ks, vs):
+    """FP8 e4m3 K / V with per-tensor scales: the oracle runs on the dequantised cache (quantisation error is the
+    caller's business, not the kernel's), so the usual tolerance applies."""
+    w = synth.Workload(f"fp8_{d}_{hq}_{hk}", dt, hq, hk, d, d, lens, is_alibi=alibi, dist="normal", scale=0.5, seed=81)
+    q, k, v, cu = w.make("cpu")
+    k8, k_deq = quantise_e4m3(k, ks)
+    v8, v_deq = quantise_e4m3(v, vs)
+    expect, lse_e = oracle.attn_cpu(q, k_deq, v_deq, cu, dim_v=d, is_alibi=alibi, return_lse=True)
+    o = torch.full((len(lens), hq, d), float("nan"), dtype=dt, device=DEV)
+    lse = torch.empty(len(lens), hq, dtype=torch.float32, device=DEV)
+    args = native_lib.make_args(q.to(DEV), k8.to(DEV), v8.to(DEV), o, cu.to(DEV), max(w.max_seq_k, 1), d, is_alibi=alibi,
+                                lse=lse, num_splits=splits, k_scale=ks, v_scale=vs)
+    before = native_lib.launch_count()
+    native_lib.decode_fwd(args)
+    torch.cuda.synchronize()
+    assert native_lib.launch_count() > before and native_lib.device_status() == native_lib.DA_OK
+    assert_close(o, expect, w.name)
+    fin = torch.isfinite(lse_e)
+    assert (lse.cpu()[fin] - lse_e[fin]).abs().max().item() <= 2e-3
+
+
+def test_fp8_kv_cache_paged_and_errors(native_lib, oracle):
+    w = synth.Workload("fp8_paged", torch.bfloat16, 32, 8, 128, 128, [700, 64, 130], dist="normal", scale=0.5, seed=82)
+    q, k, v, cu = w.make("cpu")
+    k8, k_deq = quantise_e4m3(k, 0.5)
+    v8, v_deq = quantise_e4m3(v, 0.5)
+    expect = oracle.attn_cpu(q, k_deq, v_deq, cu)
+    for page in (64, 16):
+        kp, vp, table = to_pages(k8.view(torch.uint8), v8.view(torch.uint8), cu, page, seed=5)
+        kp, vp = kp.view(torch.float8_e4m3fn), vp.view(torch.float8_e4m3fn)  # rows no sequence owns hold NaN bytes
+        o = torch.full((3, 32, 128), float("nan"), dtype=w.dtype, device=DEV)
+        args = native_lib.make_args(q.to(DEV), kp.to(DEV), vp.to(DEV), o, cu.to(DEV), w.max_seq_k, 128, block_table=table.to(DEV),
+                                    page_size=page, k_scale=0.5, v_scale=0.5)
+        native_lib.decode_fwd(args)
+        torch.cuda.synchronize()
+        assert_close(o, expect, f"fp8 paged {page}")
+    # the latent-KV shape has no FP8 path
+    wm = synth.Workload("fp8_mla", torch.bfloat16, 128, 1, 576, 512, [64], dist="normal", scale=0.3, mla=True, seed=83)
+    q, kv, _, cu = wm.make("cpu")
+    kv8 = kv.float().to(torch.float8_e4m3fn)
+    o = torch.empty(1, 128, 512, dtype=wm.dtype, device=DEV)
+    with pytest.raises(native_lib.DecodingAttnError) as e:
+        native_lib.decode_fwd(native_lib.make_args(q.to(DEV), kv8.to(DEV), None, o, cu.to(DEV), 64, 512))
+    assert e.value.status == native_lib.DA_ERR_UNSUPPORTED
