@@ -13,9 +13,15 @@
 // V columns (dims 256c..256c+255) of all 128 keys for P.V.  Nothing is computed twice, every K row is
 // read by one CTA for S, and the 128 x 512 fp32 output fits because a CTA's 64 x 512 share is 128
 // TMEM lanes x 256 columns.  What a CTA reads per tile: its 64 keys x 576 dims for S (nine 8 KB
-// blocks streamed through a ring, each released by a tcgen05.commit right after its four MMAs) and
-// 128 keys x 256 dims for P.V (two 32 KB half-tile slots), 136 KB against 2 x 72 KB for a kernel
-// whose two CTAs work apart; the second reader of a row hits L2.
+// blocks streamed by TMA through a ring of nine slots, each released by a tcgen05.commit right after its
+// four MMAs) and 128 keys x 256 dims for P.V (two 32 KB half-tile slots, cp.async), 136 KB against
+// 2 x 72 KB for a kernel whose two CTAs work apart; the second reader of a row hits L2.
+// What bounds it (measured, batch 128 x 4096 keys, 190 us): neither the tensor pipe (2 176 cycles of
+// MMAs per tile) nor DRAM (52 %), but the time a ring slot takes to come back -- one SM's TMA engine
+// writes a 128-byte row every ~5 cycles (330 cycles per block, 2 970 per tile) and a refill can only be
+// asked for once the slot has been consumed, so a tile costs about one memory latency plus the TMA
+// time, 4 900 cycles on an idle GPU and 5 500 under load.  A second tile of ring slots does not fit
+// beside Q (40 KB), P (16 KB) and the V slots (96 KB).
 //
 // TMEM columns per CTA: S0 | S1 (64 each: lanes 0-63 keys 0-63 of the tile, lanes 64-127 keys 64-127,
 // rows = this CTA's heads) | O (256: lanes 0-63 dims 0-255, lanes 64-127 dims 256-511) | Q (4 x 32:
@@ -201,15 +207,6 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             const int key0 = k_begin + t * kTile + (int)rank * kHalf;  // this CTA's first key of the tile
             const int rows = max(0, min(kHalf, k_end - key0));
             const size_t tok0 = rows > 0 ? kv_tile_row(p, b, seq_begin, key0) : 0;
-#ifdef DA_MLA2_PREFETCH
-            {   // ask L2 for this CTA's rows of a later tile as one contiguous run (packed rows only)
-                const int kp = key0 + DA_MLA2_PREFETCH * kTile;
-                if (lane == 0 && p.k_row_stride == kDim && !p.block_table && kp + kHalf <= k_end) {
-                    const T *src = k_g + ((size_t)seq_begin + kp) * kDim;
-                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(kHalf * kDim * 2) : "memory");
-                }
-            }
-#endif
             for (int j = 0; j < kBlocks && ok; ++j) {
                 if (round > 0) ok = mbar_wait(&a_empty[slot], (round & 1u) ^ 1u, abort_flag);
                 if (!ok) break;
