@@ -278,8 +278,9 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
             return fail(DA_ERR_UNSUPPORTED, "an FP8 cache is supported for (dim, dim_v) (64,64) (96,96) (128,128) (256,256) with v given");
         }
     } else if (shape == Shape::kMla && mla_on_tensor_cores(a)) {
-        // SM pairs (cta_group::2) unless the cache is paged in pages shorter than the 64 keys one CTA stages at a time
-        shape = (!a.block_table || a.page_size >= 64) && !env_overrides().mla_1sm ? Shape::kMla2Sm : Shape::kMlaTc;
+        // SM pairs (cta_group::2) unless the cache is paged in pages shorter than the keys one CTA stages at a time
+        const int half_tile = split_info_mla_2sm().tile_keys / 2;
+        shape = (!a.block_table || a.page_size >= half_tile) && !env_overrides().mla_1sm ? Shape::kMla2Sm : Shape::kMlaTc;
     }
     if (a.kv_dtype != DA_KV_FP8_E4M3 && (shape == Shape::kD64 || shape == Shape::kD128 || shape == Shape::kD256) &&
         gqa_on_tensor_cores(a)) {
@@ -575,7 +576,7 @@ int da_decode_fwd(const da_decode_args_t *a) {
     }
     if (plan.shape == Shape::kMla2Sm) {
         // q as [batch][head_q][576] in boxes {64, min(64, head_q), 1} (one CTA's heads; rows past head_q read as
-        // zeros); the latent cache as [rows][576] in boxes {64, 64 keys}; both 128-byte-swizzled.
+        // zeros); the latent cache as [rows][576] in boxes {64, half a tile of keys}; both 128-byte-swizzled.
         const uint64_t qd[3] = {576, (uint64_t)a->head_q, (uint64_t)a->batch};
         const uint64_t qs[2] = {576 * 2, (uint64_t)p.q_row_stride * 2};
         const uint32_t qb[3] = {64, (uint32_t)(a->head_q < 64 ? a->head_q : 64), 1};
@@ -583,7 +584,7 @@ int da_decode_fwd(const da_decode_args_t *a) {
         if (rc != DA_OK) return rc;
         const uint64_t kd[2] = {576, kMapRows};
         const uint64_t ks[1] = {(uint64_t)p.k_row_stride * 2};
-        const uint32_t kb[2] = {64, 64};
+        const uint32_t kb[2] = {64, (uint32_t)(plan.tile_keys / 2)};  // one CTA's keys of a tile
         rc = make_tensor_map(p.k, 2, kd, ks, kb, true, bf16 ? 1 : 0, &maps.v);
         if (rc != DA_OK) return rc;
     }

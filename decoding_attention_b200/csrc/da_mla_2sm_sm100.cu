@@ -49,27 +49,43 @@ constexpr int kHeads = 128;        // M of both contractions (pair)
 constexpr int kRows = 64;          // heads per CTA
 constexpr int kDim = 576;
 constexpr int kDimV = 512;
-constexpr int kTile = 128;         // keys per pair tile
-constexpr int kHalf = 64;          // keys per CTA in S / per V half-tile slot
+// Keys per pair tile.  128 is what ships; 64 (twice as many ring slots and V slots of half the size, six Q blocks in
+// TMEM) is kept compiling because it is the obvious next thing to try and was measured: 307 us against 187 us
+// at batch 128 x 4096 keys.  A tile's cost is mostly fixed -- the softmax hand-over between S and P.V takes about
+// two thousand cycles whatever the tile holds -- so halving the tile doubles the number of hand-overs.
+#ifndef DA_MLA2_TILE
+#define DA_MLA2_TILE 128
+#endif
+constexpr int kTile = DA_MLA2_TILE; // keys per pair tile (64 or 128)
+constexpr int kHalf = kTile / 2;   // keys per CTA in S / per V half-tile slot
 constexpr int kBlocks = kDim / 64; // 64-element (128-byte) column blocks of a row
 constexpr int kVBlocks = 4;        // V blocks per CTA (256 of the 512 output dims)
 #ifndef DA_MLA2_QTMEM
+#if DA_MLA2_TILE == 64
+#define DA_MLA2_QTMEM 6
+#define DA_MLA2_ASLOTS 18
+#define DA_MLA2_VSLOTS 7
+#define DA_MLA2_PBUFS 2
+#else
 #define DA_MLA2_QTMEM 4
 #define DA_MLA2_ASLOTS 9
 #define DA_MLA2_VSLOTS 3
 #define DA_MLA2_PBUFS 1
 #endif
-constexpr int kQTmemBlocks = DA_MLA2_QTMEM;    // Q blocks 0..3 live in TMEM
+#endif
+constexpr int kQTmemBlocks = DA_MLA2_QTMEM;    // Q blocks 0 .. kQTmemBlocks-1 live in TMEM
 constexpr int kQSmemBlocks = kBlocks - kQTmemBlocks;
-constexpr int kBlockBytes = 64 * 128;  // [64 rows x 64 elements], 128-byte swizzle: a Q, K or P block
+constexpr int kQBlockBytes = 64 * 128;     // [64 heads x 64 dims], 128-byte swizzle: a Q block (and a 64-key block of P)
+constexpr int kKBlockBytes = kHalf * 128;  // [kHalf keys x 64 dims]: a K block of one CTA
 constexpr int kASlots = DA_MLA2_ASLOTS;         // ring of TMA-streamed K blocks
 constexpr int kVSlots = DA_MLA2_VSLOTS;         // ring of V half-tiles
-constexpr int kVSlotBytes = kVBlocks * kBlockBytes;
+constexpr int kVSlotBytes = kVBlocks * kKBlockBytes;
 constexpr int kPBufs = DA_MLA2_PBUFS;          // P tiles in shared memory
-constexpr int kPBytes = 2 * kBlockBytes;  // [64 heads x 128 keys]
+constexpr int kPBytes = (kTile / 64) * kQBlockBytes;  // [64 heads x kTile keys]
+constexpr int kQStageSlots = (kQTmemBlocks * kQBlockBytes + kVSlotBytes - 1) / kVSlotBytes;  // V slots that stage Q at first
 constexpr int kOffQ = 0;
-constexpr int kOffA = kOffQ + kQSmemBlocks * kBlockBytes;
-constexpr int kOffV = kOffA + kASlots * kBlockBytes;
+constexpr int kOffA = kOffQ + kQSmemBlocks * kQBlockBytes;
+constexpr int kOffV = kOffA + kASlots * kKBlockBytes;
 constexpr int kOffP = kOffV + kVSlots * kVSlotBytes;
 constexpr int kOffBar = kOffP + kPBufs * kPBytes;
 // q_full, q_tmem, q_stage_full, q_copied, a_full/a_empty[kASlots], v_full/v_empty[kVSlots], s_full[2], p_full[2], pv_done[2]
@@ -81,11 +97,12 @@ constexpr int kLoaderWarps = 4;
 constexpr int kLoaderThreads = kLoaderWarps * 32;
 constexpr int kThreads = 192 + kLoaderThreads;
 constexpr int kTmemCols = 512;
-constexpr int kColS = 0;      // two S buffers of 64 columns
-constexpr int kColO = 128;    // 256 output columns
-constexpr int kColQ = 384;    // kQTmemBlocks * 32 columns
+constexpr int kColS = 0;              // two S buffers of kHalf columns
+constexpr int kColO = 2 * kHalf;      // 256 output columns
+constexpr int kColQ = kColO + 256;    // kQTmemBlocks * 32 columns
 static_assert(kColQ + kQTmemBlocks * 32 <= kTmemCols, "TMEM budget");
-static_assert(kQTmemBlocks * kBlockBytes <= kVSlotBytes && kVSlots >= 2, "Q blocks 0..3 are staged in the last V slot");
+static_assert(kQStageSlots < kVSlots, "the Q blocks bound for TMEM are staged in the last V slots");
+static_assert(kTile == 64 || kTile == 128, "tile");
 static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 static_assert(128 * (256 * 4 + 16) <= kOffP - kOffA, "the epilogue stages its output in the idle rings");
 constexpr float kRescaleThreshold = 8.0f;
@@ -192,11 +209,11 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
                 // a box always delivers its full size: rows past head_q arrive as zeros
                 mbar_arrive_expect_tx_remote(lead(q_full), (uint32_t)(kQSmemBlocks * min(p.head_q, kRows) * 128));
                 for (int j = 0; j < kQSmemBlocks; ++j)
-                    tma2_load_3d(q_s + j * kBlockBytes, &tm_q, (kQTmemBlocks + j) * 64, head0, b, lead(q_full));
+                    tma2_load_3d(q_s + j * kQBlockBytes, &tm_q, (kQTmemBlocks + j) * 64, head0, b, lead(q_full));
                 // blocks 0..3 pass through the last V slot on their way to TMEM
                 mbar_arrive_expect_tx(q_stage_full, (uint32_t)(kQTmemBlocks * min(p.head_q, kRows) * 128));
                 for (int j = 0; j < kQTmemBlocks; ++j)
-                    tma_load_tile_3d(v_s + (kVSlots - 1) * kVSlotBytes + j * kBlockBytes, &tm_q, j * 64, head0, b, q_stage_full);
+                    tma_load_tile_3d(v_s + (kVSlots - kQStageSlots) * kVSlotBytes + j * kQBlockBytes, &tm_q, j * 64, head0, b, q_stage_full);
             } else {
                 mbar_arrive_remote(lead(q_full));
             }
@@ -210,14 +227,14 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             for (int j = 0; j < kBlocks && ok; ++j) {
                 if (round > 0) ok = mbar_wait(&a_empty[slot], (round & 1u) ^ 1u, abort_flag);
                 if (!ok) break;
-                uint8_t *dst = a_s + slot * kBlockBytes;
+                uint8_t *dst = a_s + slot * kKBlockBytes;
                 // a_full[slot] of the rank-0 CTA takes ONE arrival per use, rank 0's, which also announces the
                 // bytes: its own block when that comes by TMA, and always the peer's 8 KB -- delivered by the
                 // peer's TMA copy, or counted by hand when the peer had to write a ragged block with stores.
                 // (No remote arrival per block: a cluster-scope release costs about a thousand cycles.)
                 if (rows == kHalf) {
                     if (lane == 0) {
-                        if (rank == 0) mbar_arrive_expect_tx(&a_full[slot], 2 * kBlockBytes);
+                        if (rank == 0) mbar_arrive_expect_tx(&a_full[slot], 2 * kKBlockBytes);
                         tma2_load_2d(dst, &tm_k, j * 64, (int)tok0, lead(&a_full[slot]));
                     }
                 } else {
@@ -233,10 +250,10 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
                     __syncwarp();
                     if (lane == 0) {
                         if (rank == 0) {
-                            mbar_arrive_expect_tx(&a_full[slot], kBlockBytes);
+                            mbar_arrive_expect_tx(&a_full[slot], kKBlockBytes);
                         } else {
                             fence_acq_rel_cluster();
-                            mbar_complete_tx_remote(lead(&a_full[slot]), kBlockBytes);
+                            mbar_complete_tx_remote(lead(&a_full[slot]), kKBlockBytes);
                         }
                     }
                 }
@@ -254,25 +271,25 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             const uint64_t q_desc0 = smem_desc(smem_u32(q_s), 16, 1024, 2);
             const uint64_t a_desc0 = smem_desc(smem_u32(a_s), 16, 1024, 2);
             const uint64_t p_desc0 = smem_desc(smem_u32(p_s), 16, 1024, 2);
-            const uint64_t v_desc0 = smem_desc(smem_u32(v_s), kBlockBytes, 1024, 2);  // V slot, MN-major
+            const uint64_t v_desc0 = smem_desc(smem_u32(v_s), kKBlockBytes, 1024, 2);  // V slot, MN-major
             const uint32_t q_tmem_addr = tmem_base + kColQ;
             int a_slot = 0;
             uint32_t a_round = 0;
                 auto issue_qk = [&](int t) -> bool {
-                const uint32_t d = tmem_base + kColS + (t & 1) * 64;
+                const uint32_t d = tmem_base + kColS + (t & 1) * kHalf;
                 // (rolled over the blocks, unrolled over the four 16-element steps of a block: small code, and the
                 // descriptors of a block differ from the previous block's by constants)
 #pragma unroll 1
                 for (int j = 0; j < kBlocks; ++j) {
                     if (!mbar_wait(&a_full[a_slot], a_round & 1u, abort_flag)) return false;
                     tc_fence_after();
-                    const uint64_t bd = a_desc0 + (uint64_t)((a_slot * kBlockBytes) >> 4);
+                    const uint64_t bd = a_desc0 + (uint64_t)((a_slot * kKBlockBytes) >> 4);
                     if (j < kQTmemBlocks) {
 #pragma unroll
                         for (int ks = 0; ks < 4; ++ks)
                             umma2_ts(d, q_tmem_addr + j * 32 + ks * 8, bd + (uint64_t)(ks * 2), kIdescQK, (j | ks) ? 1u : 0u, leader);
                     } else {
-                        const uint64_t qd = q_desc0 + (uint64_t)(((j - kQTmemBlocks) * kBlockBytes) >> 4);
+                        const uint64_t qd = q_desc0 + (uint64_t)(((j - kQTmemBlocks) * kQBlockBytes) >> 4);
 #pragma unroll
                         for (int ks = 0; ks < 4; ++ks)
                             umma2_ss(d, qd + (uint64_t)(ks * 2), bd + (uint64_t)(ks * 2), kIdescQK, (j | ks) ? 1u : 0u, leader);
@@ -311,12 +328,14 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
                     tc_fence_after();
                     const uint64_t vd = v_desc0 + (uint64_t)((vs * kVSlotBytes) >> 4);
 #pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        // A = P[64 heads x 16 keys] of key half h; B = V[16 keys x 128 dims] per CTA, blocks {0,1} then {2,3}
-                        const uint64_t ad = pd + (uint64_t)(((h * kBlockBytes) >> 4) + ks * 2);
+                    for (int ks = 0; ks < kHalf / 16; ++ks) {
+                        // A = P[64 heads x 16 keys]: keys h * kHalf + ks * 16 .. of the tile, in 64-key swizzled blocks;
+                        // B = V[16 keys x 128 dims] per CTA, blocks {0,1} then {2,3}
+                        const int key = h * kHalf + ks * 16;
+                        const uint64_t ad = pd + (uint64_t)(((key / 64) * kQBlockBytes + (key % 64) * 2) >> 4);
                         const uint64_t bd = vd + (uint64_t)((ks * 16 * 128) >> 4);
                         umma2_ss(d, ad, bd, kIdescPV, (t | h | ks) ? 1u : 0u, leader);
-                        umma2_ss(d + 128, ad, bd + (uint64_t)((2 * kBlockBytes) >> 4), kIdescPV, (t | h | ks) ? 1u : 0u, leader);
+                        umma2_ss(d + 128, ad, bd + (uint64_t)((2 * kKBlockBytes) >> 4), kIdescPV, (t | h | ks) ? 1u : 0u, leader);
                     }
                     umma2_commit_both(&v_empty[vs], leader);
                 }
@@ -343,15 +362,15 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             const size_t tok0 = rows > 0 ? kv_tile_row(p, b, seq_begin, key0) : 0;
             const int vs = i % kVSlots;
             if (i >= kVSlots) ok = mbar_wait(&v_empty[vs], ((uint32_t)(i / kVSlots) & 1u) ^ 1u, abort_flag);
-            if (ok && i == kVSlots - 1) ok = mbar_wait(q_copied, 0, abort_flag);  // the slot staged Q blocks until now
+            if (ok && i >= kVSlots - kQStageSlots && i < kVSlots) ok = mbar_wait(q_copied, 0, abort_flag);  // the slot staged Q blocks
             if (!ok) break;
             uint8_t *slot = v_s + vs * kVSlotBytes;
 #pragma unroll
             for (int n = 0; n < kVBlocks * kHalf * 8 / kLoaderThreads; ++n) {
                 const int e = lt + n * kLoaderThreads;
-                const int j = e >> 9, r = (e >> 3) & 63, cc = e & 7;
+                const int j = e / (kHalf * 8), r = (e >> 3) % kHalf, cc = e & 7;
                 const T *src = k_g + (tok0 + max(0, min(r, rows - 1))) * p.k_row_stride + ((int)rank * kVBlocks + j) * 64 + cc * 8;
-                cp_async16(slot + j * kBlockBytes + r * 128 + ((cc ^ (r & 7)) << 4), src, r < rows ? 16u : 0u);  // 0: zero fill
+                cp_async16(slot + j * kKBlockBytes + r * 128 + ((cc ^ (r & 7)) << 4), src, r < rows ? 16u : 0u);  // 0: zero fill
             }
             cp_async_commit();
             if (i >= 1) {  // the half-tile issued one iteration ago has landed: publish it to the tensor pipe
@@ -381,14 +400,14 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             // blocks arrive by TMA in the last V slot (which the loaders leave alone until q_copied completes) and
             // each thread moves its own row: 16-byte loads of one row per lane straight from global memory would
             // cost one L1 wavefront per lane and instruction, about four thousand cycles per CTA.
-            const uint8_t *q_stage = v_s + (kVSlots - 1) * kVSlotBytes;
+            const uint8_t *q_stage = v_s + (kVSlots - kQStageSlots) * kVSlotBytes;
             const bool have_q = head0 < p.head_q;
             if (have_q) ok = __all_sync(0xffffffffu, mbar_wait(q_stage_full, 0, abort_flag)) != 0;
 #pragma unroll
             for (int j = 0; j < kQTmemBlocks; ++j) {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    const uint4 v = (valid && ok) ? *reinterpret_cast<const uint4 *>(q_stage + j * kBlockBytes + r * 128 + ((i ^ (r & 7)) << 4))
+                    const uint4 v = (valid && ok) ? *reinterpret_cast<const uint4 *>(q_stage + j * kQBlockBytes + r * 128 + ((i ^ (r & 7)) << 4))
                                                   : make_uint4(0, 0, 0, 0);
                     buf[4 * i] = v.x, buf[4 * i + 1] = v.y, buf[4 * i + 2] = v.z, buf[4 * i + 3] = v.w;
                 }
@@ -410,23 +429,34 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
         for (int t = 0; t < n_tiles; ++t) {
             const int key0 = k_begin + t * kTile + kh * kHalf;  // first key of this thread's 64 columns
             const int rows = k_end - key0;                       // columns >= rows are past the end
-            const uint32_t s_addr = lane_base + kColS + (t & 1) * 64;
+            const uint32_t s_addr = lane_base + kColS + (t & 1) * kHalf;
             if (ok) ok = wait_all(&s_full[t & 1], (uint32_t)(t / 2) & 1u);
             float s[kHalf];
             float mx = -INFINITY;
             if (ok) {
                 tc_fence_after();
-                uint32_t buf2[32];
-                tmem_ld32(s_addr, buf);       // both halves of the row are requested before the wait:
-                tmem_ld32(s_addr + 32, buf2);  // a TMEM load takes a few hundred cycles to return
-                tmem_wait_ld();
+                if (kHalf == 64) {
+                    uint32_t buf2[32];
+                    tmem_ld32(s_addr, buf);        // both halves of the row are requested before the wait:
+                    tmem_ld32(s_addr + 32, buf2);  // a TMEM load takes a few hundred cycles to return
+                    tmem_wait_ld();
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const float x0 = __uint_as_float(buf[j]) * p.scale_log2 + slope2 * (float)(key0 + j + pos_shift);
-                    const float x1 = __uint_as_float(buf2[j]) * p.scale_log2 + slope2 * (float)(key0 + 32 + j + pos_shift);
-                    s[j] = (j < rows) ? (valid ? x0 : 0.0f) : -INFINITY;
-                    s[32 + j] = (32 + j < rows) ? (valid ? x1 : 0.0f) : -INFINITY;
-                    mx = fmaxf(mx, fmaxf(s[j], s[32 + j]));
+                    for (int j = 0; j < 32; ++j) {
+                        const float x0 = __uint_as_float(buf[j]) * p.scale_log2 + slope2 * (float)(key0 + j + pos_shift);
+                        const float x1 = __uint_as_float(buf2[j]) * p.scale_log2 + slope2 * (float)(key0 + 32 + j + pos_shift);
+                        s[j] = (j < rows) ? (valid ? x0 : 0.0f) : -INFINITY;
+                        s[kHalf - 32 + j] = (32 + j < rows) ? (valid ? x1 : 0.0f) : -INFINITY;
+                        mx = fmaxf(mx, fmaxf(s[j], s[kHalf - 32 + j]));
+                    }
+                } else {
+                    tmem_ld32(s_addr, buf);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float x0 = __uint_as_float(buf[j]) * p.scale_log2 + slope2 * (float)(key0 + j + pos_shift);
+                        s[j] = (j < rows) ? (valid ? x0 : 0.0f) : -INFINITY;
+                        mx = fmaxf(mx, s[j]);
+                    }
                 }
             }
             // one reference per head: the two threads of a head swap their maxima
@@ -461,11 +491,13 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
                 ok = wait_all(&pv_done[(t - 1) & 1], (uint32_t)((t - 1) / 2) & 1u);
                 if (!ok) continue;
             }
-            // P = exp2(S - m_ref), rounded to the input type: row r, keys kh*64.. of the tile, K-major swizzled
-            uint8_t *p_row = p_s + (t % kPBufs) * kPBytes + kh * kBlockBytes + r * 128;
+            // P = exp2(S - m_ref), rounded to the input type: row r, keys kh * kHalf .. of the tile, K-major in 64-key
+            // swizzled blocks
+            const int pkey = kh * kHalf;
+            uint8_t *p_row = p_s + (t % kPBufs) * kPBytes + (pkey / 64) * kQBlockBytes + r * 128;
             float sum = 0.0f;
 #pragma unroll
-            for (int cc = 0; cc < 8; ++cc) {
+            for (int cc = 0; cc < kHalf / 8; ++cc) {
                 uint32_t w[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -479,7 +511,8 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
                         w[j] = *reinterpret_cast<uint32_t *>(&hh);
                     }
                 }
-                *reinterpret_cast<uint4 *>(p_row + ((cc ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                const int chunk = (pkey % 64) / 8 + cc;  // 16-byte chunk of the 128-byte row
+                *reinterpret_cast<uint4 *>(p_row + ((chunk ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
             l += sum;
             fence_proxy_async();
