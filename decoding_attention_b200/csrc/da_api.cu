@@ -125,9 +125,10 @@ bool mla_on_tensor_cores(const da_decode_args_t &a) {
 // tensor cores for 64 x 4096 keys), and from 8 heads up it is bound by instruction issue anyway (dim
 // 256, 32 heads: 979 against 141 us).
 bool gqa_on_tensor_cores(const da_decode_args_t &a) {
-    if (!a.v || a.dim != a.dim_v || (a.dim != 64 && a.dim != 128 && a.dim != 256)) return false;
+    if (!a.v || a.dim != a.dim_v || (a.dim != 64 && a.dim != 96 && a.dim != 128 && a.dim != 256)) return false;
     const int64_t group = a.head_q / a.head_k;
     if (env_overrides().force_simt || group > 128) return false;
+    // (head dim 96 runs on the tensor-core kernel's 128-column instantiation, the tensor maps zero-filling columns 96-127)
     return a.dim == 128 ? (group >= 3 && group != 4) : group >= 5;
 }
 
@@ -282,7 +283,8 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
         const int half_tile = split_info_mla_2sm().tile_keys / 2;
         shape = (!a.block_table || a.page_size >= half_tile) && !env_overrides().mla_1sm ? Shape::kMla2Sm : Shape::kMlaTc;
     }
-    if (a.kv_dtype != DA_KV_FP8_E4M3 && (shape == Shape::kD64 || shape == Shape::kD128 || shape == Shape::kD256) &&
+    if (a.kv_dtype != DA_KV_FP8_E4M3 &&
+        (shape == Shape::kD64 || shape == Shape::kD96 || shape == Shape::kD128 || shape == Shape::kD256) &&
         gqa_on_tensor_cores(a)) {
         shape = Shape::kGqaTc;  // (an FP8 cache is read by the CUDA-core kernel, whatever the group size)
     }
@@ -517,6 +519,7 @@ int da_decode_fwd(const da_decode_args_t *a) {
     p.o_row_stride = a->o_row_stride ? a->o_row_stride : a->head_q * a->dim_v;
     p.head_q = (int)a->head_q;
     p.head_k = (int)a->head_k;
+    p.dim = (int)a->dim;
     p.group = (int)(a->head_q / a->head_k);
     p.head_chunks = plan.head_chunks;
     p.batch = (int)a->batch;
@@ -559,7 +562,7 @@ int da_decode_fwd(const da_decode_args_t *a) {
     if (plan.shape == Shape::kGqaTc) {
         // q as [batch][head_q][dim] in boxes {64, min(128, head_q), 1}; K and V as [rows][head_k][dim] in
         // boxes {64, 1, tile}: all 128-byte-swizzled, the layout the UMMA descriptors name.
-        const uint64_t dim = (uint64_t)a->dim;  // 64, 128 or 256
+        const uint64_t dim = (uint64_t)a->dim;  // 64, 96, 128 or 256 (96: boxes at column 64 come back half zero-filled)
         const uint64_t qd[3] = {dim, (uint64_t)a->head_q, (uint64_t)a->batch};
         const uint64_t qs[2] = {dim * 2, (uint64_t)p.q_row_stride * 2};
         const uint32_t qb[3] = {64, (uint32_t)(a->head_q < 128 ? a->head_q : 128), 1};
@@ -617,7 +620,7 @@ int da_decode_fwd(const da_decode_args_t *a) {
         case Shape::kD128: e = launch_split_d128(bf16, fp8, plan.heads, p, maps, stream); break;
         case Shape::kD256: e = launch_split_d256(bf16, fp8, plan.heads, p, maps, stream); break;
         case Shape::kMla: e = launch_split_mla_simt(bf16, plan.heads, p, maps, stream); break;
-        case Shape::kGqaTc: e = launch_gqa_tc(bf16, (int)a->dim, p, tm_q, maps.k, maps.v, stream); break;
+        case Shape::kGqaTc: e = launch_gqa_tc(bf16, a->dim == 96 ? 128 : (int)a->dim, p, tm_q, maps.k, maps.v, stream); break;
         case Shape::kMlaTc: e = launch_mla_tc(bf16, p, maps.k, maps.v, stream); break;
         case Shape::kMla2Sm: e = launch_mla_2sm(bf16, p, maps.k, maps.v, stream); break;
         default: e = cudaErrorInvalidValue; break;

@@ -40,6 +40,7 @@ struct SplitParams {
     int page_shift;            // log2(page_size); pages hold a whole number of key tiles
     long long q_row_stride, k_row_stride, v_row_stride, o_row_stride;  // in elements
     int head_q, head_k;
+    int dim;           // head dim of q / k as the caller gave it (a kernel may run it padded, e.g. 96 as 128)
     int group;         // query heads per KV head
     int head_chunks;   // CTAs that share one KV head (group / heads-per-CTA)
     int batch;

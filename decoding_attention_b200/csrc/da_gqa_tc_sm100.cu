@@ -1,4 +1,4 @@
-// Grouped-query / multi-query decode attention (head dims 64, 128, 256) on the sm_100a tensor cores,
+// Grouped-query / multi-query decode attention (head dims 64, 96, 128, 256) on the sm_100a tensor cores,
 // for KV heads that serve a group of query heads the CUDA-core kernel handles badly (more than 4, or
 // not 1, 2 or 4; at most 128).
 //
@@ -91,6 +91,10 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
     const int b = p.batch_order ? p.batch_order[blockIdx.z] : (int)blockIdx.z;
     const int G = p.group;            // query heads of this KV head: rows 0..G-1 of the tile
     const int h0 = hk * G;
+    // The head dim the caller's tensors have.  It equals D except for head dim 96, which runs on the D = 128
+    // instantiation: the tensor maps declare 96 columns, so the second 64-column box of every row arrives with
+    // its last 32 columns zero-filled, S and O come out as for 128 columns of which the last 32 are zero.
+    const int dreal = p.dim;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int seq_begin = p.cu_seq_k[b];
     const int len = p.cu_seq_k[b + 1] - seq_begin;
@@ -101,10 +105,10 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
 
     if (k_begin >= k_end) {
         if (p.num_splits == 1) {  // empty sequence: zero rows, LSE = -inf
-            for (int idx = tid; idx < G * kDim; idx += kThreads) {
-                const int h = h0 + idx / kDim, d = idx % kDim;
-                if (o_out) o_out[(size_t)b * p.o_row_stride + (size_t)h * kDim + d] = from_float<T>(0.0f);
-                if (p.o_f32) p.o_f32[((size_t)b * p.head_q + h) * kDim + d] = 0.0f;
+            for (int idx = tid; idx < G * dreal; idx += kThreads) {
+                const int h = h0 + idx / dreal, d = idx % dreal;
+                if (o_out) o_out[(size_t)b * p.o_row_stride + (size_t)h * dreal + d] = from_float<T>(0.0f);
+                if (p.o_f32) p.o_f32[((size_t)b * p.head_q + h) * dreal + d] = 0.0f;
             }
             if (p.lse && tid < G) p.lse[(size_t)b * p.head_q + h0 + tid] = -INFINITY;
         }
@@ -172,8 +176,8 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             mbar_arrive_expect_tx(q_full, kBlocks * min(kRows, p.head_q) * 128);
             for (int kb = 0; kb < kBlocks; ++kb) tma_load_tile_3d(q_s + kb * kQBlockBytes, &tm_q, kb * 64, h0, b, q_full);
         }
-        const T *k_g = reinterpret_cast<const T *>(p.k) + (size_t)hk * kDim;
-        const T *v_g = reinterpret_cast<const T *>(p.v) + (size_t)hk * kDim;
+        const T *k_g = reinterpret_cast<const T *>(p.k) + (size_t)hk * dreal;
+        const T *v_g = reinterpret_cast<const T *>(p.v) + (size_t)hk * dreal;
         const int run = kShortPages ? kv_run_keys(p, kTile) : kTile;
         for (int t = 0; t < n_tiles && ok; ++t) {
             const int st = t % kStages;
@@ -203,7 +207,7 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                 for (int i = lane; i < kTile * kChunks; i += 32) {
                     const int r = i / kChunks, c = i % kChunks;
                     uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
-                    if (r < rows) {
+                    if (r < rows && c * 8 < dreal) {  // columns past the real head dim stay zero
                         const size_t row = row_of(r);
                         kv = *reinterpret_cast<const uint4 *>(k_g + row * p.k_row_stride + c * 8);
                         vv = *reinterpret_cast<const uint4 *>(v_g + row * p.v_row_stride + c * 8);
@@ -416,14 +420,14 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                     const float a1 = (kStreams == 2 && w1 > 0.0f) ? __uint_as_float(ob[j]) * w1 : 0.0f;
                     out[j] = (a0 + a1) * inv;
                 }
-                if (!valid) continue;
+                if (!valid || d0 >= dreal) continue;  // (a head dim run padded has whole column groups of zeros)
                 if (p.num_splits > 1) {
-                    float4 *dst = reinterpret_cast<float4 *>(p.part_o + row * kDim + d0);
+                    float4 *dst = reinterpret_cast<float4 *>(p.part_o + row * dreal + d0);
 #pragma unroll
                     for (int j = 0; j < CW / 4; ++j) dst[j] = make_float4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
                 } else {
                     if (o_out) {
-                        uint4 *dst = reinterpret_cast<uint4 *>(o_out + (size_t)b * p.o_row_stride + (size_t)h * kDim + d0);
+                        uint4 *dst = reinterpret_cast<uint4 *>(o_out + (size_t)b * p.o_row_stride + (size_t)h * dreal + d0);
 #pragma unroll
                         for (int j = 0; j < CW / 8; ++j) {
                             alignas(16) T tmp[8];
@@ -433,7 +437,7 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                         }
                     }
                     if (p.o_f32) {
-                        float *dst = p.o_f32 + ((size_t)b * p.head_q + h) * kDim + d0;
+                        float *dst = p.o_f32 + ((size_t)b * p.head_q + h) * dreal + d0;
 #pragma unroll
                         for (int j = 0; j < CW; ++j) dst[j] = out[j];
                     }

@@ -17,9 +17,17 @@ _LIB = None
 _REF = None
 
 
+def reference_dir():
+    """A checkout of the reference project: $DA_REFERENCE_DIR, else a folder named "reference" beside this
+    repository; None when neither exists."""
+    cand = os.environ.get("DA_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return cand if os.path.isfile(os.path.join(cand, "csrc", "common", "tester.h")) else None
+
+
 def build(quiet=True):
     """Compile the oracle (and the reference's CPU path when a reference checkout is present)."""
-    subprocess.run(["make", "-C", _HERE, "all"], check=True,
+    ref = reference_dir()
+    subprocess.run(["make", "-C", _HERE, "all"] + (["REF=" + ref] if ref else []), check=True,
                    stdout=subprocess.DEVNULL if quiet else None, stderr=subprocess.STDOUT if quiet else None)
 
 

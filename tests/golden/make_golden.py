@@ -50,7 +50,10 @@ def load_torch_attn(ref_root):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    from oracle import attn_oracle
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else attn_oracle.reference_dir()
+    if not ref_root:
+        sys.exit("usage: make_golden.py <checkout of the reference project>")
     torch_attn = load_torch_attn(ref_root)
     for name, dtype, batch, seq_k, head_q, head_k, dim, dim_v, dist, scale in CASES:
         mla = dim != dim_v

@@ -444,3 +444,23 @@ def test_fp8_kv_cache_paged_and_errors(native_lib, oracle):
     with pytest.raises(native_lib.DecodingAttnError) as e:
         native_lib.decode_fwd(native_lib.make_args(q.to(DEV), kv8.to(DEV), None, o, cu.to(DEV), 64, 512))
     assert e.value.status == native_lib.DA_ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("hq,hk", [(64, 8), (40, 8), (32, 1), (24, 4)])
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+def test_head_dim_96_large_groups(native_lib, oracle, hq, hk, dt):
+    """Head dim 96 with more than four query heads per KV head runs on the tensor-core kernel's 128-column
+    instantiation (tensor maps zero-fill columns 96-127): ragged tiles, ALiBi, splits, paged caches."""
+    w = synth.Workload(f"d96_{hq}_{hk}", dt, hq, hk, 96, 96, [700, 64, 1, 129, 0, 2100], is_alibi=True, dist="normal",
+                       scale=0.5, seed=91)
+    check(native_lib, oracle, w)
+    check(native_lib, oracle, w, num_splits=3)
+    q, k, v, cu = w.make("cpu")
+    expect = oracle.attn_cpu(q, k, v, cu, dim_v=96, is_alibi=True)
+    for page in (64, 16):
+        k_pool, v_pool, table = to_pages(k, v, cu, page, seed=page)
+        o = torch.full((w.batch, hq, 96), float("nan"), dtype=dt, device=DEV)
+        native_lib.decode_fwd(native_lib.make_args(q.to(DEV), k_pool.to(DEV), v_pool.to(DEV), o, cu.to(DEV), w.max_seq_k, 96,
+                                                   is_alibi=True, block_table=table.to(DEV), page_size=page))
+        torch.cuda.synchronize()
+        assert_close(o, expect, f"{w.name} paged {page}")
