@@ -102,13 +102,14 @@ def _ptr(t):
 
 def make_args(q, k, v, o, cu_seq_k, max_seq_k, dim_v, is_alibi=False, softmax_scale=None, lse=None, o_f32=None,
               kv_pos_offset=None, kv_total_len=None, workspace=None, num_splits=0, stream=0, packed=False,
-              block_table=None, page_size=0, k_scale=None, v_scale=None):
+              block_table=None, page_size=0, k_scale=None, v_scale=None, int4=False):
     """Fill a DecodeArgs from torch tensors (device tensors, or host tensors for the *_host call).
 
     Paged cache: pass ``block_table`` (int32 [batch, blocks]) and ``page_size``; ``k`` / ``v`` are then the
     page pools, either [num_pages * page_size, head_k, dim] or [num_pages, page_size, head_k, dim].
-    FP8 cache: ``k`` / ``v`` of dtype torch.float8_e4m3fn (q and o stay fp16 / bf16) with per-tensor
-    ``k_scale`` / ``v_scale`` (default 1)."""
+    Quantised cache (q and o stay fp16 / bf16) with per-tensor ``k_scale`` / ``v_scale`` (default 1): ``k`` / ``v``
+    of dtype torch.float8_e4m3fn or torch.int8; or, with ``int4=True``, torch.uint8 tensors [rows, head_k, dim / 2]
+    holding two signed 4-bit values per byte (even element in the low nibble)."""
     import torch
     a = DecodeArgs()
     a.struct_size = ctypes.sizeof(DecodeArgs)
@@ -123,10 +124,11 @@ def make_args(q, k, v, o, cu_seq_k, max_seq_k, dim_v, is_alibi=False, softmax_sc
         v = v.view(-1, v.shape[2], v.shape[3]) if v is not None else None
     a.head_q, a.dim = q.shape[1], q.shape[2]
     a.head_k = k.shape[1]
+    per_byte = 2 if int4 else 1  # elements per stored byte: strides are given in elements
     a.dim_v = int(dim_v)
     if not packed:
-        a.q_row_stride, a.k_row_stride = q.stride(0), k.stride(0)
-        a.v_row_stride = v.stride(0) if v is not None else 0
+        a.q_row_stride, a.k_row_stride = q.stride(0), k.stride(0) * per_byte
+        a.v_row_stride = v.stride(0) * per_byte if v is not None else 0
         a.o_row_stride = o.stride(0) if o is not None else 0
     a.softmax_scale = float(softmax_scale) if softmax_scale else 0.0
     a.lse, a.o_f32 = _ptr(lse), _ptr(o_f32)
@@ -135,8 +137,8 @@ def make_args(q, k, v, o, cu_seq_k, max_seq_k, dim_v, is_alibi=False, softmax_sc
         a.workspace = workspace.data_ptr()
         a.workspace_bytes = workspace.numel() * workspace.element_size()
     a.stream = int(stream) if stream else None
-    if k.dtype == getattr(torch, "float8_e4m3fn", None):
-        a.kv_dtype = 1
+    if int4 or k.dtype in (getattr(torch, "float8_e4m3fn", None), torch.int8):
+        a.kv_dtype = 3 if int4 else (2 if k.dtype == torch.int8 else 1)
         a.k_scale = float(k_scale) if k_scale else 1.0
         a.v_scale = float(v_scale) if v_scale else 1.0
     if block_table is not None:

@@ -274,19 +274,19 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
                     "with v and (576,512) without",
                     (long long)a.dim, (long long)a.dim_v, has_v ? "given" : "NULL");
     }
-    if (a.kv_dtype == DA_KV_FP8_E4M3) {
+    if (a.kv_dtype != DA_KV_SAME_AS_Q) {
         if (shape == Shape::kMla) {
-            return fail(DA_ERR_UNSUPPORTED, "an FP8 cache is supported for (dim, dim_v) (64,64) (96,96) (128,128) (256,256) with v given");
+            return fail(DA_ERR_UNSUPPORTED, "a quantised cache is supported for (dim, dim_v) (64,64) (96,96) (128,128) (256,256) with v given");
         }
     } else if (shape == Shape::kMla && mla_on_tensor_cores(a)) {
         // SM pairs (cta_group::2) unless the cache is paged in pages shorter than the keys one CTA stages at a time
         const int half_tile = split_info_mla_2sm().tile_keys / 2;
         shape = (!a.block_table || a.page_size >= half_tile) && !env_overrides().mla_1sm ? Shape::kMla2Sm : Shape::kMlaTc;
     }
-    if (a.kv_dtype != DA_KV_FP8_E4M3 &&
+    if (a.kv_dtype == DA_KV_SAME_AS_Q &&
         (shape == Shape::kD64 || shape == Shape::kD96 || shape == Shape::kD128 || shape == Shape::kD256) &&
         gqa_on_tensor_cores(a)) {
-        shape = Shape::kGqaTc;  // (an FP8 cache is read by the CUDA-core kernel, whatever the group size)
+        shape = Shape::kGqaTc;  // (a quantised cache is read by the CUDA-core kernel, whatever the group size)
     }
     const int group = (int)(a.head_q / a.head_k);
     const int heads = heads_per_cta(shape, group);
@@ -394,15 +394,16 @@ int check_args(const da_decode_args_t *a) {
                              a->head_q * a->dim_v};
     for (int i = 0; i < 4; ++i) {
         if (strides[i] == 0) continue;
-        const int64_t unit = (a->kv_dtype == DA_KV_FP8_E4M3 && (i == 1 || i == 2)) ? 16 : 8;  // 16 bytes either way
+        const bool kv_stride = i == 1 || i == 2;  // 16 bytes, whatever the element size
+        const int64_t unit = !kv_stride || a->kv_dtype == DA_KV_SAME_AS_Q ? 8 : (a->kv_dtype == DA_KV_INT4 ? 32 : 16);
         if (strides[i] < mins[i] || strides[i] % unit != 0) {
             return fail(DA_ERR_INVALID_ARG, "row stride %d must be a multiple of 16 bytes and cover a row", i);
         }
     }
-    if (a->kv_dtype != DA_KV_SAME_AS_Q && a->kv_dtype != DA_KV_FP8_E4M3) {
-        return fail(DA_ERR_INVALID_ARG, "kv_dtype %d: 0 (the type of q) or 1 (FP8 e4m3) expected", a->kv_dtype);
+    if (a->kv_dtype < DA_KV_SAME_AS_Q || a->kv_dtype > DA_KV_INT4) {
+        return fail(DA_ERR_INVALID_ARG, "kv_dtype %d: 0 (the type of q), 1 (FP8 e4m3), 2 (int8) or 3 (int4) expected", a->kv_dtype);
     }
-    if (a->kv_dtype == DA_KV_FP8_E4M3 && !a->v) return fail(DA_ERR_UNSUPPORTED, "an FP8 cache needs a separate v tensor");
+    if (a->kv_dtype != DA_KV_SAME_AS_Q && !a->v) return fail(DA_ERR_UNSUPPORTED, "a quantised cache needs a separate v tensor");
     if (a->block_table) {
         // A key tile (32 or 64 keys) is fetched in runs of consecutive rows: whole, or page by page.
         if (a->page_size < 16 || (a->page_size & (a->page_size - 1)) != 0) {
@@ -529,7 +530,7 @@ int da_decode_fwd(const da_decode_args_t *a) {
     const float scale = a->softmax_scale > 0.0f ? a->softmax_scale : (float)(1.0 / std::sqrt((double)a->dim));
     p.scale_log2 = scale * kLog2e;
     p.out_scale = 1.0f;
-    if (a->kv_dtype == DA_KV_FP8_E4M3) {  // the cache stands for k * k_scale, v * v_scale: both factors leave the loops
+    if (a->kv_dtype != DA_KV_SAME_AS_Q) {  // the cache stands for k * k_scale, v * v_scale: both factors leave the loops
         p.scale_log2 *= a->k_scale > 0.0f ? a->k_scale : 1.0f;
         p.out_scale = a->v_scale > 0.0f ? a->v_scale : 1.0f;
     }
@@ -550,7 +551,7 @@ int da_decode_fwd(const da_decode_args_t *a) {
     const int box_keys = (a->block_table && a->page_size < plan.tile_keys) ? a->page_size : plan.tile_keys;
 
     const bool bf16 = a->is_bf16 != 0;
-    const bool fp8 = a->kv_dtype == DA_KV_FP8_E4M3;
+    const int kvq = a->kv_dtype;  // 0 as q, 1 FP8, 2 int8, 3 int4
     KvMaps maps;
     memset(&maps, 0, sizeof(maps));
     // Tiled TMA needs a global stride that is a multiple of 16 bytes (checked above: 8 elements) and
@@ -606,19 +607,21 @@ int da_decode_fwd(const da_decode_args_t *a) {
         if (rc != DA_OK) return rc;
     }
     if (p.use_tmap) {
-        const int kv_dt = fp8 ? 2 : (bf16 ? 1 : 0);
-        rc = make_kv_tensor_map(p.k, p.k_row_stride, p.head_k, (int)a->dim, box_keys, kv_dt, &maps.k);
+        // a quantised cache is mapped as bytes: a head's row is dim (8-bit) or dim / 2 (4-bit) of them
+        const int kv_dt = kvq ? 2 : (bf16 ? 1 : 0);
+        const int per_byte = kvq == DA_KV_INT4 ? 2 : 1;
+        rc = make_kv_tensor_map(p.k, p.k_row_stride / per_byte, p.head_k, (int)a->dim / per_byte, box_keys, kv_dt, &maps.k);
         if (rc != DA_OK) return rc;
-        rc = make_kv_tensor_map(p.v, p.v_row_stride, p.head_k, (int)a->dim_v, box_keys, kv_dt, &maps.v);
+        rc = make_kv_tensor_map(p.v, p.v_row_stride / per_byte, p.head_k, (int)a->dim_v / per_byte, box_keys, kv_dt, &maps.v);
         if (rc != DA_OK) return rc;
     }
     cudaError_t e;
     if (g_prof_start) cudaEventRecord(g_prof_start, stream);
     switch (plan.shape) {
-        case Shape::kD64: e = launch_split_d64(bf16, fp8, plan.heads, p, maps, stream); break;
-        case Shape::kD96: e = launch_split_d96(bf16, fp8, plan.heads, p, maps, stream); break;
-        case Shape::kD128: e = launch_split_d128(bf16, fp8, plan.heads, p, maps, stream); break;
-        case Shape::kD256: e = launch_split_d256(bf16, fp8, plan.heads, p, maps, stream); break;
+        case Shape::kD64: e = launch_split_d64(bf16, kvq, plan.heads, p, maps, stream); break;
+        case Shape::kD96: e = launch_split_d96(bf16, kvq, plan.heads, p, maps, stream); break;
+        case Shape::kD128: e = launch_split_d128(bf16, kvq, plan.heads, p, maps, stream); break;
+        case Shape::kD256: e = launch_split_d256(bf16, kvq, plan.heads, p, maps, stream); break;
         case Shape::kMla: e = launch_split_mla_simt(bf16, plan.heads, p, maps, stream); break;
         case Shape::kGqaTc: e = launch_gqa_tc(bf16, a->dim == 96 ? 128 : (int)a->dim, p, tm_q, maps.k, maps.v, stream); break;
         case Shape::kMlaTc: e = launch_mla_tc(bf16, p, maps.k, maps.v, stream); break;
@@ -673,9 +676,10 @@ int da_decode_fwd_host(const da_decode_args_t *h) {
     if (total_k < 0) return fail(DA_ERR_INVALID_ARG, "cu_seq_k must not decrease");
     auto up = [](size_t x) { return (x + 255) / 256 * 256; };
     const size_t q_b = up((size_t)h->batch * h->head_q * h->dim * 2);
-    const size_t kv_eb = h->kv_dtype == DA_KV_FP8_E4M3 ? 1 : 2;  // bytes per cache element
-    const size_t k_b = up((size_t)total_k * h->head_k * h->dim * kv_eb);
-    const size_t v_b = h->v ? up((size_t)total_k * h->head_k * h->dim_v * kv_eb) : 0;
+    const size_t kv_bits = h->kv_dtype == DA_KV_SAME_AS_Q ? 16 : (h->kv_dtype == DA_KV_INT4 ? 4 : 8);  // per cache element
+    const size_t k_bytes = (size_t)total_k * h->head_k * h->dim * kv_bits / 8;
+    const size_t v_bytes = h->v ? (size_t)total_k * h->head_k * h->dim_v * kv_bits / 8 : 0;
+    const size_t k_b = up(k_bytes), v_b = up(v_bytes);
     const size_t o_b = up((size_t)h->batch * h->head_q * h->dim_v * 2);
     const size_t cu_b = up((size_t)(h->batch + 1) * 4);
     const size_t lse_b = h->lse ? up((size_t)h->batch * h->head_q * 4) : 0;
@@ -707,9 +711,9 @@ int da_decode_fwd_host(const da_decode_args_t *h) {
     if (e == cudaSuccess)
         e = cudaMemcpyAsync(dq, h->q, (size_t)h->batch * h->head_q * h->dim * 2, cudaMemcpyHostToDevice, stream);
     if (e == cudaSuccess)
-        e = cudaMemcpyAsync(dk, h->k, (size_t)total_k * h->head_k * h->dim * kv_eb, cudaMemcpyHostToDevice, stream);
+        e = cudaMemcpyAsync(dk, h->k, k_bytes, cudaMemcpyHostToDevice, stream);
     if (e == cudaSuccess && h->v)
-        e = cudaMemcpyAsync(dv, h->v, (size_t)total_k * h->head_k * h->dim_v * kv_eb, cudaMemcpyHostToDevice, stream);
+        e = cudaMemcpyAsync(dv, h->v, v_bytes, cudaMemcpyHostToDevice, stream);
     if (e != cudaSuccess) return fail(DA_ERR_CUDA, "host-to-device copy: %s", cudaGetErrorString(e));
     rc = da_decode_fwd(&d);
     if (rc != DA_OK) return rc;

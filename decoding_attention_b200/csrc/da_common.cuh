@@ -48,8 +48,8 @@ struct SplitParams {
     int chunk_keys;    // keys per split (multiple of the tile)
     int is_alibi;
     int use_tmap;      // full tiles are fetched with one tiled TMA copy through the tensor maps
-    float scale_log2;  // softmax scale * log2(e) (times the K scale of an FP8 cache)
-    float out_scale;   // factor on the output: the V scale of an FP8 cache, else 1
+    float scale_log2;  // softmax scale * log2(e) (times the K scale of a quantised cache)
+    float out_scale;   // factor on the output: the V scale of a quantised cache, else 1
 };
 
 // Has an earlier CTA of this very launch given up a bounded wait?  (Later launches carry another id
@@ -241,11 +241,21 @@ __device__ __forceinline__ void unpack8_e4m3(const uint2 &raw, float (&f)[8]) {
         f[2 * i + 1] = t.y;
     }
 }
-// One lane's chunk of a K or V row in shared memory: eight elements of the 16-bit type T, or eight FP8 bytes.
-template <typename T, bool FP8>
+// One lane's chunk of a K or V row in shared memory, eight elements, to fp32.  KVQ: 0 = the 16-bit type T (16 bytes),
+// 1 = FP8 e4m3 (8 bytes), 2 = signed 8-bit integers (8 bytes), 3 = signed 4-bit integers, low nibble first (4 bytes).
+template <typename T, int KVQ>
 __device__ __forceinline__ void load_chunk8(const uint8_t *ptr, float (&f)[8]) {
-    if (FP8) {
+    if (KVQ == 1) {
         unpack8_e4m3(*reinterpret_cast<const uint2 *>(ptr), f);
+    } else if (KVQ == 2) {
+        const uint2 raw = *reinterpret_cast<const uint2 *>(ptr);
+        const uint32_t w[2] = {raw.x, raw.y};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = (float)(int)(int8_t)((w[i >> 2] >> ((i & 3) * 8)) & 0xffu);
+    } else if (KVQ == 3) {
+        const uint32_t w = *reinterpret_cast<const uint32_t *>(ptr);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = (float)(((int)(w << (28 - 4 * i))) >> 28);  // sign-extended nibble i
     } else {
         unpack8<T>(*reinterpret_cast<const uint4 *>(ptr), f);
     }

@@ -18,14 +18,14 @@ struct SplitVariantInfo {
 };
 
 // Per-shape launchers (da_split_d*.cu).  `heads` must be one of the values the shape instantiates;
-// returns cudaErrorInvalidValue otherwise.  `fp8`: the cache holds FP8 e4m3 bytes (q and o keep the 16-bit type).
+// returns cudaErrorInvalidValue otherwise.  `kvq`: how the cache is stored (0 as q, 1 FP8 e4m3, 2 int8, 3 int4; q and o keep the 16-bit type).
 struct KvMaps {
     CUtensorMap k, v;
 };
-cudaError_t launch_split_d64(bool bf16, bool fp8, int heads, const SplitParams &p, const KvMaps &m, cudaStream_t s);
-cudaError_t launch_split_d96(bool bf16, bool fp8, int heads, const SplitParams &p, const KvMaps &m, cudaStream_t s);
-cudaError_t launch_split_d128(bool bf16, bool fp8, int heads, const SplitParams &p, const KvMaps &m, cudaStream_t s);
-cudaError_t launch_split_d256(bool bf16, bool fp8, int heads, const SplitParams &p, const KvMaps &m, cudaStream_t s);
+cudaError_t launch_split_d64(bool bf16, int kvq, int heads, const SplitParams &p, const KvMaps &m, cudaStream_t s);
+cudaError_t launch_split_d96(bool bf16, int kvq, int heads, const SplitParams &p, const KvMaps &m, cudaStream_t s);
+cudaError_t launch_split_d128(bool bf16, int kvq, int heads, const SplitParams &p, const KvMaps &m, cudaStream_t s);
+cudaError_t launch_split_d256(bool bf16, int kvq, int heads, const SplitParams &p, const KvMaps &m, cudaStream_t s);
 cudaError_t launch_split_mla_simt(bool bf16, int heads, const SplitParams &p, const KvMaps &m, cudaStream_t s);
 SplitVariantInfo split_info_d64(int heads);
 SplitVariantInfo split_info_d96(int heads);

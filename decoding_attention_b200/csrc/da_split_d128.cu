@@ -13,24 +13,28 @@
 namespace da {
 namespace {
 // lanes per key row, keys per lane-group and tile, consumer warps, pipeline stages
-template <typename T, int G, int KPT, bool FP8 = false>
-using Cfg = SplitCfg<T, 128, 128, 16, G, KPT, 4, DA_D128_STAGES, false, DA_D128_MINB, FP8>;
+template <typename T, int G, int KPT, int KVQ = 0>
+using Cfg = SplitCfg<T, 128, 128, 16, G, KPT, 4, DA_D128_STAGES, false, DA_D128_MINB, KVQ>;
 
-template <typename T, bool FP8>
+template <typename T, int KVQ>
 cudaError_t launch_t(int heads, const SplitParams &p, const KvMaps &m, cudaStream_t s) {
     switch (heads) {
-        case 1: return launch_split<Cfg<T, 1, DA_D128_KPT, FP8>>(p, m.k, m.v, s);
-        case 2: return launch_split<Cfg<T, 2, DA_D128_KPT, FP8>>(p, m.k, m.v, s);
-        case 4: return launch_split<Cfg<T, 4, DA_D128_KPT, FP8>>(p, m.k, m.v, s);
+        case 1: return launch_split<Cfg<T, 1, DA_D128_KPT, KVQ>>(p, m.k, m.v, s);
+        case 2: return launch_split<Cfg<T, 2, DA_D128_KPT, KVQ>>(p, m.k, m.v, s);
+        case 4: return launch_split<Cfg<T, 4, DA_D128_KPT, KVQ>>(p, m.k, m.v, s);
         default: return cudaErrorInvalidValue;
     }
 }
 }  // namespace
 
-// fp8: K and V are FP8 e4m3 bytes (q and o stay 16-bit)
-cudaError_t launch_split_d128(bool bf16, bool fp8, int heads, const SplitParams &p, const KvMaps &m, cudaStream_t s) {
-    if (fp8) return bf16 ? launch_t<__nv_bfloat16, true>(heads, p, m, s) : launch_t<__half, true>(heads, p, m, s);
-    return bf16 ? launch_t<__nv_bfloat16, false>(heads, p, m, s) : launch_t<__half, false>(heads, p, m, s);
+// kvq: how K and V are stored (0 as q, 1 FP8 e4m3, 2 int8, 3 int4); q and o stay 16-bit
+cudaError_t launch_split_d128(bool bf16, int kvq, int heads, const SplitParams &p, const KvMaps &m, cudaStream_t s) {
+    switch (kvq) {
+        case 1: return bf16 ? launch_t<__nv_bfloat16, 1>(heads, p, m, s) : launch_t<__half, 1>(heads, p, m, s);
+        case 2: return bf16 ? launch_t<__nv_bfloat16, 2>(heads, p, m, s) : launch_t<__half, 2>(heads, p, m, s);
+        case 3: return bf16 ? launch_t<__nv_bfloat16, 3>(heads, p, m, s) : launch_t<__half, 3>(heads, p, m, s);
+        default: return bf16 ? launch_t<__nv_bfloat16, 0>(heads, p, m, s) : launch_t<__half, 0>(heads, p, m, s);
+    }
 }
 
 SplitVariantInfo split_info_d128(int heads) {

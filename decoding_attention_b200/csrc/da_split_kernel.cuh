@@ -22,14 +22,15 @@
 
 namespace da {
 
-// FP8_: K and V hold one-byte FP8 e4m3 values (q and o keep the 16-bit type T); a lane then owns 8-byte chunks.
+// KVQ_: how K and V are stored (q and o keep the 16-bit type T): 0 = as T, 1 = FP8 e4m3 bytes, 2 = signed 8-bit
+// integers, 3 = signed 4-bit integers, two per byte (low nibble first).  A lane always owns eight elements at a time.
 template <typename T_, int D_, int DV_, int LANES_, int G_, int KPT_, int NWARPS_, int STAGES_, bool MLA_, int MINB_ = 1,
-          bool FP8_ = false>
+          int KVQ_ = 0>
 struct SplitCfg {
     using T = T_;
-    static constexpr bool FP8 = FP8_;
-    static constexpr int KV_BYTES = FP8_ ? 1 : 2;      // bytes per K / V element
-    static constexpr int CHUNK_BYTES = 8 * KV_BYTES;   // eight elements: what one lane reads at a time
+    static constexpr int KVQ = KVQ_;
+    static constexpr int KV_BITS = KVQ_ == 0 ? 16 : (KVQ_ == 3 ? 4 : 8);  // bits per K / V element
+    static constexpr int CHUNK_BYTES = KV_BITS;        // eight elements: what one lane reads at a time
     static constexpr int D = D_, DV = DV_, LANES = LANES_, G = G_, KPT = KPT_, NWARPS = NWARPS_, STAGES = STAGES_;
     static constexpr bool MLA = MLA_;
     static constexpr int MINB = MINB_;             // resident CTAs per SM the register budget must allow              // V is the first DV elements of each K row
@@ -41,7 +42,7 @@ struct SplitCfg {
     static constexpr int NV = KPT * G;             // scores per group per tile
     static constexpr int RV = NV >= LANES ? NV / LANES : 1;   // scores a lane holds after the reduce-scatter
     static constexpr int REP = NV >= LANES ? 1 : LANES / NV;  // lanes holding the same score
-    static constexpr int K_ROW_BYTES = D * KV_BYTES, V_ROW_BYTES = DV * KV_BYTES;
+    static constexpr int K_ROW_BYTES = D * KV_BITS / 8, V_ROW_BYTES = DV * KV_BITS / 8;
     static constexpr int K_TILE_BYTES = TILE * K_ROW_BYTES;
     static constexpr int V_TILE_BYTES = MLA ? 0 : TILE * V_ROW_BYTES;
     static constexpr int THREADS = (NWARPS + 1) * 32;
@@ -216,9 +217,9 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
 
     if (warp == C::NWARPS) {
         // ---------------- producer warp ----------------
-        constexpr int EB = C::KV_BYTES;  // element size of the cache
-        const uint8_t *kg = reinterpret_cast<const uint8_t *>(p.k) + (size_t)hk * D * EB;
-        const uint8_t *vg = reinterpret_cast<const uint8_t *>(p.v) + (size_t)hk * (C::MLA ? D : DV) * EB;
+        constexpr int EBITS = C::KV_BITS;  // element size of the cache, in bits (strides count elements)
+        const uint8_t *kg = reinterpret_cast<const uint8_t *>(p.k) + (size_t)hk * D * EBITS / 8;
+        const uint8_t *vg = reinterpret_cast<const uint8_t *>(p.v) + (size_t)hk * (C::MLA ? D : DV) * EBITS / 8;
         if (p.use_tmap && lane == 0) {
             tma_prefetch_desc(&tm_k);
             if (!C::MLA) tma_prefetch_desc(&tm_v);
@@ -244,10 +245,10 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
             if (short_pages) {
                 load_tile_short_pages(p.block_table, p.block_table_stride, p.page_shift, b, key0, rows, TILE, whole,
                                       ks + st * C::K_TILE_BYTES, C::K_ROW_BYTES, &tm_k, hk, kg,
-                                      p.k_row_stride * (long long)EB, &full_k[st], lane);
+                                      p.k_row_stride * (long long)EBITS / 8, &full_k[st], lane);
             } else if (!whole) {
                 for (int r = lane; r < rows; r += 32) {
-                    bulk_copy_g2s(ks + st * C::K_TILE_BYTES + r * C::K_ROW_BYTES, kg + (tok0 + r) * p.k_row_stride * EB,
+                    bulk_copy_g2s(ks + st * C::K_TILE_BYTES + r * C::K_ROW_BYTES, kg + (tok0 + r) * p.k_row_stride * EBITS / 8,
                                   C::K_ROW_BYTES, &full_k[st]);
                 }
             }
@@ -263,11 +264,11 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
                 if (short_pages) {
                     load_tile_short_pages(p.block_table, p.block_table_stride, p.page_shift, b, key0, rows, TILE, whole,
                                           vs + st * C::V_TILE_BYTES, C::V_ROW_BYTES, &tm_v, hk, vg,
-                                          p.v_row_stride * (long long)EB, &full_v[st], lane);
+                                          p.v_row_stride * (long long)EBITS / 8, &full_v[st], lane);
                 } else if (!whole) {
                     for (int r = lane; r < rows; r += 32) {
                         bulk_copy_g2s(vs + st * C::V_TILE_BYTES + r * C::V_ROW_BYTES,
-                                      vg + (tok0 + r) * p.v_row_stride * EB, C::V_ROW_BYTES, &full_v[st]);
+                                      vg + (tok0 + r) * p.v_row_stride * EBITS / 8, C::V_ROW_BYTES, &full_v[st]);
                     }
                 }
             }
@@ -351,7 +352,7 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
 #pragma unroll
             for (int n = 0; n < NCH; ++n) {
                 float kf[8];
-                load_chunk8<T, C::FP8>(kt + kl * C::K_ROW_BYTES + (c + n * LANES) * C::CHUNK_BYTES, kf);
+                load_chunk8<T, C::KVQ>(kt + kl * C::K_ROW_BYTES + (c + n * LANES) * C::CHUNK_BYTES, kf);
 #pragma unroll
                 for (int g = 0; g < G; ++g) {
 #pragma unroll
@@ -433,7 +434,7 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
 #pragma unroll
                 for (int n = 0; n < NCHV; ++n) {
                     float vf[8];
-                    load_chunk8<T, C::FP8>(vt + kl * VROW + (c + n * LANES) * C::CHUNK_BYTES, vf);
+                    load_chunk8<T, C::KVQ>(vt + kl * VROW + (c + n * LANES) * C::CHUNK_BYTES, vf);
 #pragma unroll
                     for (int g = 0; g < G; ++g) {
 #pragma unroll

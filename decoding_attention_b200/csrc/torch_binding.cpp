@@ -45,7 +45,9 @@ Outputs run(const at::Tensor &q, const at::Tensor &k, const std::optional<at::Te
     const bool is_bf16 = q_dtype == torch::kBFloat16;
     // An FP8 e4m3 cache (k and v both) is an extension; the reference requires the dtype of q
     // (csrc/torch/decoding_torch.cpp:28, :57).
-    const bool fp8_cache = k.scalar_type() == at::kFloat8_e4m3fn;
+    // A quantised cache (k and v both) is an extension: FP8 e4m3, or int8 (torch.int8); int4 goes through the C ABI.
+    const bool int8_cache = k.scalar_type() == at::kChar;
+    const bool fp8_cache = k.scalar_type() == at::kFloat8_e4m3fn || int8_cache;
     TORCH_CHECK(fp8_cache || k.dtype() == q_dtype, "query and key must have the same dtype");
     TORCH_CHECK(cu_seq_k.dtype() == torch::kInt32, "cu_seq_k must have dtype int32");
 
@@ -91,7 +93,7 @@ Outputs run(const at::Tensor &q, const at::Tensor &k, const std::optional<at::Te
 
     if (v_.has_value()) {
         const at::Tensor &v = v_.value();
-        TORCH_CHECK(v.dtype() == k.dtype(), fp8_cache ? "key and value must both be FP8" : "query and value must have the same dtype");
+        TORCH_CHECK(v.dtype() == k.dtype(), fp8_cache ? "key and value must have the same quantised dtype" : "query and value must have the same dtype");
         DA_CHECK_DEVICE(v);
         TORCH_CHECK(v.device() == q.device(), "all tensors must be on one device");
         TORCH_CHECK(v.stride(-1) == 1, "value must have contiguous last dimension");
@@ -130,8 +132,8 @@ Outputs run(const at::Tensor &q, const at::Tensor &k, const std::optional<at::Te
     a.softmax_scale = softmax_scale.has_value() ? (float)softmax_scale.value() : 0.0f;
     a.stream = stream;
     if (fp8_cache) {
-        TORCH_CHECK(v_.has_value(), "an FP8 cache needs a value tensor");
-        a.kv_dtype = DA_KV_FP8_E4M3;
+        TORCH_CHECK(v_.has_value(), "a quantised cache needs a value tensor");
+        a.kv_dtype = int8_cache ? DA_KV_INT8 : DA_KV_FP8_E4M3;
         a.k_scale = (float)k_scale;
         a.v_scale = (float)v_scale;
     }

@@ -83,17 +83,19 @@ typedef struct da_decode_args {
     int64_t block_table_stride; /* elements per row, >= ceil(longest sequence / page_size) */
     int32_t page_size;
 
-    /* Quantised cache (optional).  kv_dtype 0: k and v hold the type of q (the reference's only case);
-     * DA_KV_FP8_E4M3: k and v hold one-byte FP8 e4m3 values and stand for k * k_scale and v * v_scale
-     * (one scale per tensor; <= 0 selects 1).  q, o and all arithmetic stay as they are; strides and
-     * dims still count elements.  Supported with v given and (dim, dim_v) one of (64,64) (96,96)
-     * (128,128) (256,256); the latent-KV shape returns DA_ERR_UNSUPPORTED.  The reference lists KV-cache
-     * quantisation as not done (README.md:154-156). */
+    /* Quantised cache (optional).  kv_dtype 0: k and v hold the type of q (the reference's only case).
+     * DA_KV_FP8_E4M3 / DA_KV_INT8: one byte per element (FP8 e4m3, or a signed 8-bit integer);
+     * DA_KV_INT4: signed 4-bit integers, two per byte, the element with the even index in the low nibble.
+     * The tensors stand for k * k_scale and v * v_scale (one scale per tensor; <= 0 selects 1).  q, o
+     * and all arithmetic stay as they are; strides and dims still count elements (row strides: multiples
+     * of 16 bytes).  Supported with v given and (dim, dim_v) one of (64,64) (96,96) (128,128) (256,256);
+     * the latent-KV shape returns DA_ERR_UNSUPPORTED.  The reference lists KV-cache quantisation as not
+     * done (README.md:154-156). */
     int32_t kv_dtype;
     float k_scale, v_scale;
 } da_decode_args_t;
 
-enum { DA_KV_SAME_AS_Q = 0, DA_KV_FP8_E4M3 = 1 };
+enum { DA_KV_SAME_AS_Q = 0, DA_KV_FP8_E4M3 = 1, DA_KV_INT8 = 2, DA_KV_INT4 = 3 };
 
 /* Runs decode attention.  Stands in for decoding_attn() (csrc/ops/decoding_attn.h:29-30,
  * csrc/ops/decoding_attn.cpp:70-76) and everything below it: run_dmha_fwd / DA_FP16_SWITCH /

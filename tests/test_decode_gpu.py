@@ -464,3 +464,46 @@ def test_head_dim_96_large_groups(native_lib, oracle, hq, hk, dt):
                                                    is_alibi=True, block_table=table.to(DEV), page_size=page))
         torch.cuda.synchronize()
         assert_close(o, expect, f"{w.name} paged {page}")
+
+
+def quantise_int(x, scale, bits):
+    """(stored tensor, dequantised tensor in x's dtype) for signed `bits`-bit integers with one scale per tensor.
+    8 bits: torch.int8.  4 bits: torch.uint8 of half the last dimension, the even element in the low nibble.
+    Integers up to 127 times a power-of-two scale are exact in fp16 and bf16."""
+    lim = (1 << (bits - 1)) - 1
+    qi = torch.round(x.float() / scale).clamp(-lim - 1, lim).to(torch.int32)
+    deq = (qi.float() * scale).to(x.dtype)
+    if bits == 8:
+        return qi.to(torch.int8), deq
+    lo, hi = qi[..., 0::2] & 0xF, qi[..., 1::2] & 0xF
+    return (lo | (hi << 4)).to(torch.uint8), deq
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("dt,hq,hk,d,lens,alibi,splits", [
+    (torch.bfloat16, 32, 8, 128, [700, 64, 1, 129, 0], False, 0),
+    (torch.float16, 32, 8, 128, [2100, 333], True, 3),
+    (torch.bfloat16, 16, 4, 64, [333, 1000], False, 2),
+    (torch.float16, 12, 4, 96, [257, 31], True, 0),
+    (torch.bfloat16, 8, 2, 256, [100, 400], False, 0),
+    (torch.float16, 32, 1, 128, [300, 65], False, 0),
+])
+def test_integer_kv_cache(native_lib, oracle, bits, dt, hq, hk, d, lens, alibi, splits):
+    """Signed 8-bit and 4-bit K / V with per-tensor scales, against the oracle on the dequantised cache."""
+    w = synth.Workload(f"int{bits}_{d}_{hq}_{hk}", dt, hq, hk, d, d, lens, is_alibi=alibi, dist="normal", scale=0.5, seed=85)
+    q, k, v, cu = w.make("cpu")
+    ks, vs = (2.0 ** -6, 2.0 ** -5) if bits == 8 else (0.25, 0.5)
+    kq, k_deq = quantise_int(k, ks, bits)
+    vq, v_deq = quantise_int(v, vs, bits)
+    expect, lse_e = oracle.attn_cpu(q, k_deq, v_deq, cu, dim_v=d, is_alibi=alibi, return_lse=True)
+    o = torch.full((len(lens), hq, d), float("nan"), dtype=dt, device=DEV)
+    lse = torch.empty(len(lens), hq, dtype=torch.float32, device=DEV)
+    args = native_lib.make_args(q.to(DEV), kq.to(DEV), vq.to(DEV), o, cu.to(DEV), max(w.max_seq_k, 1), d, is_alibi=alibi,
+                                lse=lse, num_splits=splits, k_scale=ks, v_scale=vs, int4=(bits == 4))
+    assert args.kv_dtype == (2 if bits == 8 else 3)
+    native_lib.decode_fwd(args)
+    torch.cuda.synchronize()
+    assert native_lib.device_status() == native_lib.DA_OK
+    assert_close(o, expect, w.name)
+    fin = torch.isfinite(lse_e)
+    assert (lse.cpu()[fin] - lse_e[fin]).abs().max().item() <= 2e-3
