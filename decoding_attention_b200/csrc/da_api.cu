@@ -73,7 +73,7 @@ int device_state(DeviceState **out) {
     return DA_OK;
 }
 
-enum class Shape { kD64, kD96, kD128, kD256, kMla, kMlaTc, kMla2Sm, kGqaTc, kNone };
+enum class Shape { kD64, kD96, kD128, kD256, kMla, kMla2Sm, kGqaTc, kNone };
 
 Shape shape_of(int64_t dim, int64_t dim_v, bool has_v) {
     if (has_v) {
@@ -90,20 +90,15 @@ Shape shape_of(int64_t dim, int64_t dim_v, bool has_v) {
 // Environment overrides, read once per process (the reference has none; these exist for benchmarks):
 //   DA_NUM_SPLITS=<n>   key-range splits per sequence when the caller leaves num_splits at 0
 //   DA_KERNEL=simt      keep every shape on the CUDA-core kernel (no tensor-core path)
-//   DA_KERNEL=mla1sm    latent-KV shape on the one-SM-per-CTA tensor-core kernel instead of SM pairs
 struct EnvOverrides {
     int num_splits = 0;
     bool force_simt = false;
-    bool mla_1sm = false;
 };
 const EnvOverrides &env_overrides() {
     static const EnvOverrides env = [] {
         EnvOverrides e;
         if (const char *s = getenv("DA_NUM_SPLITS")) e.num_splits = atoi(s) > 0 ? atoi(s) : 0;
-        if (const char *k = getenv("DA_KERNEL")) {
-            e.force_simt = strcmp(k, "simt") == 0;
-            e.mla_1sm = strcmp(k, "mla1sm") == 0;
-        }
+        if (const char *k = getenv("DA_KERNEL")) e.force_simt = strcmp(k, "simt") == 0;
         return e;
     }();
     return env;
@@ -135,7 +130,7 @@ bool gqa_on_tensor_cores(const da_decode_args_t &a) {
 int heads_per_cta(Shape s, int group) {
     if (s == Shape::kMla) return 1;
     if (s == Shape::kGqaTc) return group;
-    if (s == Shape::kMlaTc || s == Shape::kMla2Sm) return group;  // all heads of the KV head in one CTA / CTA pair
+    if (s == Shape::kMla2Sm) return group;  // all heads of the KV head in one CTA / CTA pair
     if (group % 4 == 0) return 4;
     if (group % 2 == 0) return 2;
     return 1;
@@ -149,7 +144,6 @@ SplitVariantInfo variant_info(Shape s, int heads) {
         case Shape::kD256: return split_info_d256(heads);
         case Shape::kMla: return split_info_mla_simt(heads);
         case Shape::kGqaTc: return split_info_gqa_tc();
-        case Shape::kMlaTc: return split_info_mla_tc();
         case Shape::kMla2Sm: return split_info_mla_2sm();
         default: return {0, 0, 0};
     }
@@ -279,9 +273,7 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
             return fail(DA_ERR_UNSUPPORTED, "a quantised cache is supported for (dim, dim_v) (64,64) (96,96) (128,128) (256,256) with v given");
         }
     } else if (shape == Shape::kMla && mla_on_tensor_cores(a)) {
-        // SM pairs (cta_group::2) unless the cache is paged in pages shorter than the keys one CTA stages at a time
-        const int half_tile = split_info_mla_2sm().tile_keys / 2;
-        shape = (!a.block_table || a.page_size >= half_tile) && !env_overrides().mla_1sm ? Shape::kMla2Sm : Shape::kMlaTc;
+        shape = Shape::kMla2Sm;
     }
     if (a.kv_dtype == DA_KV_SAME_AS_Q &&
         (shape == Shape::kD64 || shape == Shape::kD96 || shape == Shape::kD128 || shape == Shape::kD256) &&
@@ -293,8 +285,8 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
     const SplitVariantInfo info = variant_info(shape, heads);
     const int tile = info.tile_keys;
     // The tensor-core MLA kernel runs two CTAs (one per half of the output columns) per key range.
-    // The tensor-core MLA kernels run two CTAs per key range: apart (each one half of the output columns), or as a pair.
-    const int64_t units = shape == Shape::kMlaTc ? a.batch * 2 : shape == Shape::kMla2Sm ? a.batch : a.batch * a.head_k * (group / heads);
+    // The tensor-core MLA kernel runs one pair of CTAs (two SMs) per key range.
+    const int64_t units = shape == Shape::kMla2Sm ? a.batch : a.batch * a.head_k * (group / heads);
     const int64_t max_len = a.max_seq_k > 0 ? a.max_seq_k : 1;
     const int64_t tiles_per_unit = (max_len + tile - 1) / tile;
 
@@ -305,7 +297,7 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
         splits = a.num_splits;
     } else if (env_overrides().num_splits > 0) {
         splits = env_overrides().num_splits;
-    } else if (shape == Shape::kMlaTc || shape == Shape::kMla2Sm || shape == Shape::kGqaTc) {
+    } else if (shape == Shape::kMla2Sm || shape == Shape::kGqaTc) {
         // One CTA per SM and long-running CTAs: pick the split count whose CTA total fills whole
         // waves best, weighed against the fixed cost of every extra CTA.
         const int64_t slots = shape == Shape::kMla2Sm ? sm_count / 2 : sm_count;
@@ -556,8 +548,7 @@ int da_decode_fwd(const da_decode_args_t *a) {
     memset(&maps, 0, sizeof(maps));
     // Tiled TMA needs a global stride that is a multiple of 16 bytes (checked above: 8 elements) and
     // a box of at most 256 elements per dimension; the latent-KV rows (576) keep the row-wise path.
-    p.use_tmap = (plan.shape != Shape::kMla) && (plan.shape != Shape::kMlaTc) && (plan.shape != Shape::kMla2Sm) &&
-                 (plan.shape != Shape::kGqaTc);
+    p.use_tmap = (plan.shape != Shape::kMla) && (plan.shape != Shape::kMla2Sm) && (plan.shape != Shape::kGqaTc);
     CUtensorMap tm_q;
     memset(&tm_q, 0, sizeof(tm_q));
     if (plan.shape == Shape::kGqaTc) {
@@ -588,21 +579,9 @@ int da_decode_fwd(const da_decode_args_t *a) {
         if (rc != DA_OK) return rc;
         const uint64_t kd[2] = {576, kMapRows};
         const uint64_t ks[1] = {(uint64_t)p.k_row_stride * 2};
-        const uint32_t kb[2] = {64, (uint32_t)(plan.tile_keys / 2)};  // one CTA's keys of a tile
-        rc = make_tensor_map(p.k, 2, kd, ks, kb, true, bf16 ? 1 : 0, &maps.v);
-        if (rc != DA_OK) return rc;
-    }
-    if (plan.shape == Shape::kMlaTc) {
-        // q as [batch][128][576] in boxes {64, 128, 1}; the latent cache as [rows][576] in boxes
-        // {64, tile}; both land 128-byte-swizzled, the layout the UMMA descriptors name.
-        const uint64_t qd[3] = {576, (uint64_t)a->head_q, (uint64_t)a->batch};
-        const uint64_t qs[2] = {576 * 2, (uint64_t)p.q_row_stride * 2};
-        const uint32_t qb[3] = {64, (uint32_t)a->head_q, 1};  // head_q <= 128 rows
-        rc = make_tensor_map(p.q, 3, qd, qs, qb, true, bf16 ? 1 : 0, &maps.k);
-        if (rc != DA_OK) return rc;
-        const uint64_t kd[2] = {576, kMapRows};
-        const uint64_t ks[1] = {(uint64_t)p.k_row_stride * 2};
-        const uint32_t kb[2] = {64, (uint32_t)box_keys};
+        // one CTA's keys of a tile, or a page when pages are shorter
+        const uint32_t half = (uint32_t)(plan.tile_keys / 2);
+        const uint32_t kb[2] = {64, (a->block_table && (uint32_t)a->page_size < half) ? (uint32_t)a->page_size : half};
         rc = make_tensor_map(p.k, 2, kd, ks, kb, true, bf16 ? 1 : 0, &maps.v);
         if (rc != DA_OK) return rc;
     }
@@ -624,7 +603,6 @@ int da_decode_fwd(const da_decode_args_t *a) {
         case Shape::kD256: e = launch_split_d256(bf16, kvq, plan.heads, p, maps, stream); break;
         case Shape::kMla: e = launch_split_mla_simt(bf16, plan.heads, p, maps, stream); break;
         case Shape::kGqaTc: e = launch_gqa_tc(bf16, a->dim == 96 ? 128 : (int)a->dim, p, tm_q, maps.k, maps.v, stream); break;
-        case Shape::kMlaTc: e = launch_mla_tc(bf16, p, maps.k, maps.v, stream); break;
         case Shape::kMla2Sm: e = launch_mla_2sm(bf16, p, maps.k, maps.v, stream); break;
         default: e = cudaErrorInvalidValue; break;
     }

@@ -33,15 +33,10 @@ SplitVariantInfo split_info_d128(int heads);
 SplitVariantInfo split_info_d256(int heads);
 SplitVariantInfo split_info_mla_simt(int heads);
 
-// Tensor-core (tcgen05 / TMEM) kernel for 128 query heads over one latent KV head (da_mla_sm100.cu).
-// tm_q: rank-3 map of q, box {64, 128, 1}; tm_k: rank-2 map of the latent cache, box {64, tile keys};
+// Tensor-core (tcgen05 / TMEM) kernel for up to 128 query heads over one latent KV head, on SM pairs
+// (da_mla_2sm_sm100.cu): clusters of two CTAs issue cta_group::2 MMAs, each CTA
+// holding 64 of the 128 head rows.  tm_q: box {64, min(64, head_q), 1}; tm_k: box {64, 64 keys or a shorter page};
 // both with the 128-byte swizzle.
-cudaError_t launch_mla_tc(bool bf16, const SplitParams &p, const CUtensorMap &tm_q, const CUtensorMap &tm_k,
-                          cudaStream_t s);
-SplitVariantInfo split_info_mla_tc();
-// The same shape on SM pairs (da_mla_2sm_sm100.cu): clusters of two CTAs issue cta_group::2 MMAs, each CTA
-// holding 64 of the 128 head rows.  tm_q: box {64, min(64, head_q), 1}; tm_k: box {64, 64 keys}.  Needs a
-// packed cache or pages of at least 64 keys.
 cudaError_t launch_mla_2sm(bool bf16, const SplitParams &p, const CUtensorMap &tm_q, const CUtensorMap &tm_k,
                            cudaStream_t s);
 SplitVariantInfo split_info_mla_2sm();

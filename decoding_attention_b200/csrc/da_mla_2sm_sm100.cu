@@ -107,7 +107,10 @@ static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 static_assert(128 * (256 * 4 + 16) <= kOffP - kOffA, "the epilogue stages its output in the idle rings");
 constexpr float kRescaleThreshold = 8.0f;
 
-template <typename T>
+// kShortPages: the cache is paged in pages shorter than the kHalf keys one CTA stages at a time; a block is then
+// fetched page by page (one TMA box per page) and the V loaders look every row's page up.  A separate
+// instantiation, so that the common case keeps its straight-line address arithmetic.
+template <typename T, bool kShortPages>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k) {
     extern __shared__ uint8_t smem_raw[];
@@ -224,6 +227,9 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             const int key0 = k_begin + t * kTile + (int)rank * kHalf;  // this CTA's first key of the tile
             const int rows = max(0, min(kHalf, k_end - key0));
             const size_t tok0 = rows > 0 ? kv_tile_row(p, b, seq_begin, key0) : 0;
+            // rows of the tile are consecutive in the cache, except across the pages of a short-page cache
+            auto row_of = [&](int r) { return kShortPages ? kv_tile_row(p, b, seq_begin, key0 + r) : tok0 + r; };
+            const int run = kShortPages ? (1 << p.page_shift) : kHalf;  // consecutive rows: a page, or the whole half tile
             for (int j = 0; j < kBlocks && ok; ++j) {
                 if (round > 0) ok = mbar_wait(&a_empty[slot], (round & 1u) ^ 1u, abort_flag);
                 if (!ok) break;
@@ -235,7 +241,8 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
                 if (rows == kHalf) {
                     if (lane == 0) {
                         if (rank == 0) mbar_arrive_expect_tx(&a_full[slot], 2 * kKBlockBytes);
-                        tma2_load_2d(dst, &tm_k, j * 64, (int)tok0, lead(&a_full[slot]));
+                        for (int k0 = 0; k0 < kHalf; k0 += run)
+                            tma2_load_2d(dst + k0 * 128, &tm_k, j * 64, (int)row_of(k0), lead(&a_full[slot]));
                     }
                 } else {
                     // ragged end of the key range: plain loads, rows past the end zeroed (the tensor map
@@ -243,7 +250,7 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
                     for (int i = lane; i < kHalf * 8; i += 32) {
                         const int r = i >> 3, cc = i & 7;
                         uint4 v = make_uint4(0, 0, 0, 0);
-                        if (r < rows) v = *reinterpret_cast<const uint4 *>(k_g + (tok0 + r) * p.k_row_stride + j * 64 + cc * 8);
+                        if (r < rows) v = *reinterpret_cast<const uint4 *>(k_g + row_of(r) * p.k_row_stride + j * 64 + cc * 8);
                         *reinterpret_cast<uint4 *>(dst + r * 128 + ((cc ^ (r & 7)) << 4)) = v;
                     }
                     fence_proxy_async();
@@ -365,12 +372,17 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             if (ok && i >= kVSlots - kQStageSlots && i < kVSlots) ok = mbar_wait(q_copied, 0, abort_flag);  // the slot staged Q blocks
             if (!ok) break;
             uint8_t *slot = v_s + vs * kVSlotBytes;
+            // thread lt copies the 16-byte chunk (lt & 7) of rows (lt >> 3) + 16 i for each of the four blocks
 #pragma unroll
-            for (int n = 0; n < kVBlocks * kHalf * 8 / kLoaderThreads; ++n) {
-                const int e = lt + n * kLoaderThreads;
-                const int j = e / (kHalf * 8), r = (e >> 3) % kHalf, cc = e & 7;
-                const T *src = k_g + (tok0 + max(0, min(r, rows - 1))) * p.k_row_stride + ((int)rank * kVBlocks + j) * 64 + cc * 8;
-                cp_async16(slot + j * kKBlockBytes + r * 128 + ((cc ^ (r & 7)) << 4), src, r < rows ? 16u : 0u);  // 0: zero fill
+            for (int ri = 0; ri < kHalf / 16; ++ri) {
+                const int r = (lt >> 3) + 16 * ri, cc = lt & 7;
+                const int rr = max(0, min(r, rows - 1));
+                const size_t trow = kShortPages ? (rows > 0 ? kv_tile_row(p, b, seq_begin, key0 + rr) : 0) : tok0 + rr;
+                const T *src = k_g + trow * p.k_row_stride + (int)rank * kVBlocks * 64 + cc * 8;
+#pragma unroll
+                for (int j = 0; j < kVBlocks; ++j) {
+                    cp_async16(slot + j * kKBlockBytes + r * 128 + ((cc ^ (r & 7)) << 4), src + j * 64, r < rows ? 16u : 0u);  // 0: zero fill
+                }
             }
             cp_async_commit();
             if (i >= 1) {  // the half-tile issued one iteration ago has landed: publish it to the tensor pipe
@@ -623,7 +635,7 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
 SplitVariantInfo split_info_mla_2sm() { return {kTile, kHeads, 1}; }
 
 // tm_q: rank-3 map over q [batch][head_q][576], box {64, min(64, head_q), 1}; tm_k: rank-2 map over the latent
-// cache [rows][576], box {64, 64 keys}; both with the 128-byte swizzle.  Grid (2, splits, batch) in clusters of
+// cache [rows][576], box {64, half a tile of keys, or a page when pages are shorter}; both with the 128-byte swizzle.  Grid (2, splits, batch) in clusters of
 // two along x: the two CTAs of a key range.
 cudaError_t launch_mla_2sm(bool bf16, const SplitParams &p, const CUtensorMap &tm_q, const CUtensorMap &tm_k,
                            cudaStream_t stream) {
@@ -632,16 +644,24 @@ cudaError_t launch_mla_2sm(bool bf16, const SplitParams &p, const CUtensorMap &t
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
     if (dev < 64 && !attr_set[dev]) {
-        err = cudaFuncSetAttribute(da_mla_2sm_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (err != cudaSuccess) return err;
-        err = cudaFuncSetAttribute(da_mla_2sm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (err != cudaSuccess) return err;
+        const void *kernels[4] = {(const void *)da_mla_2sm_kernel<__half, false>, (const void *)da_mla_2sm_kernel<__half, true>,
+                                  (const void *)da_mla_2sm_kernel<__nv_bfloat16, false>,
+                                  (const void *)da_mla_2sm_kernel<__nv_bfloat16, true>};
+        for (const void *k : kernels) {
+            err = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+            if (err != cudaSuccess) return err;
+        }
         attr_set[dev] = true;
     }
     dim3 grid(2, p.num_splits, p.batch);
     const bool overlap = p.batch_order != nullptr;
-    return bf16 ? launch_kernel(da_mla_2sm_kernel<__nv_bfloat16>, grid, kThreads, kSmemBytes, stream, overlap, p, tm_q, tm_k)
-                : launch_kernel(da_mla_2sm_kernel<__half>, grid, kThreads, kSmemBytes, stream, overlap, p, tm_q, tm_k);
+    const bool short_pages = p.block_table && (1 << p.page_shift) < kHalf;
+    if (bf16) {
+        return short_pages ? launch_kernel(da_mla_2sm_kernel<__nv_bfloat16, true>, grid, kThreads, kSmemBytes, stream, overlap, p, tm_q, tm_k)
+                           : launch_kernel(da_mla_2sm_kernel<__nv_bfloat16, false>, grid, kThreads, kSmemBytes, stream, overlap, p, tm_q, tm_k);
+    }
+    return short_pages ? launch_kernel(da_mla_2sm_kernel<__half, true>, grid, kThreads, kSmemBytes, stream, overlap, p, tm_q, tm_k)
+                       : launch_kernel(da_mla_2sm_kernel<__half, false>, grid, kThreads, kSmemBytes, stream, overlap, p, tm_q, tm_k);
 }
 
 }  // namespace da
