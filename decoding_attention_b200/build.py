@@ -26,7 +26,7 @@ NVCC_FLAGS = ["-std=c++17", "-O3", "--use_fast_math", "-gencode", "arch=compute_
               "-Xcompiler", "-fPIC", "-ccbin", CXX]
 
 CUDA_SOURCES = ["da_api.cu", "da_merge.cu", "da_split_d64.cu", "da_split_d96.cu", "da_split_d128.cu",
-                "da_split_d256.cu", "da_split_mla_simt.cu", "da_mla_2sm_sm100.cu", "da_gqa_tc_sm100.cu", "da_xmerge.cu", "da_noalloc.cu", "da_order.cu"]
+                "da_split_d256.cu", "da_split_mla_simt.cu", "da_mla_2sm_sm100.cu", "da_gqa_tc_sm100.cu", "da_gqa_quad_sm100.cu", "da_xmerge.cu", "da_noalloc.cu", "da_order.cu"]
 CXX_SOURCES = ["decoding_attn.cpp"]
 HEADERS = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))] + [
     os.path.join(ROOT, "include", "decoding_attn_b200.h"), os.path.join(ROOT, "include", "decoding_attn.h")]

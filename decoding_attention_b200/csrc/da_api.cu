@@ -73,7 +73,7 @@ int device_state(DeviceState **out) {
     return DA_OK;
 }
 
-enum class Shape { kD64, kD96, kD128, kD256, kMla, kMla2Sm, kGqaTc, kNone };
+enum class Shape { kD64, kD96, kD128, kD256, kMla, kMla2Sm, kGqaTc, kGqaQuad, kNone };
 
 Shape shape_of(int64_t dim, int64_t dim_v, bool has_v) {
     if (has_v) {
@@ -93,12 +93,14 @@ Shape shape_of(int64_t dim, int64_t dim_v, bool has_v) {
 struct EnvOverrides {
     int num_splits = 0;
     bool force_simt = false;
+    bool no_quad = false;  // development switch (DA_KERNEL=gqa1): small groups stay on the one-stream-pair kernel
 };
 const EnvOverrides &env_overrides() {
     static const EnvOverrides env = [] {
         EnvOverrides e;
         if (const char *s = getenv("DA_NUM_SPLITS")) e.num_splits = atoi(s) > 0 ? atoi(s) : 0;
         if (const char *k = getenv("DA_KERNEL")) e.force_simt = strcmp(k, "simt") == 0;
+        if (const char *k = getenv("DA_KERNEL")) e.no_quad = strcmp(k, "gqa1") == 0;
         return e;
     }();
     return env;
@@ -129,7 +131,7 @@ bool gqa_on_tensor_cores(const da_decode_args_t &a) {
 
 int heads_per_cta(Shape s, int group) {
     if (s == Shape::kMla) return 1;
-    if (s == Shape::kGqaTc) return group;
+    if (s == Shape::kGqaTc || s == Shape::kGqaQuad) return group;
     if (s == Shape::kMla2Sm) return group;  // all heads of the KV head in one CTA / CTA pair
     if (group % 4 == 0) return 4;
     if (group % 2 == 0) return 2;
@@ -144,6 +146,7 @@ SplitVariantInfo variant_info(Shape s, int heads) {
         case Shape::kD256: return split_info_d256(heads);
         case Shape::kMla: return split_info_mla_simt(heads);
         case Shape::kGqaTc: return split_info_gqa_tc();
+        case Shape::kGqaQuad: return split_info_gqa_quad();
         case Shape::kMla2Sm: return split_info_mla_2sm();
         default: return {0, 0, 0};
     }
@@ -279,6 +282,8 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
         (shape == Shape::kD64 || shape == Shape::kD96 || shape == Shape::kD128 || shape == Shape::kD256) &&
         gqa_on_tensor_cores(a)) {
         shape = Shape::kGqaTc;  // (a quantised cache is read by the CUDA-core kernel, whatever the group size)
+        // Up to 32 heads per KV head: four key streams, one per TMEM lane quadrant (head dim 256 has no room for it).
+        if (a.head_q / a.head_k <= 32 && a.dim != 256 && !env_overrides().no_quad) shape = Shape::kGqaQuad;
     }
     const int group = (int)(a.head_q / a.head_k);
     const int heads = heads_per_cta(shape, group);
@@ -297,7 +302,7 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
         splits = a.num_splits;
     } else if (env_overrides().num_splits > 0) {
         splits = env_overrides().num_splits;
-    } else if (shape == Shape::kMla2Sm || shape == Shape::kGqaTc) {
+    } else if (shape == Shape::kMla2Sm || shape == Shape::kGqaTc || shape == Shape::kGqaQuad) {
         // One CTA per SM and long-running CTAs: pick the split count whose CTA total fills whole
         // waves best, weighed against the fixed cost of every extra CTA.
         const int64_t slots = shape == Shape::kMla2Sm ? sm_count / 2 : sm_count;
@@ -548,16 +553,19 @@ int da_decode_fwd(const da_decode_args_t *a) {
     memset(&maps, 0, sizeof(maps));
     // Tiled TMA needs a global stride that is a multiple of 16 bytes (checked above: 8 elements) and
     // a box of at most 256 elements per dimension; the latent-KV rows (576) keep the row-wise path.
-    p.use_tmap = (plan.shape != Shape::kMla) && (plan.shape != Shape::kMla2Sm) && (plan.shape != Shape::kGqaTc);
+    p.use_tmap = (plan.shape != Shape::kMla) && (plan.shape != Shape::kMla2Sm) && (plan.shape != Shape::kGqaTc) &&
+                 (plan.shape != Shape::kGqaQuad);
     CUtensorMap tm_q;
     memset(&tm_q, 0, sizeof(tm_q));
-    if (plan.shape == Shape::kGqaTc) {
-        // q as [batch][head_q][dim] in boxes {64, min(128, head_q), 1}; K and V as [rows][head_k][dim] in
+    if (plan.shape == Shape::kGqaTc || plan.shape == Shape::kGqaQuad) {
+        // q as [batch][head_q][dim] in boxes {64, min(128, head_q), 1} (32 rows for the four-stream kernel, which
+        // stages the group once per row block); K and V as [rows][head_k][dim] in
         // boxes {64, 1, tile}: all 128-byte-swizzled, the layout the UMMA descriptors name.
         const uint64_t dim = (uint64_t)a->dim;  // 64, 96, 128 or 256 (96: boxes at column 64 come back half zero-filled)
         const uint64_t qd[3] = {dim, (uint64_t)a->head_q, (uint64_t)a->batch};
         const uint64_t qs[2] = {dim * 2, (uint64_t)p.q_row_stride * 2};
-        const uint32_t qb[3] = {64, (uint32_t)(a->head_q < 128 ? a->head_q : 128), 1};
+        const uint32_t q_rows = plan.shape == Shape::kGqaQuad ? 32 : 128;
+        const uint32_t qb[3] = {64, (uint32_t)(a->head_q < q_rows ? a->head_q : q_rows), 1};
         rc = make_tensor_map(p.q, 3, qd, qs, qb, true, bf16 ? 1 : 0, &tm_q);
         if (rc != DA_OK) return rc;
         const uint64_t kd[3] = {dim, (uint64_t)a->head_k, kMapRows};
@@ -603,6 +611,7 @@ int da_decode_fwd(const da_decode_args_t *a) {
         case Shape::kD256: e = launch_split_d256(bf16, kvq, plan.heads, p, maps, stream); break;
         case Shape::kMla: e = launch_split_mla_simt(bf16, plan.heads, p, maps, stream); break;
         case Shape::kGqaTc: e = launch_gqa_tc(bf16, a->dim == 96 ? 128 : (int)a->dim, p, tm_q, maps.k, maps.v, stream); break;
+        case Shape::kGqaQuad: e = launch_gqa_quad(bf16, a->dim == 96 ? 128 : (int)a->dim, p, tm_q, maps.k, stream); break;
         case Shape::kMla2Sm: e = launch_mla_2sm(bf16, p, maps.k, maps.v, stream); break;
         default: e = cudaErrorInvalidValue; break;
     }

@@ -44,6 +44,11 @@ SplitVariantInfo split_info_mla_2sm();
 cudaError_t launch_gqa_tc(bool bf16, int dim, const SplitParams &p, const CUtensorMap &tm_q, const CUtensorMap &tm_k,
                           const CUtensorMap &tm_v, cudaStream_t s);
 SplitVariantInfo split_info_gqa_tc();
+// Tensor-core kernel for head dims 64 / 128 and groups of at most 32 query heads per KV head: four key streams,
+// one per TMEM lane quadrant (da_gqa_quad_sm100.cu).  tm_q: box {64, min(32, head_q), 1}.
+cudaError_t launch_gqa_quad(bool bf16, int dim, const SplitParams &p, const CUtensorMap &tm_q, const CUtensorMap &tm_k,
+                            cudaStream_t s);
+SplitVariantInfo split_info_gqa_quad();
 
 // Merge of split / shard partials (da_merge.cu).  cu_seq_k and chunk_keys (both optional) limit a
 // row to the splits that cover keys; without them every part is read.

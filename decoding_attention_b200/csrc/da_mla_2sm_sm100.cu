@@ -95,7 +95,8 @@ constexpr int kOffXch = kOffMisc + 16;                    // float [2][128] tile
 constexpr int kSmemBytes = kOffXch + 3 * 128 * 4 + 1024;  // + alignment slack
 constexpr int kLoaderWarps = 4;
 constexpr int kLoaderThreads = kLoaderWarps * 32;
-constexpr int kThreads = 192 + kLoaderThreads;
+constexpr int kPvWarp = 6 + kLoaderThreads / 32;  // after the loader warps
+constexpr int kThreads = 192 + kLoaderThreads + 32;
 constexpr int kTmemCols = 512;
 constexpr int kColS = 0;              // two S buffers of kHalf columns
 constexpr int kColO = 2 * kHalf;      // 256 output columns
@@ -163,6 +164,7 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
     uint64_t *pv_done = p_full + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + kOffMisc);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    volatile int *s_issued = reinterpret_cast<volatile int *>(tmem_slot + 2);  // tiles whose S the rank-0 CTA has issued
     float *x_max = reinterpret_cast<float *>(smem + kOffXch);  // [2][128]
     float *x_sum = x_max + 256;                                  // [128]
 
@@ -185,6 +187,7 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             mbar_init(&pv_done[s], 1);
         }
         *abort_flag = 0;
+        *s_issued = 0;
         mbar_fence_init();
     }
     if (warp == 5) tmem_alloc(tmem_slot, kTmemCols);
@@ -272,23 +275,32 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             __syncwarp();
         }
     } else if (warp == 5) {
-        // ---------------- MMA issuer (rank 0 issues for the pair) ----------------
+        // ---------------- issuer of S = Q.K^T (the rank-0 CTA issues for the pair) ----------------
+        // The two contractions have an issuing warp each (this one and warp kPvWarp): per K block the issue loop
+        // costs a barrier wait, four MMAs and a commit, about as long as those MMAs run, so one warp issuing S
+        // and P.V in turn keeps the tensor pipe waiting for its next instruction.  The whole warp walks the loop
+        // and one elected lane issues: the same loop run by lane 0 alone was measured 55 % slower.
         if (rank == 0) {
             const uint32_t leader = elect_one();
             const uint64_t q_desc0 = smem_desc(smem_u32(q_s), 16, 1024, 2);
             const uint64_t a_desc0 = smem_desc(smem_u32(a_s), 16, 1024, 2);
-            const uint64_t p_desc0 = smem_desc(smem_u32(p_s), 16, 1024, 2);
-            const uint64_t v_desc0 = smem_desc(smem_u32(v_s), kKBlockBytes, 1024, 2);  // V slot, MN-major
             const uint32_t q_tmem_addr = tmem_base + kColQ;
             int a_slot = 0;
             uint32_t a_round = 0;
-                auto issue_qk = [&](int t) -> bool {
+            ok = mbar_wait(q_full, 0, abort_flag);
+            if (ok) ok = mbar_wait(q_tmem, 0, abort_flag);
+            if (ok) tc_fence_after();
+            for (int t = 0; t < n_tiles && ok; ++t) {
+                // S(t) goes where S(t-2) was: the softmax threads have read that once P(t-2) is complete.
+                if (t >= 2) ok = mbar_wait(&p_full[t & 1], (uint32_t)((t - 2) / 2) & 1u, abort_flag);
+                if (!ok) break;
                 const uint32_t d = tmem_base + kColS + (t & 1) * kHalf;
                 // (rolled over the blocks, unrolled over the four 16-element steps of a block: small code, and the
                 // descriptors of a block differ from the previous block's by constants)
 #pragma unroll 1
                 for (int j = 0; j < kBlocks; ++j) {
-                    if (!mbar_wait(&a_full[a_slot], a_round & 1u, abort_flag)) return false;
+                    ok = mbar_wait(&a_full[a_slot], a_round & 1u, abort_flag);
+                    if (!ok) break;
                     tc_fence_after();
                     const uint64_t bd = a_desc0 + (uint64_t)((a_slot * kKBlockBytes) >> 4);
                     if (j < kQTmemBlocks) {
@@ -307,22 +319,35 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
                         ++a_round;
                     }
                 }
+                if (!ok) break;
                 umma2_commit_both(&s_full[t & 1], leader);
-                return true;
-            };
-            ok = mbar_wait(q_full, 0, abort_flag);
-            if (ok) ok = mbar_wait(q_tmem, 0, abort_flag);
-            if (ok) tc_fence_after();
-            // Issue order S(0) S(1) P.V(0) S(2) P.V(1) ...: one call site for S keeps the kernel's code small
-            // (the unrolled issue sequences of all roles have to share the instruction cache).
-            for (int t = -1; t < n_tiles && ok; ++t) {
-                if (t + 1 < n_tiles) {
-                    ok = issue_qk(t + 1);
-                    if (!ok) break;
-                }
-                if (t < 0) continue;
+                if (leader) *s_issued = t + 1;
+            }
+        }
+        __syncwarp();
+    } else if (warp == kPvWarp) {
+        // ---------------- issuer of O += P.V (rank-0 CTA), tile by tile ----------------
+        if (rank == 0) {
+            const uint32_t leader = elect_one();
+            const uint64_t p_desc0 = smem_desc(smem_u32(p_s), 16, 1024, 2);
+            const uint64_t v_desc0 = smem_desc(smem_u32(v_s), kKBlockBytes, 1024, 2);  // V slot, MN-major
+            for (int t = 0; t < n_tiles && ok; ++t) {
                 ok = mbar_wait(&p_full[t & 1], (uint32_t)(t / 2) & 1u, abort_flag);
                 if (!ok) break;
+                // S(t+1) goes into the tensor pipe first: the softmax of tile t+1, which waits for it, is the longer
+                // chain, and P.V(t) then runs beside that softmax.
+                {
+                    const int want = min(t + 2, n_tiles);
+                    const long long t0 = clock64();
+                    while (*s_issued < want) {
+                        if (*abort_flag || clock64() - t0 > kMaxWaitCycles) {
+                            *abort_flag = 1;
+                            ok = false;
+                            break;
+                        }
+                    }
+                    if (!ok) break;
+                }
                 tc_fence_after();
                 const uint32_t d = tmem_base + kColO;
                 const uint64_t pd = p_desc0 + (uint64_t)((((t % kPBufs) * kPBytes)) >> 4);
@@ -351,7 +376,7 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             }
         }
         __syncwarp();
-    } else if (warp >= 6) {
+    } else if (warp >= 6 && warp < 6 + kLoaderThreads / 32) {
         // ---------------- V loaders: this CTA's 256 dims of all 128 keys of a tile, half-tile by half-tile ----------------
         // Jobs of 32 KB each, in the order the tensor pipe needs them: K blocks 5..8 of tile 0, then per tile t
         // the same blocks of tile t+1 and the two V half-tiles of tile t.  A job is published (its barrier in the
