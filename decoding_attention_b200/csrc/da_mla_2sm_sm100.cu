@@ -78,6 +78,12 @@ constexpr int kQSmemBlocks = kBlocks - kQTmemBlocks;
 constexpr int kQBlockBytes = 64 * 128;     // [64 heads x 64 dims], 128-byte swizzle: a Q block (and a 64-key block of P)
 constexpr int kKBlockBytes = kHalf * 128;  // [kHalf keys x 64 dims]: a K block of one CTA
 constexpr int kASlots = DA_MLA2_ASLOTS;         // ring of TMA-streamed K blocks
+constexpr int kGroup = 3;                       // K blocks per ring barrier: the issue loop pays per barrier wait and commit
+constexpr int kAGroups = kASlots / kGroup;
+static_assert(kASlots % kGroup == 0 && (kDim / 64) % kGroup == 0, "blocks travel in groups");
+constexpr int kTileGroups = (kDim / 64) / kGroup;   // groups per tile
+constexpr int kRingTiles = kAGroups / kTileGroups;  // the ring holds a whole number of tiles: a group's slot is static
+static_assert(kAGroups % kTileGroups == 0, "the K ring holds whole tiles");
 constexpr int kVSlots = DA_MLA2_VSLOTS;         // ring of V half-tiles
 constexpr int kVSlotBytes = kVBlocks * kKBlockBytes;
 constexpr int kPBufs = DA_MLA2_PBUFS;          // P tiles in shared memory
@@ -224,7 +230,7 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
                 mbar_arrive_remote(lead(q_full));
             }
         }
-        int slot = 0;
+        int gs = 0;
         uint32_t round = 0;
         for (int t = 0; t < n_tiles && ok; ++t) {
             const int key0 = k_begin + t * kTile + (int)rank * kHalf;  // this CTA's first key of the tile
@@ -233,42 +239,46 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             // rows of the tile are consecutive in the cache, except across the pages of a short-page cache
             auto row_of = [&](int r) { return kShortPages ? kv_tile_row(p, b, seq_begin, key0 + r) : tok0 + r; };
             const int run = kShortPages ? (1 << p.page_shift) : kHalf;  // consecutive rows: a page, or the whole half tile
-            for (int j = 0; j < kBlocks && ok; ++j) {
-                if (round > 0) ok = mbar_wait(&a_empty[slot], (round & 1u) ^ 1u, abort_flag);
+            for (int g = 0; g < kBlocks / kGroup && ok; ++g) {
+                if (round > 0) ok = mbar_wait(&a_empty[gs], (round & 1u) ^ 1u, abort_flag);
                 if (!ok) break;
-                uint8_t *dst = a_s + slot * kKBlockBytes;
-                // a_full[slot] of the rank-0 CTA takes ONE arrival per use, rank 0's, which also announces the
-                // bytes: its own block when that comes by TMA, and always the peer's 8 KB -- delivered by the
-                // peer's TMA copy, or counted by hand when the peer had to write a ragged block with stores.
-                // (No remote arrival per block: a cluster-scope release costs about a thousand cycles.)
+                uint8_t *dst = a_s + gs * kGroup * kKBlockBytes;
+                // a_full[gs] of the rank-0 CTA takes ONE arrival per use, rank 0's, which also announces the
+                // bytes: its own blocks when they come by TMA, and always the peer's -- delivered by the
+                // peer's TMA copies, or counted by hand when the peer had to write ragged blocks with stores.
+                // (No remote arrival per group: a cluster-scope release costs about a thousand cycles.)
                 if (rows == kHalf) {
                     if (lane == 0) {
-                        if (rank == 0) mbar_arrive_expect_tx(&a_full[slot], 2 * kKBlockBytes);
-                        for (int k0 = 0; k0 < kHalf; k0 += run)
-                            tma2_load_2d(dst + k0 * 128, &tm_k, j * 64, (int)row_of(k0), lead(&a_full[slot]));
+                        if (rank == 0) mbar_arrive_expect_tx(&a_full[gs], 2 * kGroup * kKBlockBytes);
+                        for (int k0 = 0; k0 < kHalf; k0 += run) {
+                            const int row = (int)row_of(k0);
+#pragma unroll
+                            for (int jj = 0; jj < kGroup; ++jj)
+                                tma2_load_2d(dst + jj * kKBlockBytes + k0 * 128, &tm_k, (g * kGroup + jj) * 64, row, lead(&a_full[gs]));
+                        }
                     }
                 } else {
                     // ragged end of the key range: plain loads, rows past the end zeroed (the tensor map
                     // must not be asked for rows beyond the sequence)
-                    for (int i = lane; i < kHalf * 8; i += 32) {
-                        const int r = i >> 3, cc = i & 7;
+                    for (int i = lane; i < kGroup * kHalf * 8; i += 32) {
+                        const int jj = i / (kHalf * 8), r = (i >> 3) % kHalf, cc = i & 7;
                         uint4 v = make_uint4(0, 0, 0, 0);
-                        if (r < rows) v = *reinterpret_cast<const uint4 *>(k_g + row_of(r) * p.k_row_stride + j * 64 + cc * 8);
-                        *reinterpret_cast<uint4 *>(dst + r * 128 + ((cc ^ (r & 7)) << 4)) = v;
+                        if (r < rows) v = *reinterpret_cast<const uint4 *>(k_g + row_of(r) * p.k_row_stride + (g * kGroup + jj) * 64 + cc * 8);
+                        *reinterpret_cast<uint4 *>(dst + jj * kKBlockBytes + r * 128 + ((cc ^ (r & 7)) << 4)) = v;
                     }
                     fence_proxy_async();
                     __syncwarp();
                     if (lane == 0) {
                         if (rank == 0) {
-                            mbar_arrive_expect_tx(&a_full[slot], kKBlockBytes);
+                            mbar_arrive_expect_tx(&a_full[gs], kGroup * kKBlockBytes);
                         } else {
                             fence_acq_rel_cluster();
-                            mbar_complete_tx_remote(lead(&a_full[slot]), kKBlockBytes);
+                            mbar_complete_tx_remote(lead(&a_full[gs]), kGroup * kKBlockBytes);
                         }
                     }
                 }
-                if (++slot == kASlots) {
-                    slot = 0;
+                if (++gs == kAGroups) {
+                    gs = 0;
                     ++round;
                 }
             }
@@ -285,8 +295,6 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             const uint64_t q_desc0 = smem_desc(smem_u32(q_s), 16, 1024, 2);
             const uint64_t a_desc0 = smem_desc(smem_u32(a_s), 16, 1024, 2);
             const uint32_t q_tmem_addr = tmem_base + kColQ;
-            int a_slot = 0;
-            uint32_t a_round = 0;
             ok = mbar_wait(q_full, 0, abort_flag);
             if (ok) ok = mbar_wait(q_tmem, 0, abort_flag);
             if (ok) tc_fence_after();
@@ -295,29 +303,31 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
                 if (t >= 2) ok = mbar_wait(&p_full[t & 1], (uint32_t)((t - 2) / 2) & 1u, abort_flag);
                 if (!ok) break;
                 const uint32_t d = tmem_base + kColS + (t & 1) * kHalf;
-                // (rolled over the blocks, unrolled over the four 16-element steps of a block: small code, and the
-                // descriptors of a block differ from the previous block's by constants)
-#pragma unroll 1
-                for (int j = 0; j < kBlocks; ++j) {
-                    ok = mbar_wait(&a_full[a_slot], a_round & 1u, abort_flag);
+                const int gs0 = (t % kRingTiles) * kTileGroups;       // first ring slot of this tile's groups
+                const uint32_t a_par = (uint32_t)(t / kRingTiles) & 1u;
+                // (unrolled over the tile's groups: slots, barriers and descriptors are compile-time offsets, which
+                // keeps the issue loop -- the pace-setter of the kernel -- short; one barrier wait and one commit per group)
+#pragma unroll
+                for (int g = 0; g < kTileGroups; ++g) {
+                    ok = mbar_wait(&a_full[gs0 + g], a_par, abort_flag);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint64_t bd = a_desc0 + (uint64_t)((a_slot * kKBlockBytes) >> 4);
-                    if (j < kQTmemBlocks) {
 #pragma unroll
-                        for (int ks = 0; ks < 4; ++ks)
-                            umma2_ts(d, q_tmem_addr + j * 32 + ks * 8, bd + (uint64_t)(ks * 2), kIdescQK, (j | ks) ? 1u : 0u, leader);
-                    } else {
-                        const uint64_t qd = q_desc0 + (uint64_t)(((j - kQTmemBlocks) * kQBlockBytes) >> 4);
+                    for (int jj = 0; jj < kGroup; ++jj) {
+                        const int j = g * kGroup + jj;
+                        const uint64_t bd = a_desc0 + (uint64_t)(((gs0 + g) * kGroup + jj) * (kKBlockBytes >> 4));
+                        if (j < kQTmemBlocks) {
 #pragma unroll
-                        for (int ks = 0; ks < 4; ++ks)
-                            umma2_ss(d, qd + (uint64_t)(ks * 2), bd + (uint64_t)(ks * 2), kIdescQK, (j | ks) ? 1u : 0u, leader);
+                            for (int ks = 0; ks < 4; ++ks)
+                                umma2_ts(d, q_tmem_addr + j * 32 + ks * 8, bd + (uint64_t)(ks * 2), kIdescQK, (j | ks) ? 1u : 0u, leader);
+                        } else {
+                            const uint64_t qd = q_desc0 + (uint64_t)(((j - kQTmemBlocks) * kQBlockBytes) >> 4);
+#pragma unroll
+                            for (int ks = 0; ks < 4; ++ks)
+                                umma2_ss(d, qd + (uint64_t)(ks * 2), bd + (uint64_t)(ks * 2), kIdescQK, (j | ks) ? 1u : 0u, leader);
+                        }
                     }
-                    umma2_commit_both(&a_empty[a_slot], leader);
-                    if (++a_slot == kASlots) {
-                        a_slot = 0;
-                        ++a_round;
-                    }
+                    umma2_commit_both(&a_empty[gs0 + g], leader);
                 }
                 if (!ok) break;
                 umma2_commit_both(&s_full[t & 1], leader);
