@@ -94,24 +94,27 @@ constexpr int kOffA = kOffQ + kQSmemBlocks * kQBlockBytes;
 constexpr int kOffV = kOffA + kASlots * kKBlockBytes;
 constexpr int kOffP = kOffV + kVSlots * kVSlotBytes;
 constexpr int kOffBar = kOffP + kPBufs * kPBytes;
-// q_full, q_tmem, q_stage_full, q_copied, a_full/a_empty[kASlots], v_full/v_empty[kVSlots], s_full[2], p_full[2], pv_done[2]
-constexpr int kNumBars = 4 + 2 * kASlots + 2 * kVSlots + 6;
+// q_full, q_tmem, q_stage_full, q_copied, a_full/a_empty[kASlots], v_full/v_empty[kVSlots], s_full[2], p_full[2][2], pv_done[2][2], s_empty[2]
+constexpr int kNumBars = 4 + 2 * kAGroups + 2 * kVSlots + 12;
 constexpr int kOffMisc = kOffBar + kNumBars * 8;          // tmem slot, abort flag
-constexpr int kOffXch = kOffMisc + 16;                    // float [2][128] tile maxima, float [128] row sums
-constexpr int kSmemBytes = kOffXch + 3 * 128 * 4 + 1024;  // + alignment slack
+constexpr int kOffXch = kOffMisc + 16;                    // bf16 [2][256] tile maxima, later float [256] row sums
+constexpr int kSmemBytes = kOffXch + 256 * 4 + 1024;      // + alignment slack
 constexpr int kLoaderWarps = 4;
 constexpr int kLoaderThreads = kLoaderWarps * 32;
-constexpr int kPvWarp = 6 + kLoaderThreads / 32;  // after the loader warps
-constexpr int kThreads = 192 + kLoaderThreads + 32;
+constexpr int kSoftmaxWarps = 8;                   // two per TMEM lane quadrant
+constexpr int kSoftmaxThreads = kSoftmaxWarps * 32;
+constexpr int kProducerWarp = kSoftmaxWarps, kSWarp = kSoftmaxWarps + 1, kLoaderWarp0 = kSoftmaxWarps + 2;
+constexpr int kPvWarp = kLoaderWarp0 + kLoaderWarps;
+constexpr int kThreads = (kPvWarp + 1) * 32;
 constexpr int kTmemCols = 512;
 constexpr int kColS = 0;              // two S buffers of kHalf columns
 constexpr int kColO = 2 * kHalf;      // 256 output columns
 constexpr int kColQ = kColO + 256;    // kQTmemBlocks * 32 columns
 static_assert(kColQ + kQTmemBlocks * 32 <= kTmemCols, "TMEM budget");
 static_assert(kQStageSlots < kVSlots, "the Q blocks bound for TMEM are staged in the last V slots");
-static_assert(kTile == 64 || kTile == 128, "tile");
+static_assert(kTile == 128 && kQTmemBlocks % 2 == 0, "tile");
 static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
-static_assert(128 * (256 * 4 + 16) <= kOffP - kOffA, "the epilogue stages its output in the idle rings");
+static_assert(kSoftmaxThreads * (128 * 4 + 16) <= kOffP - kOffA, "the epilogue stages its output in the idle rings");
 constexpr float kRescaleThreshold = 8.0f;
 
 // kShortPages: the cache is paged in pages shorter than the kHalf keys one CTA stages at a time; a block is then
@@ -162,24 +165,28 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
     uint64_t *q_stage_full = bars + 2;  // this CTA: Q blocks 0..3 landed in the staging slot
     uint64_t *q_copied = bars + 3;      // this CTA: the softmax warps have moved them to TMEM
     uint64_t *a_full = bars + 4;   // rank 0: streamed K block landed in both CTAs
-    uint64_t *a_empty = a_full + kASlots;
-    uint64_t *v_full = a_empty + kASlots;  // rank 0: V half-tile landed in both CTAs
+    uint64_t *a_empty = a_full + kAGroups;
+    uint64_t *v_full = a_empty + kAGroups;  // rank 0: V half-tile landed in both CTAs
     uint64_t *v_empty = v_full + kVSlots;
     uint64_t *s_full = v_empty + kVSlots;
-    uint64_t *p_full = s_full + 2;         // rank 0: P written by both CTAs
-    uint64_t *pv_done = p_full + 2;
+    // P and P.V are tracked per 64-key half of a tile, [tile parity][half]: the threads of key half h write P
+    // block h as soon as the first / second half of the previous tile's P.V has read it, and the P.V issuer
+    // starts on block 0 while block 1 is still being written.
+    uint64_t *p_full = s_full + 2;         // rank 0: P block written by both CTAs
+    uint64_t *pv_done = p_full + 4;
+    uint64_t *s_empty = pv_done + 4;       // rank 0: every softmax warp of the pair has read its S columns
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + kOffMisc);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     volatile int *s_issued = reinterpret_cast<volatile int *>(tmem_slot + 2);  // tiles whose S the rank-0 CTA has issued
-    float *x_max = reinterpret_cast<float *>(smem + kOffXch);  // [2][128]
-    float *x_sum = x_max + 256;                                  // [128]
+    __nv_bfloat16 *x_max = reinterpret_cast<__nv_bfloat16 *>(smem + kOffXch);  // [2][256] tile maxima, rounded up
+    float *x_sum = reinterpret_cast<float *>(smem + kOffXch);                   // [256] row sums, after the last tile
 
     if (tid == 0) {
         mbar_init(q_full, 2);
-        mbar_init(q_tmem, 8);
+        mbar_init(q_tmem, 2 * kSoftmaxWarps);
         mbar_init(q_stage_full, 1);
-        mbar_init(q_copied, 4);
-        for (int s = 0; s < kASlots; ++s) {
+        mbar_init(q_copied, kSoftmaxWarps);
+        for (int s = 0; s < kAGroups; ++s) {
             mbar_init(&a_full[s], 1);
             mbar_init(&a_empty[s], 1);
         }
@@ -189,14 +196,17 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&s_full[s], 1);
-            mbar_init(&p_full[s], 8);
-            mbar_init(&pv_done[s], 1);
+            mbar_init(&s_empty[s], 2 * kSoftmaxWarps);
+            for (int h = 0; h < 2; ++h) {
+                mbar_init(&p_full[2 * s + h], kSoftmaxWarps);  // the four warps of key half h, in both CTAs
+                mbar_init(&pv_done[2 * s + h], 1);
+            }
         }
         *abort_flag = 0;
         *s_issued = 0;
         mbar_fence_init();
     }
-    if (warp == 5) tmem_alloc(tmem_slot, kTmemCols);
+    if (warp == kSWarp) tmem_alloc(tmem_slot, kTmemCols);
     tc_fence_before();
     cluster_sync_all();  // both CTAs' barriers exist before anybody arrives on them remotely
     tc_fence_after();
@@ -211,7 +221,7 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
     bool ok = true;
     const T *k_g = reinterpret_cast<const T *>(p.k);
 
-    if (warp == 4) {
+    if (warp == kProducerWarp) {
         // ---------------- TMA producer: Q blocks 4..8, then this CTA's 64 keys of every tile ----------------
         const int q_rows = min(kRows, p.head_q - head0);  // rows the Q box holds (<= 0: this CTA is all padding)
         if (lane == 0) {
@@ -284,7 +294,7 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             }
             __syncwarp();
         }
-    } else if (warp == 5) {
+    } else if (warp == kSWarp) {
         // ---------------- issuer of S = Q.K^T (the rank-0 CTA issues for the pair) ----------------
         // The two contractions have an issuing warp each (this one and warp kPvWarp): per K block the issue loop
         // costs a barrier wait, four MMAs and a commit, about as long as those MMAs run, so one warp issuing S
@@ -299,8 +309,8 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             if (ok) ok = mbar_wait(q_tmem, 0, abort_flag);
             if (ok) tc_fence_after();
             for (int t = 0; t < n_tiles && ok; ++t) {
-                // S(t) goes where S(t-2) was: the softmax threads have read that once P(t-2) is complete.
-                if (t >= 2) ok = mbar_wait(&p_full[t & 1], (uint32_t)((t - 2) / 2) & 1u, abort_flag);
+                // S(t) goes where S(t-2) was, once the softmax threads have loaded that.
+                if (t >= 2) ok = mbar_wait(&s_empty[t & 1], (uint32_t)((t - 2) / 2) & 1u, abort_flag);
                 if (!ok) break;
                 const uint32_t d = tmem_base + kColS + (t & 1) * kHalf;
                 const int gs0 = (t % kRingTiles) * kTileGroups;       // first ring slot of this tile's groups
@@ -342,7 +352,7 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             const uint64_t p_desc0 = smem_desc(smem_u32(p_s), 16, 1024, 2);
             const uint64_t v_desc0 = smem_desc(smem_u32(v_s), kKBlockBytes, 1024, 2);  // V slot, MN-major
             for (int t = 0; t < n_tiles && ok; ++t) {
-                ok = mbar_wait(&p_full[t & 1], (uint32_t)(t / 2) & 1u, abort_flag);
+                ok = mbar_wait(&p_full[2 * (t & 1)], (uint32_t)(t / 2) & 1u, abort_flag);
                 if (!ok) break;
                 // S(t+1) goes into the tensor pipe first: the softmax of tile t+1, which waits for it, is the longer
                 // chain, and P.V(t) then runs beside that softmax.
@@ -365,7 +375,8 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
                 for (int h = 0; h < 2; ++h) {
                     const int i = 2 * t + h;
                     const int vs = i % kVSlots;
-                    ok = mbar_wait(&v_full[vs], (uint32_t)(i / kVSlots) & 1u, abort_flag);
+                    if (h == 1) ok = mbar_wait(&p_full[2 * (t & 1) + 1], (uint32_t)(t / 2) & 1u, abort_flag);
+                    if (ok) ok = mbar_wait(&v_full[vs], (uint32_t)(i / kVSlots) & 1u, abort_flag);
                     if (!ok) break;
                     tc_fence_after();
                     const uint64_t vd = v_desc0 + (uint64_t)((vs * kVSlotBytes) >> 4);
@@ -380,13 +391,13 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
                         umma2_ss(d + 128, ad, bd + (uint64_t)((2 * kKBlockBytes) >> 4), kIdescPV, (t | h | ks) ? 1u : 0u, leader);
                     }
                     umma2_commit_both(&v_empty[vs], leader);
+                    umma2_commit_both(&pv_done[2 * (t & 1) + h], leader);
                 }
                 if (!ok) break;
-                umma2_commit_both(&pv_done[t & 1], leader);
             }
         }
         __syncwarp();
-    } else if (warp >= 6 && warp < 6 + kLoaderThreads / 32) {
+    } else if (warp >= kLoaderWarp0 && warp < kLoaderWarp0 + kLoaderWarps) {
         // ---------------- V loaders: this CTA's 256 dims of all 128 keys of a tile, half-tile by half-tile ----------------
         // Jobs of 32 KB each, in the order the tensor pipe needs them: K blocks 5..8 of tile 0, then per tile t
         // the same blocks of tile t+1 and the two V half-tiles of tile t.  A job is published (its barrier in the
@@ -396,7 +407,7 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
         // version of this loop that was inlined four times made the whole kernel 30 % slower).  A half-tile's
         // barrier gets this warp's arrival once the next one has been issued and its own bytes have landed: two
         // half-tiles are in flight.
-        const int lt = tid - 6 * 32;  // 0..127
+        const int lt = tid - kLoaderWarp0 * 32;  // 0..127
         const int n_halves = 2 * n_tiles;
         for (int i = 0; i < n_halves && ok; ++i) {
             const int key0 = k_begin + (i >> 1) * kTile + (i & 1) * kHalf;
@@ -432,11 +443,14 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
         __syncwarp();
         if (ok && lane == 0) mbar_arrive_remote_cta(lead(&v_full[(n_halves - 1) % kVSlots]));
     } else {
-        // ---------------- softmax / epilogue: thread l <-> TMEM lane l <-> (head l & 63, key half l >> 6) ----------------
-        const int r = tid & 63, kh = tid >> 6;
+        // ---------------- softmax / epilogue: two warps per TMEM lane quadrant.  Thread (ch, l) works on lane l,
+        // i.e. head l & 63 and key half l >> 6, and on 32 of the lane's 64 score columns (ch = 0 / 1): the softmax
+        // chain of a tile is per-thread serial work, and with one thread per lane it set the kernel's pace. ----------
+        const int tl = tid & 127, ch = tid >> 7;
+        const int r = tl & 63, kh = tl >> 6;
         const int head = head0 + r;
         const bool valid = head < p.head_q;  // rows past head_q are padding
-        const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+        const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
         const float slope2 = p.is_alibi ? exp2f(-8.0f * (float)(head + 1) / (float)p.head_q) * kLog2e : 0.0f;
         const int pos_shift = (p.kv_pos_offset ? p.kv_pos_offset[b] : 0) - ((p.kv_total_len ? p.kv_total_len[b] : len) - 1);
         float m_ref = -INFINITY, l = 0.0f;
@@ -451,7 +465,8 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             const bool have_q = head0 < p.head_q;
             if (have_q) ok = __all_sync(0xffffffffu, mbar_wait(q_stage_full, 0, abort_flag)) != 0;
 #pragma unroll
-            for (int j = 0; j < kQTmemBlocks; ++j) {
+            for (int jj = 0; jj < kQTmemBlocks / 2; ++jj) {
+                const int j = ch * (kQTmemBlocks / 2) + jj;  // this warp's half of the blocks
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const uint4 v = (valid && ok) ? *reinterpret_cast<const uint4 *>(q_stage + j * kQBlockBytes + r * 128 + ((i ^ (r & 7)) << 4))
@@ -469,48 +484,41 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             }
         }
         // `ok` is kept warp-uniform, and a warp that has given up still walks the loop so that the named
-        // barriers below always see all 128 threads.
+        // barriers below always see all 256 threads.
         auto wait_all = [&](uint64_t *bar, uint32_t parity) {
             return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag)) != 0;
         };
         for (int t = 0; t < n_tiles; ++t) {
-            const int key0 = k_begin + t * kTile + kh * kHalf;  // first key of this thread's 64 columns
-            const int rows = k_end - key0;                       // columns >= rows are past the end
-            const uint32_t s_addr = lane_base + kColS + (t & 1) * kHalf;
+            const int key0 = k_begin + t * kTile + kh * kHalf + ch * 32;  // first key of this thread's 32 columns
+            const int rows = k_end - key0;                                 // columns >= rows are past the end
+            const uint32_t s_addr = lane_base + kColS + (t & 1) * kHalf + ch * 32;
             if (ok) ok = wait_all(&s_full[t & 1], (uint32_t)(t / 2) & 1u);
-            float s[kHalf];
+            float s[32];
             float mx = -INFINITY;
             if (ok) {
                 tc_fence_after();
-                if (kHalf == 64) {
-                    uint32_t buf2[32];
-                    tmem_ld32(s_addr, buf);        // both halves of the row are requested before the wait:
-                    tmem_ld32(s_addr + 32, buf2);  // a TMEM load takes a few hundred cycles to return
-                    tmem_wait_ld();
+                tmem_ld32(s_addr, buf);
+                tmem_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_remote_cta(lead(&s_empty[t & 1]));
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const float x0 = __uint_as_float(buf[j]) * p.scale_log2 + slope2 * (float)(key0 + j + pos_shift);
-                        const float x1 = __uint_as_float(buf2[j]) * p.scale_log2 + slope2 * (float)(key0 + 32 + j + pos_shift);
-                        s[j] = (j < rows) ? (valid ? x0 : 0.0f) : -INFINITY;
-                        s[kHalf - 32 + j] = (32 + j < rows) ? (valid ? x1 : 0.0f) : -INFINITY;
-                        mx = fmaxf(mx, fmaxf(s[j], s[kHalf - 32 + j]));
-                    }
-                } else {
-                    tmem_ld32(s_addr, buf);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const float x0 = __uint_as_float(buf[j]) * p.scale_log2 + slope2 * (float)(key0 + j + pos_shift);
-                        s[j] = (j < rows) ? (valid ? x0 : 0.0f) : -INFINITY;
-                        mx = fmaxf(mx, s[j]);
-                    }
+                for (int j = 0; j < 32; ++j) {
+                    const float x0 = __uint_as_float(buf[j]) * p.scale_log2 + slope2 * (float)(key0 + j + pos_shift);
+                    s[j] = (j < rows) ? (valid ? x0 : 0.0f) : -INFINITY;
+                    mx = fmaxf(mx, s[j]);
                 }
             }
-            // one reference per head: the two threads of a head swap their maxima
-            x_max[(t & 1) * 128 + tid] = mx;
-            named_bar_sync(1, 128);
+            // One reference per head: its four threads swap their maxima, rounded up to 16 bits (any common
+            // reference at or above the true maximum serves; every thread uses the rounded values, its own too).
+            x_max[(t & 1) * 256 + tid] = __float2bfloat16_ru(mx);
+            named_bar_sync(1, kSoftmaxThreads);
             if (!ok) continue;
-            mx = fmaxf(mx, x_max[(t & 1) * 128 + (tid ^ 64)]);
+            {
+                const __nv_bfloat16 *xm = x_max + (t & 1) * 256;
+                mx = fmaxf(fmaxf(__bfloat162float(xm[tid]), __bfloat162float(xm[tid ^ 64])),
+                           fmaxf(__bfloat162float(xm[tid ^ 128]), __bfloat162float(xm[tid ^ 192])));
+            }
             const bool raise = mx > m_ref + kRescaleThreshold;
             float alpha = 1.0f;
             if (raise) {
@@ -521,30 +529,30 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             if (t >= 1 && __any_sync(0xffffffffu, raise)) {
                 // Rare: the reference max of some row in this warp moved.  O must be idle (P.V of tile
                 // t-1 complete) while its rows are rescaled in place.
-                ok = wait_all(&pv_done[(t - 1) & 1], (uint32_t)((t - 1) / 2) & 1u);
+                ok = wait_all(&pv_done[2 * ((t - 1) & 1) + 1], (uint32_t)((t - 1) / 2) & 1u);
                 if (!ok) continue;
                 tc_fence_after();
 #pragma unroll 1
-                for (int c = 0; c < 256 / 32; ++c) {
-                    tmem_ld32(lane_base + kColO + c * 32, buf);
+                for (int c = 0; c < 128 / 32; ++c) {  // this thread's half of the lane's 256 columns
+                    tmem_ld32(lane_base + kColO + ch * 128 + c * 32, buf);
                     tmem_wait_ld();
 #pragma unroll
                     for (int j = 0; j < 32; ++j) buf[j] = __float_as_uint(__uint_as_float(buf[j]) * alpha);
-                    tmem_st32(lane_base + kColO + c * 32, buf);
+                    tmem_st32(lane_base + kColO + ch * 128 + c * 32, buf);
                 }
                 tmem_wait_st();
             } else if (kPBufs == 1 && t >= 1) {
-                // the single P buffer is still being read by P.V of tile t-1
-                ok = wait_all(&pv_done[(t - 1) & 1], (uint32_t)((t - 1) / 2) & 1u);
+                // this thread's block of the single P buffer is still being read by its half of P.V of tile t-1
+                ok = wait_all(&pv_done[2 * ((t - 1) & 1) + kh], (uint32_t)((t - 1) / 2) & 1u);
                 if (!ok) continue;
             }
             // P = exp2(S - m_ref), rounded to the input type: row r, keys kh * kHalf .. of the tile, K-major in 64-key
             // swizzled blocks
-            const int pkey = kh * kHalf;
+            const int pkey = kh * kHalf + ch * 32;
             uint8_t *p_row = p_s + (t % kPBufs) * kPBytes + (pkey / 64) * kQBlockBytes + r * 128;
             float sum = 0.0f;
 #pragma unroll
-            for (int cc = 0; cc < kHalf / 8; ++cc) {
+            for (int cc = 0; cc < 32 / 8; ++cc) {
                 uint32_t w[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -565,30 +573,32 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             fence_proxy_async();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive_remote_cta(lead(&p_full[t & 1]));
+            if (lane == 0) mbar_arrive_remote_cta(lead(&p_full[2 * (t & 1) + kh]));
         }
-        if (ok) ok = wait_all(&pv_done[(n_tiles - 1) & 1], (uint32_t)((n_tiles - 1) / 2) & 1u);
+        if (ok) ok = wait_all(&pv_done[2 * ((n_tiles - 1) & 1) + 1], (uint32_t)((n_tiles - 1) / 2) & 1u);
+        named_bar_sync(1, kSoftmaxThreads);  // the last tile's maxima have been read: the row sums take their place
         x_sum[tid] = l;
-        named_bar_sync(1, 128);
+        named_bar_sync(1, kSoftmaxThreads);
         if (ok) {
             tc_fence_after();
-            l += x_sum[tid ^ 64];
+            l = (x_sum[tid] + x_sum[tid ^ 64]) + (x_sum[tid ^ 128] + x_sum[tid ^ 192]);
             const float inv = 1.0f / l;
             const float lse = (m_ref + log2f(l)) * kLn2;
             const size_t row = ((size_t)b * p.head_q + head) * p.num_splits + split;
-            // This thread's 256 output values are staged in shared memory (the rings are idle now: every MMA
+            // This thread's 128 output values (half of its lane's 256 columns) are staged in shared memory (the rings are idle now: every MMA
             // of the pair has finished) and leave as one bulk copy per destination, so the writes reach
             // memory as whole lines whatever the row pitch.  Regions are 16 bytes longer than their data:
             // the float4 / uint4 stores of a quarter warp then fall into different banks.
             uint8_t *stage = smem + kOffA;
-            const int d_first = kh * 256;
+            const int d_first = kh * 256 + ch * 128;
+            const uint32_t o_addr = lane_base + kColO + ch * 128;
             auto stage_f32 = [&](float *dst_g) {
-                float *mine = reinterpret_cast<float *>(stage + (size_t)tid * (256 * 4 + 16));
+                float *mine = reinterpret_cast<float *>(stage + (size_t)tid * (128 * 4 + 16));
                 uint32_t buf2[32];
 #pragma unroll 1
-                for (int c = 0; c < 256 / 32; c += 2) {
-                    tmem_ld32(lane_base + kColO + c * 32, buf);
-                    tmem_ld32(lane_base + kColO + c * 32 + 32, buf2);
+                for (int c = 0; c < 128 / 32; c += 2) {
+                    tmem_ld32(o_addr + c * 32, buf);
+                    tmem_ld32(o_addr + c * 32 + 32, buf2);
                     tmem_wait_ld();
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
@@ -601,16 +611,16 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
                     }
                 }
                 fence_proxy_async();
-                if (valid) bulk_store_s2g(dst_g, mine, 256 * 4);
+                if (valid) bulk_store_s2g(dst_g, mine, 128 * 4);
                 bulk_store_commit();
             };
             auto stage_t = [&](T *dst_g) {
-                uint8_t *mine = stage + (size_t)tid * (256 * 2 + 16);
+                uint8_t *mine = stage + (size_t)tid * (128 * 2 + 16);
                 uint32_t buf2[32];
 #pragma unroll 1
-                for (int c = 0; c < 256 / 32; c += 2) {
-                    tmem_ld32(lane_base + kColO + c * 32, buf);
-                    tmem_ld32(lane_base + kColO + c * 32 + 32, buf2);
+                for (int c = 0; c < 128 / 32; c += 2) {
+                    tmem_ld32(o_addr + c * 32, buf);
+                    tmem_ld32(o_addr + c * 32 + 32, buf2);
                     tmem_wait_ld();
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
@@ -625,7 +635,7 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
                     }
                 }
                 fence_proxy_async();
-                if (valid) bulk_store_s2g(dst_g, mine, 256 * 2);
+                if (valid) bulk_store_s2g(dst_g, mine, 128 * 2);
                 bulk_store_commit();
             };
             float *dst_f32 = p.num_splits > 1 ? p.part_o + row * kDimV + d_first
@@ -637,7 +647,7 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             }
             if (want_t) stage_t(o_out + (size_t)b * p.o_row_stride + (size_t)head * kDimV + d_first);
             bulk_store_wait_read();
-            if (kh == 0 && valid) {
+            if (kh == 0 && ch == 0 && valid) {
                 if (p.num_splits > 1) {
                     p.part_lse[row] = lse;
                 } else if (p.lse) {
@@ -658,7 +668,7 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
     }
     tc_fence_before();
     cluster_sync_all();  // the peer may still read this CTA's shared memory (pair MMAs) or arrive on its barriers
-    if (warp == 5) {
+    if (warp == kSWarp) {
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
     }
