@@ -90,10 +90,11 @@ Shape shape_of(int64_t dim, int64_t dim_v, bool has_v) {
 // Environment overrides, read once per process (the reference has none; these exist for benchmarks):
 //   DA_NUM_SPLITS=<n>   key-range splits per sequence when the caller leaves num_splits at 0
 //   DA_KERNEL=simt      keep every shape on the CUDA-core kernel (no tensor-core path)
+//   DA_KERNEL=gqa1      groups of at most 32 query heads stay on da_gqa_tc_kernel (for comparisons with the four-stream kernel)
 struct EnvOverrides {
     int num_splits = 0;
     bool force_simt = false;
-    bool no_quad = false;  // development switch (DA_KERNEL=gqa1): small groups stay on the one-stream-pair kernel
+    bool no_quad = false;
 };
 const EnvOverrides &env_overrides() {
     static const EnvOverrides env = [] {

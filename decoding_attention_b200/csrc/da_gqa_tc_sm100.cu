@@ -115,6 +115,11 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
         return;
     }
     const int n_tiles = (k_end - k_begin + kTile - 1) / kTile;
+    // With ALiBi the bias, and with it every head's row maximum, grows towards the end of the sequence: walked
+    // front to back, every tile would raise the reference maximum of the steep heads and take the rescale path.
+    // Walked back to front the first tiles set the maximum.  `tile_of(t)` is the tile the t-th step works on.
+    const bool backwards = p.is_alibi != 0;
+    auto tile_of = [&](int t) { return backwards ? n_tiles - 1 - t : t; };
     const int active_quads = (G + 31) / 32;                   // 32-row blocks that hold valid rows
     const int participants = active_quads * 2 * 32;           // softmax threads at work on one stream
 
@@ -182,7 +187,7 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
         for (int t = 0; t < n_tiles && ok; ++t) {
             const int st = t % kStages;
             const uint32_t ph = (uint32_t)(t / kStages) & 1u;
-            const int key0 = k_begin + t * kTile;
+            const int key0 = k_begin + tile_of(t) * kTile;
             const int rows = min(kTile, k_end - key0);
             const size_t tok0 = kv_tile_row(p, b, seq_begin, key0);
             auto row_of = [&](int r) { return kShortPages ? kv_tile_row(p, b, seq_begin, key0 + r) : tok0 + r; };
@@ -295,8 +300,8 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
         for (int t = strm; t < n_tiles; t += kStreams, ++n_done) {
             const int sb = (kStreams == 2) ? strm : (t & 1);  // S buffer of this tile (= t & 1) and the barriers that go with it
             const int it = t >> 1;  // use count of those barriers
-            const int key0 = k_begin + t * kTile + hf * kColsPer;
-            const int rows = min(kTile, k_end - (k_begin + t * kTile)) - hf * kColsPer;  // valid columns of this thread
+            const int key0 = k_begin + tile_of(t) * kTile + hf * kColsPer;
+            const int rows = min(kTile, k_end - (k_begin + tile_of(t) * kTile)) - hf * kColsPer;  // valid columns of this thread
             ok = __all_sync(0xffffffffu, mbar_wait(&s_full[sb], (uint32_t)it & 1u, abort_flag));
             if (!ok) break;
             tc_fence_after();

@@ -13,26 +13,26 @@
 // V columns (dims 256c..256c+255) of all 128 keys for P.V.  Nothing is computed twice, every K row is
 // read by one CTA for S, and the 128 x 512 fp32 output fits because a CTA's 64 x 512 share is 128
 // TMEM lanes x 256 columns.  What a CTA reads per tile: its 64 keys x 576 dims for S (nine 8 KB
-// blocks streamed by TMA through a ring of nine slots, each released by a tcgen05.commit right after its
-// four MMAs) and 128 keys x 256 dims for P.V (two 32 KB half-tile slots, cp.async), 136 KB against
+// blocks streamed by TMA through a ring of nine slots, released three at a time by a tcgen05.commit right after
+// their twelve MMAs) and 128 keys x 256 dims for P.V (two 32 KB half-tile slots, cp.async), 136 KB against
 // 2 x 72 KB for a kernel whose two CTAs work apart; the second reader of a row hits L2.
-// What bounds it (measured, batch 128 x 4096 keys, 190 us): neither the tensor pipe (2 176 cycles of
-// MMAs per tile) nor DRAM (52 %), but the time a ring slot takes to come back -- one SM's TMA engine
-// writes a 128-byte row every ~5 cycles (330 cycles per block, 2 970 per tile) and a refill can only be
-// asked for once the slot has been consumed, so a tile costs about one memory latency plus the TMA
-// time, 4 900 cycles on an idle GPU and 5 500 under load.  A second tile of ring slots does not fit
-// beside Q (40 KB), P (16 KB) and the V slots (96 KB).
+// What bounds it (measured with per-tile cycle stamps, batch 128 x 4096 keys, 150 us): the K ring never made
+// the issuing warp wait; the issue loops and the softmax chain did.  A barrier wait costs the issuing warp 100-200
+// cycles even when the phase is complete, a commit 60-90, so S and P.V have an issuing warp each, the ring's
+// barriers cover three blocks, and P / P.V are tracked per 64-key half of a tile so that the next tile's P block 0
+// is written while P.V still reads block 1.  A tile takes about 2 950 cycles against 2 176 cycles of MMAs.
 //
 // TMEM columns per CTA: S0 | S1 (64 each: lanes 0-63 keys 0-63 of the tile, lanes 64-127 keys 64-127,
 // rows = this CTA's heads) | O (256: lanes 0-63 dims 0-255, lanes 64-127 dims 256-511) | Q (4 x 32:
 // the first four 64-dim blocks of Q as 16-bit pairs, head r in lanes r and r + 64, read as the A operand).
-// Warp roles (320 threads): warps 0-3 softmax/epilogue -- thread l owns TMEM lane l, i.e. head
-// (l & 63) and key half (l >> 6); the two threads of a head swap their tile maxima through shared
-// memory, keep one reference max, and write P (16-bit, 128-byte-swizzled K-major) to shared memory;
-// warp 4 TMA producer (Q blocks, streamed K blocks); warp 5 TMEM allocation and, in the rank-0 CTA,
-// MMA issue for the pair; warps 6-9 V loaders (16-byte cp.async straight into the swizzled layout,
-// because one SM's TMA engine alone moves only about 21 B/clk).
-// Barriers the MMA thread waits on live in the rank-0 CTA and count arrivals / bytes from both CTAs;
+// Warp roles (480 threads): warps 0-7 softmax/epilogue, two per TMEM lane quadrant -- thread (ch, l) works on
+// lane l, i.e. head (l & 63) and key half (l >> 6), and on 32 of the lane's 64 score columns; the four threads
+// of a head swap their tile maxima through shared memory, keep one reference max, and write P (16-bit,
+// 128-byte-swizzled K-major) to shared memory; warp 8 TMA producer (Q blocks, streamed K blocks); warp 9 TMEM
+// allocation and, in the rank-0 CTA, issue of S for the pair; warps 10-13 V loaders (16-byte cp.async straight
+// into the swizzled layout, because one SM's TMA engine alone moves only about 21 B/clk); warp 14, in the
+// rank-0 CTA, issue of P.V.
+// Barriers the issuing warps wait on live in the rank-0 CTA and count arrivals / bytes from both CTAs;
 // barriers that release buffers or publish S are signalled in both CTAs by one multicast commit.
 // Online softmax with a lazy reference max (raised only when exceeded by 2^8), so O is rescaled a
 // handful of times.  Every wait is bounded; on expiry the CTA records the timeout and still frees
@@ -49,44 +49,26 @@ constexpr int kHeads = 128;        // M of both contractions (pair)
 constexpr int kRows = 64;          // heads per CTA
 constexpr int kDim = 576;
 constexpr int kDimV = 512;
-// Keys per pair tile.  128 is what ships; 64 (twice as many ring slots and V slots of half the size, six Q blocks in
-// TMEM) is kept compiling because it is the obvious next thing to try and was measured: 307 us against 187 us
-// at batch 128 x 4096 keys.  A tile's cost is mostly fixed -- the softmax hand-over between S and P.V takes about
-// two thousand cycles whatever the tile holds -- so halving the tile doubles the number of hand-overs.
-#ifndef DA_MLA2_TILE
-#define DA_MLA2_TILE 128
-#endif
-constexpr int kTile = DA_MLA2_TILE; // keys per pair tile (64 or 128)
+// Keys per pair tile.  (64-key tiles were measured at 307 us against 187 us: a tile's cost is mostly fixed, so
+// halving the tile doubles the number of softmax hand-overs.)
+constexpr int kTile = 128;
 constexpr int kHalf = kTile / 2;   // keys per CTA in S / per V half-tile slot
 constexpr int kBlocks = kDim / 64; // 64-element (128-byte) column blocks of a row
 constexpr int kVBlocks = 4;        // V blocks per CTA (256 of the 512 output dims)
-#ifndef DA_MLA2_QTMEM
-#if DA_MLA2_TILE == 64
-#define DA_MLA2_QTMEM 6
-#define DA_MLA2_ASLOTS 18
-#define DA_MLA2_VSLOTS 7
-#define DA_MLA2_PBUFS 2
-#else
-#define DA_MLA2_QTMEM 4
-#define DA_MLA2_ASLOTS 9
-#define DA_MLA2_VSLOTS 3
-#define DA_MLA2_PBUFS 1
-#endif
-#endif
-constexpr int kQTmemBlocks = DA_MLA2_QTMEM;    // Q blocks 0 .. kQTmemBlocks-1 live in TMEM
+constexpr int kQTmemBlocks = 4;                 // Q blocks 0 .. kQTmemBlocks-1 live in TMEM
 constexpr int kQSmemBlocks = kBlocks - kQTmemBlocks;
 constexpr int kQBlockBytes = 64 * 128;     // [64 heads x 64 dims], 128-byte swizzle: a Q block (and a 64-key block of P)
 constexpr int kKBlockBytes = kHalf * 128;  // [kHalf keys x 64 dims]: a K block of one CTA
-constexpr int kASlots = DA_MLA2_ASLOTS;         // ring of TMA-streamed K blocks
+constexpr int kASlots = 9;                      // ring of TMA-streamed K blocks: one tile
 constexpr int kGroup = 3;                       // K blocks per ring barrier: the issue loop pays per barrier wait and commit
 constexpr int kAGroups = kASlots / kGroup;
 static_assert(kASlots % kGroup == 0 && (kDim / 64) % kGroup == 0, "blocks travel in groups");
 constexpr int kTileGroups = (kDim / 64) / kGroup;   // groups per tile
 constexpr int kRingTiles = kAGroups / kTileGroups;  // the ring holds a whole number of tiles: a group's slot is static
 static_assert(kAGroups % kTileGroups == 0, "the K ring holds whole tiles");
-constexpr int kVSlots = DA_MLA2_VSLOTS;         // ring of V half-tiles
+constexpr int kVSlots = 3;                      // ring of V half-tiles
 constexpr int kVSlotBytes = kVBlocks * kKBlockBytes;
-constexpr int kPBufs = DA_MLA2_PBUFS;          // P tiles in shared memory
+constexpr int kPBufs = 1;                       // P tiles in shared memory
 constexpr int kPBytes = (kTile / 64) * kQBlockBytes;  // [64 heads x kTile keys]
 constexpr int kQStageSlots = (kQTmemBlocks * kQBlockBytes + kVSlotBytes - 1) / kVSlotBytes;  // V slots that stage Q at first
 constexpr int kOffQ = 0;
@@ -154,6 +136,11 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
         return;
     }
     const int n_tiles = (k_end - k_begin + kTile - 1) / kTile;
+    // With ALiBi the bias, and with it every head's row maximum, grows towards the end of the sequence: walked
+    // front to back, every tile would raise the reference maximum of the steep heads and take the rescale path.
+    // Walked back to front the first tiles set the maximum.  `tile_of(t)` is the tile the t-th step works on.
+    const bool backwards = p.is_alibi != 0;
+    auto tile_of = [&](int t) { return backwards ? n_tiles - 1 - t : t; };
 
     uint8_t *q_s = smem + kOffQ;
     uint8_t *a_s = smem + kOffA;
@@ -243,7 +230,7 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
         int gs = 0;
         uint32_t round = 0;
         for (int t = 0; t < n_tiles && ok; ++t) {
-            const int key0 = k_begin + t * kTile + (int)rank * kHalf;  // this CTA's first key of the tile
+            const int key0 = k_begin + tile_of(t) * kTile + (int)rank * kHalf;  // this CTA's first key of the tile
             const int rows = max(0, min(kHalf, k_end - key0));
             const size_t tok0 = rows > 0 ? kv_tile_row(p, b, seq_begin, key0) : 0;
             // rows of the tile are consecutive in the cache, except across the pages of a short-page cache
@@ -410,7 +397,7 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
         const int lt = tid - kLoaderWarp0 * 32;  // 0..127
         const int n_halves = 2 * n_tiles;
         for (int i = 0; i < n_halves && ok; ++i) {
-            const int key0 = k_begin + (i >> 1) * kTile + (i & 1) * kHalf;
+            const int key0 = k_begin + tile_of(i >> 1) * kTile + (i & 1) * kHalf;
             const int rows = max(0, min(kHalf, k_end - key0));
             const size_t tok0 = rows > 0 ? kv_tile_row(p, b, seq_begin, key0) : 0;
             const int vs = i % kVSlots;
@@ -489,7 +476,7 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag)) != 0;
         };
         for (int t = 0; t < n_tiles; ++t) {
-            const int key0 = k_begin + t * kTile + kh * kHalf + ch * 32;  // first key of this thread's 32 columns
+            const int key0 = k_begin + tile_of(t) * kTile + kh * kHalf + ch * 32;  // first key of this thread's 32 columns
             const int rows = k_end - key0;                                 // columns >= rows are past the end
             const uint32_t s_addr = lane_base + kColS + (t & 1) * kHalf + ch * 32;
             if (ok) ok = wait_all(&s_full[t & 1], (uint32_t)(t / 2) & 1u);
