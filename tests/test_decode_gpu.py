@@ -507,3 +507,34 @@ def test_integer_kv_cache(native_lib, oracle, bits, dt, hq, hk, d, lens, alibi, 
     assert_close(o, expect, w.name)
     fin = torch.isfinite(lse_e)
     assert (lse.cpu()[fin] - lse_e[fin]).abs().max().item() <= 2e-3
+
+
+# Scores whose row maximum keeps rising along the sequence: the tensor-core kernels then have to raise their
+# lazy reference maximum (and rescale the accumulator rows in tensor memory) many times, which seeded N(0,1)
+# inputs hardly ever ask for.  Covers the four-stream kernel (groups of at most 32), the kernel for larger
+# groups and head dim 256, and the latent-KV pair kernel; with ALiBi the same kernels walk the keys back to front.
+@pytest.mark.parametrize("hq,hk,d,dv", [(32, 1, 128, 128), (64, 8, 128, 128), (16, 2, 64, 64), (64, 1, 128, 128),
+                                        (16, 2, 256, 256), (128, 1, 576, 512)])
+@pytest.mark.parametrize("alibi", [False, True])
+@pytest.mark.parametrize("splits", [0, 1])
+def test_rising_scores_take_the_rescale_path(native_lib, oracle, hq, hk, d, dv, alibi, splits):
+    if alibi and d == 576:
+        pytest.skip("covered by the interface tests")
+    lens = [2048 + 37, 700]
+    w = synth.Workload(f"rising_{hq}_{hk}_{d}", torch.bfloat16, hq, hk, d, dv, lens, dist="normal", scale=0.5, seed=29,
+                       is_alibi=alibi, mla=(d == 576))
+    q, k, v, cu = w.make("cpu")
+    # key j of a sequence is scaled by 0.25 + 4 j / len: score magnitudes, and with them the running maximum, grow
+    # (latent-KV rows: only the 64 columns that are not also V, three times as steeply, so that V keeps its range)
+    for b, n in enumerate(lens):
+        pos = torch.arange(n, dtype=torch.float32) / n
+        if d == 576:
+            k[cu[b]:cu[b] + n, :, 512:] = (k[cu[b]:cu[b] + n, :, 512:].float() * (0.25 + 12.0 * pos).view(n, 1, 1)).to(k.dtype)
+        else:
+            k[cu[b]:cu[b] + n] = (k[cu[b]:cu[b] + n].float() * (0.25 + 4.0 * pos).view(n, 1, 1)).to(k.dtype)
+    scale = 0.5  # (1/sqrt(dim) would be 0.04 .. 0.125): the row maxima climb by some twenty units of log2, threshold 8
+    expect, lse_e = oracle.attn_cpu(q, k, v, cu, dim_v=w.dim_v, is_alibi=alibi, return_lse=True, softmax_scale=scale)
+    o, lse = run_cabi(native_lib, w, q.to(DEV), k.to(DEV), v.to(DEV) if v is not None else None, cu.to(DEV),
+                      num_splits=splits, want_lse=True, softmax_scale=scale)
+    assert_close(o, expect, w.name)
+    assert (lse.cpu() - lse_e).abs().max().item() <= 5e-3
