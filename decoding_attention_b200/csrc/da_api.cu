@@ -337,6 +337,24 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
             const int64_t one_wave = slots / units;
             const bool fills = units * one_wave * 5 >= slots * 4;  // at least 80 % of the slots get a CTA
             if (fills && (tiles_per_unit + one_wave - 1) / one_wave >= kMinTiles) splits = one_wave;
+            if (max_len <= 2048) {
+                // Short sequences: a CTA's set-up and the merge launch weigh as much as the keys.  Cost of a split
+                // count in keys' worth of time: waves x (set-up + chunk) + merge (measured, 32 heads x dim 128:
+                // 8 x 1024 keys 35.8 us with 4 splits, 28.7 us unsplit; 4 x 1024 keys 23.6 / 21.5 / 24.6 us with 3 / 2 / 1).
+                const int64_t kSetupKeys = 384, kMergeKeys = 512;
+                int64_t best_cost = INT64_MAX;
+                for (int64_t s = 1; s <= tiles_per_unit && s <= 64; ++s) {
+                    const int64_t tpc = (tiles_per_unit + s - 1) / s;
+                    if (s > 1 && tpc < kMinTiles) break;
+                    if ((tiles_per_unit + tpc - 1) / tpc != s) continue;
+                    const int64_t waves = (units * s + slots - 1) / slots;
+                    const int64_t cost = waves * (kSetupKeys + tpc * tile) + (s > 1 ? kMergeKeys : 0);
+                    if (cost < best_cost) {
+                        best_cost = cost;
+                        splits = s;
+                    }
+                }
+            }
         }
     }
     if (splits < 1) splits = 1;

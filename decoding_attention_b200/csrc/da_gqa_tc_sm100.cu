@@ -20,7 +20,7 @@
 // Dims 64 and 128 run two independent softmax streams (even / odd tiles, one accumulator each,
 // merged at the end): 16 softmax warps.  Dim 256 has room for one accumulator only and runs one
 // stream over both S buffers: 8 softmax warps; its 64 KB tiles outlast a tile's softmax chain.
-// Then one TMA producer warp and one warp for TMEM allocation + MMA issue.  Lazy reference max as
+// Then one TMA producer warp, one warp for TMEM allocation + issue of S, one for the issue of P.V.  Lazy reference max as
 // in the MLA kernel.  Every wait is bounded (the per-tile rendezvous of the softmax threads is an
 // mbarrier).
 #include <type_traits>
@@ -60,8 +60,8 @@ struct GqaCfg {
     static constexpr int kNumBars = 1 + 2 * kStages + 11;
     static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16 + 1024;
     static constexpr int kSoftmaxWarps = 4 * kColSplit;
-    static constexpr int kProducerWarp = kSoftmaxWarps, kMmaWarp = kSoftmaxWarps + 1;
-    static constexpr int kThreads = (kSoftmaxWarps + 2) * 32;
+    static constexpr int kProducerWarp = kSoftmaxWarps, kMmaWarp = kSoftmaxWarps + 1, kPvWarp = kSoftmaxWarps + 2;
+    static constexpr int kThreads = (kSoftmaxWarps + 3) * 32;
     static constexpr int kOutPer = D / kColSplit;             // output columns per thread in the epilogue
     static_assert(D == 64 || D == 128 || D == 256, "head dim");
     static_assert(kColO + kStreams * D <= kTmemCols, "TMEM budget");
@@ -228,14 +228,18 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
             __syncwarp();
         }
     } else if (warp == kMmaWarp) {
-        // ---------------- MMA issuer ----------------
+        // ---------------- issuer of S = Q.K^T ----------------
+        // S and P.V have an issuing warp each (this one and kPvWarp): with contractions this small the issue loop --
+        // barrier waits, commits -- sets the pace, and one warp doing both needed about 1 500 cycles per tile.
         const uint32_t leader = elect_one();
-        const uint32_t q_addr = smem_u32(q_s), k_addr = smem_u32(k_s), v_addr = smem_u32(v_s), p_addr = smem_u32(p_s);
-        const uint64_t q_desc0 = smem_desc(q_addr, 16, 1024, 2);            // K-major, 8-row groups 1 KB apart
-        const uint64_t k_desc0 = smem_desc(k_addr, 16, 1024, 2);
-        const uint64_t v_desc0 = smem_desc(v_addr, kKBlockBytes, 1024, 2);  // MN-major: 64-col blocks LBO apart
-        const uint64_t p_desc0 = smem_desc(p_addr, kRows * 16, 128, 0);     // core matrices, 8-key chunks 2 KB apart
-        auto issue_qk = [&](int t) {
+        const uint64_t q_desc0 = smem_desc(smem_u32(q_s), 16, 1024, 2);  // K-major, 8-row groups 1 KB apart
+        const uint64_t k_desc0 = smem_desc(smem_u32(k_s), 16, 1024, 2);
+        ok = mbar_wait(q_full, 0, abort_flag);
+        for (int t = 0; t < n_tiles && ok; ++t) {
+            ok = mbar_wait(&kv_full[t % kStages], (uint32_t)(t / kStages) & 1u, abort_flag);
+            if (ok && t >= 2) ok = mbar_wait(&s_empty[t & 1], ((uint32_t)(t / 2) & 1u) ^ 1u, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
             const uint64_t kd = k_desc0 + (uint64_t)(((t % kStages) * kKStageBytes) >> 4);
             const uint32_t d = tmem_base + kColS + (t & 1) * kTile;
 #pragma unroll
@@ -247,26 +251,19 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                 }
             }
             umma_commit(&s_full[t & 1], leader);
-        };
-        ok = mbar_wait(q_full, 0, abort_flag);
-        if (ok) ok = mbar_wait(&kv_full[0], 0, abort_flag);
-        if (ok) {
-            tc_fence_after();
-            issue_qk(0);
         }
+        __syncwarp();
+    } else if (warp == C::kPvWarp) {
+        // ---------------- issuer of O += P.V ----------------
+        const uint32_t leader = elect_one();
+        const uint64_t v_desc0 = smem_desc(smem_u32(v_s), kKBlockBytes, 1024, 2);  // MN-major: 64-col blocks LBO apart
+        const uint64_t p_desc0 = smem_desc(smem_u32(p_s), kRows * 16, 128, 0);     // core matrices, 8-key chunks 2 KB apart
         for (int t = 0; t < n_tiles && ok; ++t) {
-            if (t + 1 < n_tiles) {
-                const int t1 = t + 1;
-                ok = mbar_wait(&kv_full[t1 % kStages], (uint32_t)(t1 / kStages) & 1u, abort_flag);
-                if (ok && t1 >= 2) ok = mbar_wait(&s_empty[t1 & 1], ((uint32_t)(t1 / 2) & 1u) ^ 1u, abort_flag);
-                if (!ok) break;
-                tc_fence_after();
-                issue_qk(t1);
-            }
+            const int st = t % kStages;
             ok = mbar_wait(&p_full[t & 1], (uint32_t)(t / 2) & 1u, abort_flag);
+            if (ok) ok = mbar_wait(&kv_full[st], (uint32_t)(t / kStages) & 1u, abort_flag);  // (long complete: this warp's own view of the V tile)
             if (!ok) break;
             tc_fence_after();
-            const int st = t % kStages;
             const uint64_t pd = p_desc0 + (uint64_t)((((kStreams == 2) ? (t & 1) : 0) * kPBytes) >> 4);
             const uint64_t vd = v_desc0 + (uint64_t)((st * kKStageBytes) >> 4);
 #pragma unroll
