@@ -164,7 +164,6 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
     uint64_t *s_empty = pv_done + 4;       // rank 0: every softmax warp of the pair has read its S columns
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + kOffMisc);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-    volatile int *s_issued = reinterpret_cast<volatile int *>(tmem_slot + 2);  // tiles whose S the rank-0 CTA has issued
     __nv_bfloat16 *x_max = reinterpret_cast<__nv_bfloat16 *>(smem + kOffXch);  // [2][256] tile maxima, rounded up
     float *x_sum = reinterpret_cast<float *>(smem + kOffXch);                   // [256] row sums, after the last tile
 
@@ -190,7 +189,6 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             }
         }
         *abort_flag = 0;
-        *s_issued = 0;
         mbar_fence_init();
     }
     if (warp == kSWarp) tmem_alloc(tmem_slot, kTmemCols);
@@ -328,7 +326,6 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
                 }
                 if (!ok) break;
                 umma2_commit_both(&s_full[t & 1], leader);
-                if (leader) *s_issued = t + 1;
             }
         }
         __syncwarp();
@@ -341,20 +338,6 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             for (int t = 0; t < n_tiles && ok; ++t) {
                 ok = mbar_wait(&p_full[2 * (t & 1)], (uint32_t)(t / 2) & 1u, abort_flag);
                 if (!ok) break;
-                // S(t+1) goes into the tensor pipe first: the softmax of tile t+1, which waits for it, is the longer
-                // chain, and P.V(t) then runs beside that softmax.
-                {
-                    const int want = min(t + 2, n_tiles);
-                    const long long t0 = clock64();
-                    while (*s_issued < want) {
-                        if (*abort_flag || clock64() - t0 > kMaxWaitCycles) {
-                            *abort_flag = 1;
-                            ok = false;
-                            break;
-                        }
-                    }
-                    if (!ok) break;
-                }
                 tc_fence_after();
                 const uint32_t d = tmem_base + kColO;
                 const uint64_t pd = p_desc0 + (uint64_t)((((t % kPBufs) * kPBytes)) >> 4);
