@@ -14,11 +14,12 @@
 // does four times the useful work and still idles; the softmax latency of four units overlaps.
 // P_q lives in tensor memory (A operand of the second contraction): 4 x 32 columns whose lanes outside
 // quadrant q are zeroed once.  Tensor memory: S 4 x 64 | P 4 x 32 | O D columns.
-// K and V units travel through separate rings of TMA boxes (a K unit is free after its S, a V unit
-// waits for the softmax of its unit).  All P.V contractions are issued in unit order by one thread, so a
-// quadrant that has to rescale its accumulator rows (rare: lazy reference max) only has to see the
-// three units before its own retire: the next P.V cannot be issued before this quadrant delivers P.
-// Every wait is bounded.  The reference runs this shape with one CTA per query head
+// K and V units travel through separate rings (a K unit is free after its S, a V unit waits for the
+// softmax of its unit): K by TMA boxes, V by 16-byte cp.async of four loader warps.  Warps: 8 softmax (two per
+// quadrant), TMA producer, S issuer, P.V issuer, 4 V loaders.  All P.V contractions are issued in unit order
+// by one warp, so a quadrant that has to rescale its accumulator rows (rare: lazy reference max) only has to
+// see the three units before its own retire: the next P.V cannot be issued before this quadrant delivers P.
+// Under ALiBi the units are walked back to front, which keeps that path rare.  Every wait is bounded.  The reference runs this shape with one CTA per query head
 // (csrc/kernel/decoding_attn/decoding_fwd_hd128_hdv128.cu:9-25), reading K and V once per head.
 #include <type_traits>
 
