@@ -663,9 +663,10 @@ def main():
     opt = ap.parse_args()
     opt.warmup = max(opt.warmup, 3)
     if opt.traffic is None and opt.seqs == SEQS_PER_GPU:
-        # dram__bytes_read.sum + dram__bytes_write.sum of one da_split_kernel launch, captured with ncu on
-        # the 32-sequence case (297.4 MB for 290.9 MB of KV) and scaled to the full workload by the keys read.
-        opt.traffic = 2.480e9
+        # DRAM bytes of one da_split_kernel launch, from an ncu capture of the 32-sequence case (291.27 MB read
+        # for 290.94 MB of KV: x 1.0011, which grows with the keys read) plus the 2.1 MB of output rows the
+        # unsplit full launch writes (the small case runs split and also writes partials, which this launch does not).
+        opt.traffic = 2.4313e9
     if opt.profile_config:
         run_profile_config(opt)
     elif opt.impl == "reference":
