@@ -27,7 +27,7 @@ class DecodeArgs(ctypes.Structure):
         ("head_k", ctypes.c_int64), ("dim", ctypes.c_int64), ("dim_v", ctypes.c_int64),
         ("q_row_stride", ctypes.c_int64), ("k_row_stride", ctypes.c_int64), ("v_row_stride", ctypes.c_int64),
         ("o_row_stride", ctypes.c_int64),
-        ("softmax_scale", ctypes.c_float), ("reserved0", ctypes.c_uint32),
+        ("softmax_scale", ctypes.c_float), ("total_k", ctypes.c_uint32),
         ("lse", ctypes.c_void_p), ("o_f32", ctypes.c_void_p),
         ("kv_pos_offset", ctypes.c_void_p), ("kv_total_len", ctypes.c_void_p),
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
@@ -118,6 +118,7 @@ def make_args(q, k, v, o, cu_seq_k, max_seq_k, dim_v, is_alibi=False, softmax_sc
     a.num_splits = int(num_splits)
     a.q, a.k, a.v, a.o, a.cu_seq_k = _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(cu_seq_k)
     a.max_seq_k = int(max_seq_k)
+    a.total_k = min(int(k.shape[0]), 0xFFFFFFFF) if block_table is None and k.dim() == 3 else 0  # packed cache: its rows
     a.batch = cu_seq_k.numel() - 1
     if block_table is not None and k.dim() == 4:  # [num_pages, page_size, head_k, dim] -> rows
         k = k.view(-1, k.shape[2], k.shape[3])

@@ -124,6 +124,7 @@ Outputs run(const at::Tensor &q, const at::Tensor &k, const std::optional<at::Te
 
     a.cu_seq_k = cu_seq_k.data_ptr<int32_t>();
     a.max_seq_k = max_seq_k;
+    a.total_k = block_table ? 0u : (uint32_t)std::min<int64_t>(total_k, 0xFFFFFFFFll);  // a packed cache's rows are the batch's keys
     a.batch = batch;
     a.head_q = head_q;
     a.head_k = head_k;

@@ -57,7 +57,9 @@ typedef struct da_decode_args {
     int64_t q_row_stride, k_row_stride, v_row_stride, o_row_stride;
 
     float softmax_scale; /* <= 0 selects 1/sqrt(dim) (csrc/ops/decoding_attn.cpp:54) */
-    uint32_t reserved0;
+    uint32_t total_k; /* optional hint: rows of k that belong to the batch's sequences (for a packed cache, its row
+                       * count), 0 = unknown.  With it the split planner can tell a ragged batch (mean length well
+                       * below max_seq_k) from a uniform one; results do not depend on it. */
 
     float *lse;   /* optional device [batch, head_q]: natural-log sum-exp of the scaled scores */
     float *o_f32; /* optional device [batch, head_q, dim_v] packed: the result before rounding */
