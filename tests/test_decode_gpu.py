@@ -538,3 +538,26 @@ def test_rising_scores_take_the_rescale_path(native_lib, oracle, hq, hk, d, dv, 
                       num_splits=splits, want_lse=True, softmax_scale=scale)
     assert_close(o, expect, w.name)
     assert (lse.cpu() - lse_e).abs().max().item() <= 5e-3
+
+
+def test_total_k_hint_changes_the_plan_not_the_result(native_lib, oracle):
+    """A ragged batch of fewer latent-KV sequences than CTA slots: with the optional total_k hint the planner
+    splits the long sequences, without it every sequence runs unsplit; both agree with the oracle."""
+    lens = [2048, 2000] + [64 + 7 * i for i in range(58)]  # 60 sequences on 74 pair slots, two of them long
+    w = synth.Workload("ragged_mla", torch.bfloat16, 128, 1, 576, 512, lens, dist="normal", scale=0.5, seed=41, mla=True)
+    q, k, v, cu = w.make("cpu")
+    expect = oracle.attn_cpu(q, k, v, cu, dim_v=w.dim_v)
+    dq, dk, dcu = q.to(DEV), k.to(DEV), cu.to(DEV)
+    plans = []
+    for hint in (True, False):
+        o = torch.empty(len(lens), w.head_q, w.dim_v, dtype=w.dtype, device=DEV)
+        args = native_lib.make_args(dq, dk, None, o, dcu, max(lens), w.dim_v, stream=torch.cuda.current_stream().cuda_stream)
+        assert args.total_k == sum(lens)
+        if not hint:
+            args.total_k = 0
+        plans.append(native_lib.num_splits(args))
+        native_lib.decode_fwd(args)
+        torch.cuda.synchronize()
+        assert native_lib.device_status() == native_lib.DA_OK
+        assert_close(o, expect, f"{w.name}_hint{hint}")
+    assert plans[0] > plans[1] == 1
