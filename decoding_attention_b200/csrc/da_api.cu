@@ -349,6 +349,14 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
         // Fewer units than CTA slots: one full wave of equal chunks beats several waves of short CTAs
         // (measured: 16 K keys x 32 heads 75.7 -> 50.1 us, 64 K keys 190 -> 167 us), as long as a chunk
         // still amortises a CTA's set-up.
+        // A ragged batch (the caller's total_k hint puts the mean length under three quarters of max_seq_k) with
+        // half as many units again as CTA slots balances itself once it is launched longest first: unsplit it saves
+        // the partials and the CTAs that find their range empty (96 / 128 / 192 sequences of 512-4096 keys, 8 KV
+        // heads: 157 -> 142, 199 -> 187, 304 -> 291 us).
+        if (a.total_k > 0 && a.batch >= 16 && units * 2 >= slots * 3) {
+            const int64_t mean_tiles = ((int64_t)a.total_k / a.batch + tile - 1) / tile;
+            if (mean_tiles * 4 <= tiles_per_unit * 3) splits = 1;
+        }
         if (units <= slots) {
             const int64_t one_wave = slots / units;
             const bool fills = units * one_wave * 5 >= slots * 4;  // at least 80 % of the slots get a CTA
