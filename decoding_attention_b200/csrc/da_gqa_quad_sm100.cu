@@ -194,15 +194,19 @@ da_gqa_quad_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q
                 }
             }
             if (rows < kUnit) {
-                // Ragged last unit: plain loads into the 128-byte-swizzled layout, rows past the end zeroed
-                // (the tensor maps must not be asked for rows beyond the sequence).
+                // Ragged last unit: 16-byte cp.async into the 128-byte-swizzled layout, rows past the end and
+                // columns past the real head dim zero-filled (the tensor maps must not be asked for rows beyond the
+                // sequence).  All of the warp's copies are in flight at once: one memory latency, where a loop of
+                // loads and stores took 2-3 us, on the one unit the whole CTA waits for.
                 constexpr int kChunks = D / 8;  // 16-byte chunks per row
                 for (int i = lane; i < kUnit * kChunks; i += 32) {
                     const int r = i / kChunks, c = i % kChunks;
-                    uint4 kv = make_uint4(0, 0, 0, 0);
-                    if (r < rows && c * 8 < dreal) kv = *reinterpret_cast<const uint4 *>(k_g + row_of(r) * p.k_row_stride + c * 8);  // columns past the real head dim stay zero
-                    *reinterpret_cast<uint4 *>(kd + (c >> 3) * kKBlockBytes + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = kv;
+                    const bool real = r < rows && c * 8 < dreal;
+                    const T *src = k_g + row_of(real ? r : 0) * p.k_row_stride + (real ? c * 8 : 0);
+                    cp_async16(kd + (c >> 3) * kKBlockBytes + r * 128 + (((c & 7) ^ (r & 7)) << 4), src, real ? 16u : 0u);
                 }
+                cp_async_commit();
+                cp_async_wait<0>();
                 fence_proxy_async();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&k_full[ks]);

@@ -206,21 +206,22 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                     }
                 }
             } else {
-                // Ragged tail: plain loads into the 128-byte-swizzled layout, rows past the end zeroed
-                // (the tensor maps must not be asked for rows beyond the sequence).
+                // Ragged tail: 16-byte cp.async into the 128-byte-swizzled layout, rows past the end and columns past
+                // the real head dim zero-filled (the tensor maps must not be asked for rows beyond the sequence).
+                // All of the warp's copies are in flight at once: one memory latency, where a loop of loads and
+                // stores took 2-3 us, on the one tile the whole CTA waits for.
                 constexpr int kChunks = kDim / 8;  // 16-byte chunks per row
                 for (int i = lane; i < kTile * kChunks; i += 32) {
                     const int r = i / kChunks, c = i % kChunks;
-                    uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
-                    if (r < rows && c * 8 < dreal) {  // columns past the real head dim stay zero
-                        const size_t row = row_of(r);
-                        kv = *reinterpret_cast<const uint4 *>(k_g + row * p.k_row_stride + c * 8);
-                        vv = *reinterpret_cast<const uint4 *>(v_g + row * p.v_row_stride + c * 8);
-                    }
+                    const bool real = r < rows && c * 8 < dreal;
+                    const size_t row = row_of(real ? r : 0);
+                    const int col = real ? c * 8 : 0;
                     const int off = (c >> 3) * kKBlockBytes + r * 128 + (((c & 7) ^ (r & 7)) << 4);
-                    *reinterpret_cast<uint4 *>(kd + off) = kv;
-                    *reinterpret_cast<uint4 *>(vd + off) = vv;
+                    cp_async16(kd + off, k_g + row * p.k_row_stride + col, real ? 16u : 0u);
+                    cp_async16(vd + off, v_g + row * p.v_row_stride + col, real ? 16u : 0u);
                 }
+                cp_async_commit();
+                cp_async_wait<0>();
                 fence_proxy_async();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&kv_full[st]);

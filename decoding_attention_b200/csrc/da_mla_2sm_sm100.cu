@@ -253,14 +253,16 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
                         }
                     }
                 } else {
-                    // ragged end of the key range: plain loads, rows past the end zeroed (the tensor map
-                    // must not be asked for rows beyond the sequence)
+                    // ragged end of the key range (the tensor map must not be asked for rows beyond the sequence)
+                    // (16-byte cp.async, all of the warp's copies in flight at once; rows past the end zero-filled)
                     for (int i = lane; i < kGroup * kHalf * 8; i += 32) {
                         const int jj = i / (kHalf * 8), r = (i >> 3) % kHalf, cc = i & 7;
-                        uint4 v = make_uint4(0, 0, 0, 0);
-                        if (r < rows) v = *reinterpret_cast<const uint4 *>(k_g + row_of(r) * p.k_row_stride + (g * kGroup + jj) * 64 + cc * 8);
-                        *reinterpret_cast<uint4 *>(dst + jj * kKBlockBytes + r * 128 + ((cc ^ (r & 7)) << 4)) = v;
+                        const bool real = r < rows;
+                        const T *src = k_g + (real ? row_of(r) * p.k_row_stride + (g * kGroup + jj) * 64 + cc * 8 : 0);
+                        cp_async16(dst + jj * kKBlockBytes + r * 128 + ((cc ^ (r & 7)) << 4), src, real ? 16u : 0u);
                     }
+                    cp_async_commit();
+                    cp_async_wait<0>();
                     fence_proxy_async();
                     __syncwarp();
                     if (lane == 0) {
