@@ -130,18 +130,19 @@ constexpr float kLazyRaise = 8.0f;
 // One K or V tile of a paged cache whose pages are shorter than the tile: one TMA box per page (whole
 // tile) or one bulk copy per row (ragged tail), the page of every run or row looked up in the block table.
 // Out of line, so that the common path's registers do not pay for it.  The caller has posted expect_tx.
+// `my_page` (whole tiles): lane i holds the tile's i-th page, read by the caller with one coalesced load ahead of
+// its wait for the stage -- one table look-up after another by a single lane, twice per tile (K and V), took
+// longer than the two stages of a tile pipeline can hide (config 2 at 16-key pages: 464 us against 377 us packed).
 static __device__ __noinline__ void load_tile_short_pages(const int *block_table, long long table_stride, int page_shift, int b, int key0,
                                                    int rows, int tile, bool whole, uint8_t *dst, int row_bytes,
                                                    const CUtensorMap *tm, int hk, const uint8_t *g_base,
-                                                   long long g_row_bytes, uint64_t *bar, int lane) {
+                                                   long long g_row_bytes, uint64_t *bar, int lane, int my_page) {
     const int run = 1 << page_shift;
     const int *pages = block_table + (size_t)b * table_stride;
     if (whole) {
-        if (lane == 0) {
-            for (int k0 = 0; k0 < tile; k0 += run) {
-                const int row = (pages[(key0 + k0) >> page_shift] << page_shift) + ((key0 + k0) & (run - 1));
-                tma_load_tile_3d(dst + (size_t)k0 * row_bytes, tm, 0, hk, row, bar);
-            }
+        for (int i = 0; i < (tile >> page_shift); ++i) {  // (tiles start on a page boundary)
+            const int row = __shfl_sync(0xffffffffu, my_page, i) << page_shift;
+            if (lane == 0) tma_load_tile_3d(dst + ((size_t)i << page_shift) * row_bytes, tm, 0, hk, row, bar);
         }
     } else {
         for (int r = lane; r < rows; r += 32) {
@@ -233,9 +234,13 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
             const int key0 = k_begin + t * TILE;
             const int rows = min(TILE, k_end - key0);
             const size_t tok0 = kv_tile_row(p, b, seq_begin, key0);
+            const bool whole = p.use_tmap && rows == TILE;  // a partial tile must not read past the sequence
+            int my_page = 0;  // short pages: lane i reads the tile's i-th page from the block table, ahead of the wait
+            if (short_pages && whole && lane < (TILE >> p.page_shift)) {
+                my_page = p.block_table[(size_t)b * p.block_table_stride + (key0 >> p.page_shift) + lane];
+            }
             if (t >= STAGES) ok = mbar_wait(&empty_k[st], ph ^ 1u, abort_flag);
             if (!ok) break;
-            const bool whole = p.use_tmap && rows == TILE;  // a partial tile must not read past the sequence
             if (lane == 0) {
                 mbar_arrive_expect_tx(&full_k[st], (uint32_t)rows * C::K_ROW_BYTES);
                 if (whole && !short_pages) tma_load_tile_3d(ks + st * C::K_TILE_BYTES, &tm_k, 0, hk, (int)tok0, &full_k[st]);
@@ -245,7 +250,7 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
             if (short_pages) {
                 load_tile_short_pages(p.block_table, p.block_table_stride, p.page_shift, b, key0, rows, TILE, whole,
                                       ks + st * C::K_TILE_BYTES, C::K_ROW_BYTES, &tm_k, hk, kg,
-                                      p.k_row_stride * (long long)EBITS / 8, &full_k[st], lane);
+                                      p.k_row_stride * (long long)EBITS / 8, &full_k[st], lane, my_page);
             } else if (!whole) {
                 for (int r = lane; r < rows; r += 32) {
                     bulk_copy_g2s(ks + st * C::K_TILE_BYTES + r * C::K_ROW_BYTES, kg + (tok0 + r) * p.k_row_stride * EBITS / 8,
@@ -264,7 +269,7 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB) da_split_kernel(const Spl
                 if (short_pages) {
                     load_tile_short_pages(p.block_table, p.block_table_stride, p.page_shift, b, key0, rows, TILE, whole,
                                           vs + st * C::V_TILE_BYTES, C::V_ROW_BYTES, &tm_v, hk, vg,
-                                          p.v_row_stride * (long long)EBITS / 8, &full_v[st], lane);
+                                          p.v_row_stride * (long long)EBITS / 8, &full_v[st], lane, my_page);
                 } else if (!whole) {
                     for (int r = lane; r < rows; r += 32) {
                         bulk_copy_g2s(vs + st * C::V_TILE_BYTES + r * C::V_ROW_BYTES,
