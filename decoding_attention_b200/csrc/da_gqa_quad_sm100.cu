@@ -184,13 +184,20 @@ da_gqa_quad_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q
             const size_t tok0 = kv_tile_row(p, b, seq_begin, key0);
             auto row_of = [&](int r) { return kShortPages ? kv_tile_row(p, b, seq_begin, key0 + r) : tok0 + r; };
             uint8_t *kd = k_s + ks * kUnitBytes;
+            int my_page = 0;
+            if (kShortPages && rows == kUnit && lane < (kUnit >> p.page_shift)) {
+                my_page = p.block_table[(size_t)b * p.block_table_stride + (key0 >> p.page_shift) + lane];
+            }
             if (j >= kNK) ok = mbar_wait(&k_empty[ks], ((uint32_t)(j / kNK) & 1u) ^ 1u, abort_flag);
             if (!ok) break;
-            if (rows == kUnit && lane == 0) {
-                mbar_arrive_expect_tx(&k_full[ks], kUnitBytes);
+            if (rows == kUnit) {
+                if (lane == 0) mbar_arrive_expect_tx(&k_full[ks], kUnitBytes);
                 for (int k0 = 0; k0 < kUnit; k0 += run) {  // one box per run of consecutive rows (a page, or the unit)
-                    const int row = (int)row_of(k0);
-                    for (int kb = 0; kb < kBlocks; ++kb) tma_load_tile_3d(kd + kb * kKBlockBytes + k0 * 128, &tm_k, kb * 64, hk, row, &k_full[ks]);
+                    // (short pages: lane i has read the unit's i-th page, all lanes with one load; units start on a page boundary)
+                    const int row = kShortPages ? (__shfl_sync(0xffffffffu, my_page, k0 >> p.page_shift) << p.page_shift) : (int)tok0;
+                    if (lane == 0) {
+                        for (int kb = 0; kb < kBlocks; ++kb) tma_load_tile_3d(kd + kb * kKBlockBytes + k0 * 128, &tm_k, kb * 64, hk, row, &k_full[ks]);
+                    }
                 }
             }
             if (rows < kUnit) {

@@ -234,6 +234,13 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             // rows of the tile are consecutive in the cache, except across the pages of a short-page cache
             auto row_of = [&](int r) { return kShortPages ? kv_tile_row(p, b, seq_begin, key0 + r) : tok0 + r; };
             const int run = kShortPages ? (1 << p.page_shift) : kHalf;  // consecutive rows: a page, or the whole half tile
+            // Short pages: lane i reads the i-th page of this CTA's half tile from the block table once per tile, all
+            // lanes with one load (a look-up per page and group by the issuing lane alone took twelve dependent loads
+            // per tile, longer than the tile itself).
+            int my_page = 0;
+            if (kShortPages && rows == kHalf && lane < (kHalf >> p.page_shift)) {
+                my_page = p.block_table[(size_t)b * p.block_table_stride + (key0 >> p.page_shift) + lane];
+            }
             for (int g = 0; g < kBlocks / kGroup && ok; ++g) {
                 if (round > 0) ok = mbar_wait(&a_empty[gs], (round & 1u) ^ 1u, abort_flag);
                 if (!ok) break;
@@ -243,10 +250,11 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
                 // peer's TMA copies, or counted by hand when the peer had to write ragged blocks with stores.
                 // (No remote arrival per group: a cluster-scope release costs about a thousand cycles.)
                 if (rows == kHalf) {
-                    if (lane == 0) {
-                        if (rank == 0) mbar_arrive_expect_tx(&a_full[gs], 2 * kGroup * kKBlockBytes);
-                        for (int k0 = 0; k0 < kHalf; k0 += run) {
-                            const int row = (int)row_of(k0);
+                    if (lane == 0 && rank == 0) mbar_arrive_expect_tx(&a_full[gs], 2 * kGroup * kKBlockBytes);
+                    for (int k0 = 0; k0 < kHalf; k0 += run) {
+                        // (half tiles start on a page boundary: a page's first row is page << page_shift)
+                        const int row = kShortPages ? (__shfl_sync(0xffffffffu, my_page, k0 >> p.page_shift) << p.page_shift) : (int)tok0;
+                        if (lane == 0) {
 #pragma unroll
                             for (int jj = 0; jj < kGroup; ++jj)
                                 tma2_load_2d(dst + jj * kKBlockBytes + k0 * 128, &tm_k, (g * kGroup + jj) * 64, row, lead(&a_full[gs]));
