@@ -383,7 +383,7 @@ da_gqa_quad_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q
                 // This quadrant's previous P.V (unit j - 4) has finished: its P columns are free again.
                 ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[quad], (uint32_t)(n - 1) & 1u, abort_flag));
                 if (!ok) break;
-                if (__any_sync(0xffffffffu, raise)) {
+                if (__any_sync(0xffffffffu, raise && valid)) {
                     // Rare: the reference max of some row of this quadrant moved; rescale this thread's half of the
                     // row's accumulator columns in place.  Every P.V rewrites all 128 rows, so none may be in flight:
                     // those of units j-1, j-2, j-3 must have retired; the next one waits for this quadrant's P.

@@ -333,7 +333,7 @@ da_gqa_tc_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q, 
                 const int tp = t - kStreams;
                 ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(kStreams == 2) ? strm : (tp & 1)], (uint32_t)(tp >> 1) & 1u, abort_flag));
                 if (!ok) break;
-                if (__any_sync(0xffffffffu, raise)) {
+                if (__any_sync(0xffffffffu, raise && valid)) {
                     // Rare: the reference max of some row of this quadrant moved; rescale this thread's half
                     // of the row's accumulator columns in place.
                     tc_fence_after();
