@@ -76,8 +76,8 @@ constexpr int kOffA = kOffQ + kQSmemBlocks * kQBlockBytes;
 constexpr int kOffV = kOffA + kASlots * kKBlockBytes;
 constexpr int kOffP = kOffV + kVSlots * kVSlotBytes;
 constexpr int kOffBar = kOffP + kPBufs * kPBytes;
-// q_full, q_tmem, q_stage_full, q_copied, a_full/a_empty[kASlots], v_full/v_empty[kVSlots], s_full[2], p_full[2][2], pv_done[2][2], s_empty[2]
-constexpr int kNumBars = 4 + 2 * kAGroups + 2 * kVSlots + 12;
+// q_full, q_tmem, q_stage_full, q_copied, a_full/a_empty[kASlots], v_full/v_empty[kVSlots], s_full[2], p_full[2][2], pv_done[2][2], s_empty[2], o_stable[2]
+constexpr int kNumBars = 4 + 2 * kAGroups + 2 * kVSlots + 14;
 constexpr int kOffMisc = kOffBar + kNumBars * 8;          // tmem slot, abort flag
 constexpr int kOffXch = kOffMisc + 16;                    // bf16 [2][256] tile maxima, later float [256] row sums
 constexpr int kSmemBytes = kOffXch + 256 * 4 + 1024;      // + alignment slack
@@ -162,6 +162,7 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
     uint64_t *p_full = s_full + 2;         // rank 0: P block written by both CTAs
     uint64_t *pv_done = p_full + 4;
     uint64_t *s_empty = pv_done + 4;       // rank 0: every softmax warp of the pair has read its S columns
+    uint64_t *o_stable = s_empty + 2;      // rank 0: no softmax warp of the pair is rescaling its accumulator rows for this tile
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + kOffMisc);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     __nv_bfloat16 *x_max = reinterpret_cast<__nv_bfloat16 *>(smem + kOffXch);  // [2][256] tile maxima, rounded up
@@ -183,6 +184,7 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
         for (int s = 0; s < 2; ++s) {
             mbar_init(&s_full[s], 1);
             mbar_init(&s_empty[s], 2 * kSoftmaxWarps);
+            mbar_init(&o_stable[s], 2 * kSoftmaxWarps);
             for (int h = 0; h < 2; ++h) {
                 mbar_init(&p_full[2 * s + h], kSoftmaxWarps);  // the four warps of key half h, in both CTAs
                 mbar_init(&pv_done[2 * s + h], 1);
@@ -347,6 +349,10 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
             const uint64_t v_desc0 = smem_desc(smem_u32(v_s), kKBlockBytes, 1024, 2);  // V slot, MN-major
             for (int t = 0; t < n_tiles && ok; ++t) {
                 ok = mbar_wait(&p_full[2 * (t & 1)], (uint32_t)(t / 2) & 1u, abort_flag);
+                // P block 0 is complete once the warps of key half 0 have written it; the warps of key half 1 may
+                // still be rescaling their lanes' accumulator columns (the rare raised reference maximum), and
+                // every P.V rewrites all of O: wait until every softmax warp of the pair is past that point.
+                if (ok) ok = mbar_wait(&o_stable[t & 1], (uint32_t)(t / 2) & 1u, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d = tmem_base + kColO;
@@ -506,9 +512,10 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
                 m_ref = mx;
                 l *= alpha;
             }
-            if (t >= 1 && __any_sync(0xffffffffu, raise)) {
+            const bool rescale = t >= 1 && __any_sync(0xffffffffu, raise);
+            if (rescale) {
                 // Rare: the reference max of some row in this warp moved.  O must be idle (P.V of tile
-                // t-1 complete) while its rows are rescaled in place.
+                // t-1 complete, P.V of this tile held back by o_stable) while its rows are rescaled in place.
                 ok = wait_all(&pv_done[2 * ((t - 1) & 1) + 1], (uint32_t)((t - 1) / 2) & 1u);
                 if (!ok) continue;
                 tc_fence_after();
@@ -521,7 +528,11 @@ da_mla_2sm_kernel(const SplitParams p, const __grid_constant__ CUtensorMap tm_q,
                     tmem_st32(lane_base + kColO + ch * 128 + c * 32, buf);
                 }
                 tmem_wait_st();
-            } else if (kPBufs == 1 && t >= 1) {
+                tc_fence_before();
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive_remote_cta(lead(&o_stable[t & 1]));  // this warp's accumulator rows are as P.V(t) may find them
+            if (!rescale && kPBufs == 1 && t >= 1) {
                 // this thread's block of the single P buffer is still being read by its half of P.V of tile t-1
                 ok = wait_all(&pv_done[2 * ((t - 1) & 1) + kh], (uint32_t)((t - 1) / 2) & 1u);
                 if (!ok) continue;
