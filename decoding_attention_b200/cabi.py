@@ -12,7 +12,7 @@ LIB_PATH = os.environ.get("DA_LIB_PATH") or os.path.join(_PKG, "libdecoding_attn
 
 DA_OK, DA_ERR_INVALID_ARG, DA_ERR_UNSUPPORTED, DA_ERR_WORKSPACE, DA_ERR_CUDA, DA_ERR_TIMEOUT = range(6)
 
-EXPORTS = ["da_decode_fwd", "da_decode_fwd_host", "da_decode_fwd_static", "da_static_scratch_bytes", "da_decode_workspace_bytes", "da_decode_num_splits",
+EXPORTS = ["da_decode_fwd", "da_decode_fwd_host", "da_decode_fwd_static", "da_static_scratch_bytes", "da_decode_workspace_bytes", "da_decode_num_splits", "da_plan_num_splits",
            "da_merge_partials", "da_exchange_merge", "da_exchange_merge_bounded", "da_exchange_buffer_bytes", "da_set_profile_events", "da_selftest_wait_timeout", "da_device_status", "da_status_string", "da_last_error", "da_launch_count"]
 
 
@@ -65,6 +65,8 @@ def lib():
         l.da_decode_workspace_bytes.argtypes = [ctypes.POINTER(DecodeArgs)]
         l.da_decode_num_splits.restype = ctypes.c_int
         l.da_decode_num_splits.argtypes = [ctypes.POINTER(DecodeArgs)]
+        l.da_plan_num_splits.restype = ctypes.c_int
+        l.da_plan_num_splits.argtypes = [ctypes.POINTER(DecodeArgs), ctypes.c_int]
         l.da_merge_partials.restype = ctypes.c_int
         l.da_merge_partials.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64,
                                         ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
@@ -167,6 +169,11 @@ def workspace_bytes(args):
 
 def num_splits(args):
     return lib().da_decode_num_splits(ctypes.byref(args))
+
+
+def plan_num_splits(args, sm_count):
+    """Split count the planner picks for a device with `sm_count` SMs; touches no device."""
+    return lib().da_plan_num_splits(ctypes.byref(args), int(sm_count))
 
 
 def device_status():

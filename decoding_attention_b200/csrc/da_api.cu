@@ -497,6 +497,13 @@ int da_decode_num_splits(const da_decode_args_t *a) {
     return plan.num_splits;
 }
 
+int da_plan_num_splits(const da_decode_args_t *a, int sm_count) {
+    if (check_args(a) != DA_OK || sm_count <= 0) return -1;
+    Plan plan;
+    if (make_plan(*a, sm_count, &plan) != DA_OK) return -1;
+    return plan.num_splits;
+}
+
 int da_decode_fwd(const da_decode_args_t *a) {
     int rc = check_args(a);
     if (rc != DA_OK) return rc;

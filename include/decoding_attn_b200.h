@@ -149,6 +149,9 @@ size_t da_decode_workspace_bytes(const da_decode_args_t *args);
 
 /* The split count da_decode_fwd will use for these arguments (diagnostics / benchmarks). */
 int da_decode_num_splits(const da_decode_args_t *args);
+/* The same for a device with `sm_count` SMs, without touching any device (no pointer is dereferenced): what the
+ * host-side tests pin the planner's decisions with.  -1 on invalid arguments. */
+int da_plan_num_splits(const da_decode_args_t *args, int sm_count);
 
 /* Merges `num_parts` partial results of the same rows, each computed over a disjoint key range:
  *   o = sum_r exp(lse_r - LSE) o_r,  LSE = log sum_r exp(lse_r).
