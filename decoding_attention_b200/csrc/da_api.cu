@@ -346,9 +346,6 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
         // config 2, 2 048 units of up to 64 tiles, 396 us with the two splits the cap asks for, 377 us unsplit)
         if (a.batch < 16 && tiles_per_cta > kMaxTiles) tiles_per_cta = kMaxTiles;
         splits = (tiles_per_unit + tiles_per_cta - 1) / tiles_per_cta;
-        // Fewer units than CTA slots: one full wave of equal chunks beats several waves of short CTAs
-        // (measured: 16 K keys x 32 heads 75.7 -> 50.1 us, 64 K keys 190 -> 167 us), as long as a chunk
-        // still amortises a CTA's set-up.
         // A ragged batch (the caller's total_k hint puts the mean length under three quarters of max_seq_k) with
         // half as many units again as CTA slots balances itself once it is launched longest first: unsplit it saves
         // the partials and the CTAs that find their range empty (96 / 128 / 192 sequences of 512-4096 keys, 8 KV
@@ -357,6 +354,9 @@ int make_plan(const da_decode_args_t &a, int sm_count, Plan *plan) {
             const int64_t mean_tiles = ((int64_t)a.total_k / a.batch + tile - 1) / tile;
             if (mean_tiles * 4 <= tiles_per_unit * 3) splits = 1;
         }
+        // Fewer units than CTA slots: one full wave of equal chunks beats several waves of short CTAs
+        // (measured: 16 K keys x 32 heads 75.7 -> 50.1 us, 64 K keys 190 -> 167 us), as long as a chunk
+        // still amortises a CTA's set-up.
         if (units <= slots) {
             const int64_t one_wave = slots / units;
             const bool fills = units * one_wave * 5 >= slots * 4;  // at least 80 % of the slots get a CTA
